@@ -1,0 +1,449 @@
+// bf16 GEMM for sm_100a: TMA-fed shared-memory pipeline, tcgen05.mma with fp32 accumulators in TMEM, persistent
+// CTAs (one per SM), warp-specialised (TMA producer / MMA issuer / 4 epilogue warps), double-buffered accumulators
+// so that the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// One kernel covers the three layouts a Linear layer needs (forward Y = X W^T, dgrad dX = dY W, wgrad dW = dY^T X)
+// by letting either operand be K-major or MN-major in shared memory, and covers dim-0-sharded weights by giving
+// the B operand / the output a third "shard" coordinate:
+//   * forward with gathered weights:  B rows (output columns) come from R buffers `b_shard_stride` apart,
+//   * dgrad:                          the contraction runs over R weight shards,
+//   * wgrad with reduce-scatter:      output row block s is added into the buffer `c_shards[s]`, which may live in
+//                                     another GPU's memory (plain red.global over NVLink; never TMA).
+// Epilogues: bf16 store, fp32 store / accumulate / red.add, and the gated-MLP epilogue act(gate) * up computed from
+// a tile whose 256 accumulator columns are 128 gate columns followed by 128 up columns.
+//
+// Replaces the library GEMM calls behind the reference's `olmax/nn/functional.py:14-27` (linear) and
+// `olmax/nn/mlp.py:69-73` (gated MLP).
+#include "gemm.h"
+
+#include "host_common.h"
+#include "sm100.cuh"
+
+namespace ob {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int MN_BLOCK_BYTES = 64 * BK * 2;  // one 64(MN) x 64(K) MN-major block: 8 KiB
+constexpr int TMEM_COLS = 512;
+constexpr int GEMM_THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+
+struct KernelParams {
+  int M, N, Kc;
+  int M_s, N_s, Kc_s;
+  int m_tiles_per_shard, n_tiles_per_shard, k_iters_per_shard;
+  int m_shards, n_shards, k_shards;
+  int bn_out;  // output columns per tile: 256, or 128 for the gated epilogue
+  int epi;
+  float alpha;
+  void* c;
+  void* c2;
+  void* c3;
+  void* const* c_shards;
+  long long ldc;
+  int* status;
+};
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  float u = k0 * (x + k1 * x * x * x);
+  return 0.5f * x * (1.0f + tanhf(u));
+}
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const __grid_constant__ CUtensorMap tmB2, const KernelParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;                       // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;             // [STAGES]
+  uint64_t* tfull_bar = bars + 2 * STAGES;         // [2]
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull_bar[b], 1);
+      mbar_init(&tempty_bar[b], 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int m_tiles = p.m_shards * p.m_tiles_per_shard;
+  const int n_tiles = p.n_shards * p.n_tiles_per_shard;
+  const int total_tiles = m_tiles * n_tiles;
+  const int k_iters = p.k_shards * p.k_iters_per_shard;
+  const bool glu = (p.epi == EPI_SWIGLU || p.epi == EPI_GEGLU);
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      if (glu) tma_prefetch_desc(&tmB2);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int mt = tile % m_tiles, nt = tile / m_tiles;
+        const int m0 = (mt / p.m_tiles_per_shard) * p.M_s + (mt % p.m_tiles_per_shard) * BM;
+        const int n_shard = nt / p.n_tiles_per_shard;
+        const int n_local0 = (nt % p.n_tiles_per_shard) * p.bn_out;
+        for (int kit = 0; kit < k_iters; ++kit) {
+          const int k_shard = kit / p.k_iters_per_shard;
+          const int k_local = (kit % p.k_iters_per_shard) * BK;
+          const int k_glob = k_shard * p.Kc_s + k_local;
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 100);
+          if (!ok) break;
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_STAGE_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+          if (A_MN) {
+            tma_load_3d(sa, &tmA, &full_bar[stage], m0, k_glob, 0);
+            tma_load_3d(sa + MN_BLOCK_BYTES, &tmA, &full_bar[stage], m0 + 64, k_glob, 0);
+          } else {
+            tma_load_3d(sa, &tmA, &full_bar[stage], k_glob, m0, 0);
+          }
+          if (B_MN) {
+            // dims (N, Kc_s, k_shards): four 64-wide blocks along N
+            const int n0 = n_local0;  // MN-major B is never N-sharded
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              tma_load_3d(sb + j * MN_BLOCK_BYTES, &tmB, &full_bar[stage], n0 + j * 64, k_local, k_shard);
+          } else if (glu) {
+            tma_load_3d(sb, &tmB, &full_bar[stage], k_glob, n_local0, n_shard);
+            tma_load_3d(sb + B_STAGE_BYTES / 2, &tmB2, &full_bar[stage], k_glob, n_local0, n_shard);
+          } else {
+            tma_load_3d(sb, &tmB, &full_bar[stage], k_glob, n_local0, n_shard);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+        const int buf = it & 1;
+        const uint32_t tphase = (uint32_t)(it >> 1) & 1u;
+        ok = mbar_wait(&tempty_bar[buf], tphase ^ 1u, abort_flag, p.status, 200);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        for (int kit = 0; kit < k_iters; ++kit) {
+          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 201);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4) {
+            const uint64_t da = A_MN ? make_smem_desc(sa + k4 * 2048, MN_BLOCK_BYTES, 1024)
+                                     : make_smem_desc(sa + k4 * 32, 0, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + k4 * 2048, MN_BLOCK_BYTES, 1024)
+                                     : make_smem_desc(sb + k4 * 32, 0, 1024);
+            umma_ss(d_tmem, da, db, idesc, (kit | k4) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit(&tfull_bar[buf]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------- epilogue (warps 2..5) -------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    const int row_in_tile = q * 32 + lane;
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      const int buf = it & 1;
+      const uint32_t tphase = (uint32_t)(it >> 1) & 1u;
+      const int mt = tile % m_tiles, nt = tile / m_tiles;
+      const int m_shard = mt / p.m_tiles_per_shard;
+      const int m_local0 = (mt % p.m_tiles_per_shard) * BM;
+      const int n_shard = nt / p.n_tiles_per_shard;
+      const int n_local0 = (nt % p.n_tiles_per_shard) * p.bn_out;
+      const int m_valid = min(BM, p.M_s - m_local0);
+      const int n_valid = min(p.bn_out, p.N_s - n_local0);
+      const int n_glob0 = n_shard * p.N_s + n_local0;
+      ok = mbar_wait(&tfull_bar[buf], tphase, abort_flag, p.status, 300);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(q * 32) << 16);
+      const bool row_ok = row_in_tile < m_valid;
+      // Row base pointers.  With c_shards the output rows of shard s live in buffer c_shards[s].
+      long long row_off;
+      uint8_t* cbase;
+      if (p.c_shards != nullptr) {
+        cbase = reinterpret_cast<uint8_t*>(p.c_shards[m_shard]);
+        row_off = (long long)(m_local0 + row_in_tile) * p.ldc + n_glob0;
+      } else {
+        cbase = reinterpret_cast<uint8_t*>(p.c);
+        row_off = (long long)(m_shard * p.M_s + m_local0 + row_in_tile) * p.ldc + n_glob0;
+      }
+      if (!glu) {
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (c0 >= n_valid) break;  // warp-uniform
+          uint32_t r[32];
+          tmem_ld32(t_row + (uint32_t)c0, r);
+          tmem_ld_wait();
+          if (row_ok) {
+            const int nv = min(32, n_valid - c0);
+            if (p.epi == EPI_BF16) {
+              bf16* dst = reinterpret_cast<bf16*>(cbase) + row_off + c0;
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                if (g * 8 + 8 <= nv) {
+                  uint4 v;
+                  v.x = pack_bf16x2(__uint_as_float(r[g * 8 + 0]) * p.alpha, __uint_as_float(r[g * 8 + 1]) * p.alpha);
+                  v.y = pack_bf16x2(__uint_as_float(r[g * 8 + 2]) * p.alpha, __uint_as_float(r[g * 8 + 3]) * p.alpha);
+                  v.z = pack_bf16x2(__uint_as_float(r[g * 8 + 4]) * p.alpha, __uint_as_float(r[g * 8 + 5]) * p.alpha);
+                  v.w = pack_bf16x2(__uint_as_float(r[g * 8 + 6]) * p.alpha, __uint_as_float(r[g * 8 + 7]) * p.alpha);
+                  *reinterpret_cast<uint4*>(dst + g * 8) = v;
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j)
+                    if (g * 8 + j < nv) dst[g * 8 + j] = __float2bfloat16(__uint_as_float(r[g * 8 + j]) * p.alpha);
+                }
+              }
+            } else {
+              float* dst = reinterpret_cast<float*>(cbase) + row_off + c0;
+#pragma unroll
+              for (int g = 0; g < 8; ++g) {
+                if (g * 4 + 4 <= nv) {
+                  float4 v = make_float4(__uint_as_float(r[g * 4 + 0]) * p.alpha, __uint_as_float(r[g * 4 + 1]) * p.alpha,
+                                         __uint_as_float(r[g * 4 + 2]) * p.alpha, __uint_as_float(r[g * 4 + 3]) * p.alpha);
+                  float4* d4 = reinterpret_cast<float4*>(dst + g * 4);
+                  if (p.epi == EPI_F32) {
+                    *d4 = v;
+                  } else if (p.epi == EPI_F32_ACC) {
+                    float4 o = *d4;
+                    o.x += v.x; o.y += v.y; o.z += v.z; o.w += v.w;
+                    *d4 = o;
+                  } else {  // EPI_F32_RED: the destination may be another GPU's memory
+                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(d4), "f"(v.x), "f"(v.y),
+                                 "f"(v.z), "f"(v.w)
+                                 : "memory");
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    if (g * 4 + j < nv) {
+                      float v = __uint_as_float(r[g * 4 + j]) * p.alpha;
+                      if (p.epi == EPI_F32) dst[g * 4 + j] = v;
+                      else if (p.epi == EPI_F32_ACC) dst[g * 4 + j] += v;
+                      else atomicAdd(dst + g * 4 + j, v);
+                    }
+                  }
+                }
+              }
+            }
+          }
+        }
+      } else {
+        // gated epilogue: columns [0,128) = gate, [128,256) = up
+        bf16* cact = reinterpret_cast<bf16*>(p.c);
+        bf16* cg = reinterpret_cast<bf16*>(p.c2);
+        bf16* cu = reinterpret_cast<bf16*>(p.c3);
+        for (int c0 = 0; c0 < 128; c0 += 16) {
+          if (c0 >= n_valid) break;
+          uint32_t g[16], u[16];
+          tmem_ld16(t_row + (uint32_t)c0, g);
+          tmem_ld16(t_row + (uint32_t)(128 + c0), u);
+          tmem_ld_wait();
+          if (row_ok) {
+            const int nv = min(16, n_valid - c0);
+            float a[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              // round gate / up to bf16 first so that act(g)*u matches what a backward pass recomputes from them
+              float gf = __bfloat162float(__float2bfloat16(__uint_as_float(g[j])));
+              float uf = __bfloat162float(__float2bfloat16(__uint_as_float(u[j])));
+              a[j] = (p.epi == EPI_SWIGLU ? silu(gf) : gelu_tanh(gf)) * uf;
+            }
+            const long long off = row_off + c0;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              if (h * 8 + 8 <= nv) {
+                uint4 va, vg, vu;
+                va.x = pack_bf16x2(a[h * 8 + 0], a[h * 8 + 1]);
+                va.y = pack_bf16x2(a[h * 8 + 2], a[h * 8 + 3]);
+                va.z = pack_bf16x2(a[h * 8 + 4], a[h * 8 + 5]);
+                va.w = pack_bf16x2(a[h * 8 + 6], a[h * 8 + 7]);
+                *reinterpret_cast<uint4*>(cact + off + h * 8) = va;
+                if (cg != nullptr) {
+                  vg.x = pack_bf16x2(__uint_as_float(g[h * 8 + 0]), __uint_as_float(g[h * 8 + 1]));
+                  vg.y = pack_bf16x2(__uint_as_float(g[h * 8 + 2]), __uint_as_float(g[h * 8 + 3]));
+                  vg.z = pack_bf16x2(__uint_as_float(g[h * 8 + 4]), __uint_as_float(g[h * 8 + 5]));
+                  vg.w = pack_bf16x2(__uint_as_float(g[h * 8 + 6]), __uint_as_float(g[h * 8 + 7]));
+                  *reinterpret_cast<uint4*>(cg + off + h * 8) = vg;
+                  vu.x = pack_bf16x2(__uint_as_float(u[h * 8 + 0]), __uint_as_float(u[h * 8 + 1]));
+                  vu.y = pack_bf16x2(__uint_as_float(u[h * 8 + 2]), __uint_as_float(u[h * 8 + 3]));
+                  vu.z = pack_bf16x2(__uint_as_float(u[h * 8 + 4]), __uint_as_float(u[h * 8 + 5]));
+                  vu.w = pack_bf16x2(__uint_as_float(u[h * 8 + 6]), __uint_as_float(u[h * 8 + 7]));
+                  *reinterpret_cast<uint4*>(cu + off + h * 8) = vu;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  if (h * 8 + j < nv) {
+                    cact[off + h * 8 + j] = __float2bfloat16(a[h * 8 + j]);
+                    if (cg != nullptr) {
+                      cg[off + h * 8 + j] = __float2bfloat16(__uint_as_float(g[h * 8 + j]));
+                      cu[off + h * 8 + j] = __float2bfloat16(__uint_as_float(u[h * 8 + j]));
+                    }
+                  }
+                }
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&tempty_bar[buf]);
+    }
+  }
+
+  // teardown: everyone meets here (also after an aborted wait), then the allocating warp frees TMEM
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+template <bool A_MN, bool B_MN>
+static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const KernelParams& kp,
+                  int grid, cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    OB_CUDA_OK(cudaFuncSetAttribute(gemm_bf16_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    SMEM_BYTES));
+    attr_set = true;
+  }
+  gemm_bf16_kernel<A_MN, B_MN><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(tA, tB, tB2, kp);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace ob
+
+using namespace ob;
+
+extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
+  if (a == nullptr) OB_FAIL(-1, "null args");
+  if (a->M <= 0 || a->N <= 0 || a->Kc <= 0) OB_FAIL(-2, "empty problem M=%d N=%d K=%d", a->M, a->N, a->Kc);
+  const bool glu = (a->epi == EPI_SWIGLU || a->epi == EPI_GEGLU);
+  const int M_s = a->M_s > 0 ? a->M_s : a->M;
+  const int N_s = a->N_s > 0 ? a->N_s : a->N;
+  const int Kc_s = a->Kc_s > 0 ? a->Kc_s : a->Kc;
+  if (a->M % M_s || a->N % N_s || a->Kc % Kc_s) OB_FAIL(-3, "shard extents must divide M/N/K");
+  if (a->Kc % 8 || Kc_s % 8 || N_s % 8 || M_s % 8) OB_FAIL(-4, "M_s, N_s, K_s must be multiples of 8");
+  if (a->b_mn && N_s != a->N) OB_FAIL(-5, "an MN-major B operand cannot be N-sharded");
+  if (!a->b_mn && Kc_s != a->Kc) OB_FAIL(-6, "a K-major B operand cannot be K-sharded");
+  if (glu && (a->b_mn || a->a_mn || a->b2 == nullptr)) OB_FAIL(-7, "gated epilogue needs K-major A, B and b2");
+  if (a->c_shards == nullptr && M_s != a->M && a->epi != EPI_F32_RED && false) OB_FAIL(-8, "unreachable");
+
+  KernelParams kp;
+  kp.M = a->M; kp.N = a->N; kp.Kc = a->Kc;
+  kp.M_s = M_s; kp.N_s = N_s; kp.Kc_s = Kc_s;
+  kp.bn_out = glu ? 128 : BN;
+  kp.m_shards = a->M / M_s;
+  kp.n_shards = a->N / N_s;
+  kp.k_shards = a->Kc / Kc_s;
+  kp.m_tiles_per_shard = (M_s + BM - 1) / BM;
+  kp.n_tiles_per_shard = (N_s + kp.bn_out - 1) / kp.bn_out;
+  kp.k_iters_per_shard = (Kc_s + BK - 1) / BK;
+  kp.epi = a->epi;
+  kp.alpha = a->alpha;
+  kp.c = a->c; kp.c2 = a->c2; kp.c3 = a->c3;
+  kp.c_shards = a->c_shards;
+  kp.ldc = a->ldc;
+  kp.status = a->status;
+
+  CUtensorMap tA, tB, tB2;
+  memset(&tB2, 0, sizeof(tB2));
+  int rc;
+  if (a->a_mn) {  // stored [Kc, M], M contiguous
+    uint64_t dims[3] = {(uint64_t)a->M, (uint64_t)a->Kc, 1};
+    uint64_t str[2] = {(uint64_t)a->lda * 2, (uint64_t)a->lda * 2 * (uint64_t)a->Kc};
+    uint32_t box[3] = {64, (uint32_t)BK, 1};
+    rc = encode_tmap(&tA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a->a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  } else {  // stored [M, Kc], Kc contiguous
+    uint64_t dims[3] = {(uint64_t)a->Kc, (uint64_t)a->M, 1};
+    uint64_t str[2] = {(uint64_t)a->lda * 2, (uint64_t)a->lda * 2 * (uint64_t)a->M};
+    uint32_t box[3] = {(uint32_t)BK, (uint32_t)BM, 1};
+    rc = encode_tmap(&tA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a->a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  }
+  if (rc) return rc;
+  const long long bss = a->b_shard_stride > 0 ? a->b_shard_stride : 0;
+  if (a->b_mn) {  // stored [Kc, N] per k-shard, N contiguous
+    uint64_t dims[3] = {(uint64_t)a->N, (uint64_t)Kc_s, (uint64_t)kp.k_shards};
+    uint64_t sstride = kp.k_shards > 1 ? (uint64_t)bss * 2 : (uint64_t)a->ldb * 2 * (uint64_t)Kc_s;
+    uint64_t str[2] = {(uint64_t)a->ldb * 2, sstride};
+    uint32_t box[3] = {64, (uint32_t)BK, 1};
+    rc = encode_tmap(&tB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a->b, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+  } else {  // stored [N_s, Kc] per n-shard, Kc contiguous
+    uint64_t dims[3] = {(uint64_t)a->Kc, (uint64_t)N_s, (uint64_t)kp.n_shards};
+    uint64_t sstride = kp.n_shards > 1 ? (uint64_t)bss * 2 : (uint64_t)a->ldb * 2 * (uint64_t)N_s;
+    uint64_t str[2] = {(uint64_t)a->ldb * 2, sstride};
+    uint32_t box[3] = {(uint32_t)BK, (uint32_t)(glu ? 128 : BN), 1};
+    rc = encode_tmap(&tB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a->b, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    if (glu) {
+      rc = encode_tmap(&tB2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a->b2, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+      if (rc) return rc;
+    }
+  }
+  if ((kp.n_shards > 1 || kp.k_shards > 1) && bss <= 0) OB_FAIL(-9, "sharded B needs b_shard_stride");
+
+  const int total = kp.m_shards * kp.m_tiles_per_shard * kp.n_shards * kp.n_tiles_per_shard;
+  int cap = a->max_ctas > 0 ? a->max_ctas : sm_count();
+  int grid = total < cap ? total : cap;
+  if (a->a_mn) {
+    return a->b_mn ? launch<true, true>(tA, tB, tB2, kp, grid, stream) : launch<true, false>(tA, tB, tB2, kp, grid, stream);
+  }
+  return a->b_mn ? launch<false, true>(tA, tB, tB2, kp, grid, stream) : launch<false, false>(tA, tB, tB2, kp, grid, stream);
+}
+
+extern "C" const char* ob_last_error() { return ob::last_error_buf(); }

@@ -1,0 +1,53 @@
+// C interface of the tcgen05 bf16 GEMM (see gemm.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum ObGemmEpilogue {
+  EPI_BF16 = 0,     // C(bf16)  = alpha * A.B
+  EPI_F32 = 1,      // C(fp32)  = alpha * A.B
+  EPI_F32_ACC = 2,  // C(fp32) += alpha * A.B        (read-modify-write, local memory)
+  EPI_F32_RED = 3,  // C(fp32) += alpha * A.B        (red.global.add; destination may be a peer GPU's memory)
+  EPI_SWIGLU = 4,   // C(bf16)  = silu(A.B) * (A.B2); optionally c2 = A.B, c3 = A.B2
+  EPI_GEGLU = 5,    // C(bf16)  = gelu_tanh(A.B) * (A.B2)
+};
+
+// C[M, N] = A[M, Kc] . B[Kc, N]  with bf16 operands and fp32 accumulation.
+//   a_mn = 0: A stored [M, Kc] (Kc contiguous), a_mn = 1: A stored [Kc, M] (M contiguous); lda = row stride, elements
+//   b_mn = 0: B stored [N, Kc] (Kc contiguous), b_mn = 1: B stored [Kc, N] (N contiguous); ldb = row stride, elements
+// Sharding (0 = unsharded):
+//   N_s:  with b_mn = 0, output columns [s*N_s, (s+1)*N_s) use the B rows at b + s*b_shard_stride
+//   Kc_s: with b_mn = 1, contraction block s uses the B rows at b + s*b_shard_stride
+//   M_s:  output rows [s*M_s, (s+1)*M_s) are written to c_shards[s] (row index local to the shard) when c_shards is
+//         given, otherwise to c
+// All extents that are sharded, and lda/ldb/ldc, must be multiples of 8 elements; all base pointers 16-byte aligned.
+typedef struct ObGemmArgs {
+  const void* a;
+  long long lda;
+  const void* b;
+  long long ldb;
+  long long b_shard_stride;
+  const void* b2;
+  void* c;
+  long long ldc;
+  void* c2;
+  void* c3;
+  void* const* c_shards;  // DEVICE array of base pointers, one per M shard
+  int M, N, Kc;
+  int M_s, N_s, Kc_s;
+  int a_mn, b_mn;
+  int epi;
+  float alpha;
+  int* status;   // device int[4]: a kernel-side wait that ran out writes its code here (may be null)
+  int max_ctas;  // 0 = one CTA per SM
+} ObGemmArgs;
+
+int ob_gemm_bf16(const ObGemmArgs* args, cudaStream_t stream);
+const char* ob_last_error();
+
+#ifdef __cplusplus
+}
+#endif
