@@ -1,0 +1,446 @@
+// Bandwidth-bound kernels of the train step for sm_100a: RMSNorm forward/backward (with fused residual adds and a
+// strided "per-head" addressing mode for QK-norm), rotary embedding, gated-MLP activation forward/backward,
+// embedding gather / gradient scatter over (possibly peer-resident) vocabulary shards.
+//
+// All kernels move 16 bytes per thread per access, keep the row in registers between the reduction and the
+// normalisation (one read, one write of every tensor), and compute in fp32 with bf16 storage, matching the
+// reference's "upcast, compute, cast back" rule (`olmax/nn/functional.py:51-67`, `olmax/nn/rope.py:99-115`,
+// `olmax/nn/mlp.py:69-73`, `olmax/nn/embedding.py:30-32`).
+#include "elementwise.h"
+#include "host_common.h"
+#include "sm100.cuh"
+
+namespace ob {
+
+struct __align__(16) bf16x8 {
+  uint32_t v[4];
+};
+
+__device__ __forceinline__ void load8(const bf16* p, float (&f)[8]) {
+  const bf16x8 raw = *reinterpret_cast<const bf16x8*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = unpack_bf16x2(raw.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void store8(bf16* p, const float (&f)[8]) {
+  bf16x8 raw;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) raw.v[i] = pack_bf16x2(f[2 * i], f[2 * i + 1]);
+  *reinterpret_cast<bf16x8*>(p) = raw;
+}
+__device__ __forceinline__ void load8f(const float* p, float (&f)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+// Sum over the TPR threads that share a row (TPR = 16 or 32: shuffles; TPR = 256: shuffles + shared memory).
+template <int TPR>
+__device__ __forceinline__ float row_sum(float v, float* red) {
+  if (TPR <= 32) {
+#pragma unroll
+    for (int off = TPR / 2; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+  } else {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < TPR / 32; ++i) t += red[i];
+    return t;
+  }
+}
+
+constexpr int NORM_THREADS = 256;
+constexpr int MAX_VPT = 4;  // 8-element vectors per thread kept in registers
+
+// Rows are addressed as  base + (row / heads) * ld + (row % heads) * d   (heads = 1, ld = d: plain 2-D tensor).
+__device__ __forceinline__ long long row_offset(long long row, int heads, long long ld, int d) {
+  return heads == 1 ? row * ld : (row / heads) * ld + (row % heads) * (long long)d;
+}
+
+// t = x (+ res if add_before);  sum_out = t (optional);  y = t * rstd * w (+ res if !add_before and res given)
+template <int TPR>
+__global__ void __launch_bounds__(NORM_THREADS)
+    rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res, const bf16* __restrict__ w,
+                       bf16* __restrict__ y, bf16* __restrict__ sum_out, float* __restrict__ rstd_out, long long rows,
+                       int d, int heads, long long ld_x, long long ld_res, long long ld_y, int add_before, float eps) {
+  __shared__ float red[NORM_THREADS / 32];
+  constexpr int ROWS_PER_BLOCK = NORM_THREADS / TPR;
+  const int sub = threadIdx.x / TPR, tr = threadIdx.x % TPR;
+  const int nvec = d / 8;
+  for (long long row0 = (long long)blockIdx.x * ROWS_PER_BLOCK; row0 < rows; row0 += (long long)gridDim.x * ROWS_PER_BLOCK) {
+    const long long row = row0 + sub;
+    const bool live = row < rows;
+    const long long ox = live ? row_offset(row, heads, ld_x, d) : 0;
+    const long long ores = live ? row_offset(row, heads, ld_res, d) : 0;
+    const long long oy = live ? row_offset(row, heads, ld_y, d) : 0;
+    float t[MAX_VPT][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_VPT; ++i) {
+      const int vi = tr + i * TPR;
+      if (live && vi < nvec) {
+        load8(x + ox + vi * 8, t[i]);
+        if (res != nullptr && add_before) {
+          float r[8];
+          load8(res + ores + vi * 8, r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) t[i][j] = __bfloat162float(__float2bfloat16(t[i][j] + r[j]));
+          if (sum_out != nullptr) store8(sum_out + oy + vi * 8, t[i]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += t[i][j] * t[i][j];
+      }
+    }
+    ss = row_sum<TPR>(ss, red);
+    const float rstd = rsqrtf(ss / (float)d + eps);
+    if (live && tr == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+#pragma unroll
+    for (int i = 0; i < MAX_VPT; ++i) {
+      const int vi = tr + i * TPR;
+      if (live && vi < nvec) {
+        float wv[8], o[8];
+        load8(w + vi * 8, wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = t[i][j] * rstd * wv[j];
+        if (res != nullptr && !add_before) {
+          float r[8];
+          load8(res + ores + vi * 8, r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = __bfloat162float(__float2bfloat16(o[j])) + r[j];
+        }
+        store8(y + oy + vi * 8, o);
+      }
+    }
+  }
+}
+
+// dx = rstd * (w*dy - xhat * mean(w*dy*xhat)) (+ dsum);  dw += sum_rows dy * xhat  (fp32 atomics, accumulating)
+template <int TPR>
+__global__ void __launch_bounds__(NORM_THREADS)
+    rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                       const float* __restrict__ rstd_in, const bf16* __restrict__ dsum, bf16* __restrict__ dx,
+                       float* __restrict__ dw, long long rows, int d, int heads, long long ld_dy, long long ld_x,
+                       long long ld_dx, float dw_scale) {
+  __shared__ float red[NORM_THREADS / 32];
+  extern __shared__ float dw_part[];  // [d] per-block partial of dw
+  constexpr int ROWS_PER_BLOCK = NORM_THREADS / TPR;
+  const int sub = threadIdx.x / TPR, tr = threadIdx.x % TPR;
+  const int nvec = d / 8;
+  float dwacc[MAX_VPT][8];
+#pragma unroll
+  for (int i = 0; i < MAX_VPT; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+  for (long long row0 = (long long)blockIdx.x * ROWS_PER_BLOCK; row0 < rows; row0 += (long long)gridDim.x * ROWS_PER_BLOCK) {
+    const long long row = row0 + sub;
+    const bool live = row < rows;
+    const long long ody = live ? row_offset(row, heads, ld_dy, d) : 0;
+    const long long ox = live ? row_offset(row, heads, ld_x, d) : 0;
+    const long long odx = live ? row_offset(row, heads, ld_dx, d) : 0;
+    const float rstd = live ? rstd_in[row] : 0.f;
+    float g[MAX_VPT][8], xh[MAX_VPT][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_VPT; ++i) {
+      const int vi = tr + i * TPR;
+      if (live && vi < nvec) {
+        float wv[8];
+        load8(dy + ody + vi * 8, g[i]);
+        load8(x + ox + vi * 8, xh[i]);
+        load8(w + vi * 8, wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] *= rstd;
+          dwacc[i][j] += g[i][j] * xh[i][j];
+          g[i][j] *= wv[j];
+          dot += g[i][j] * xh[i][j];
+        }
+      }
+    }
+    dot = row_sum<TPR>(dot, red) / (float)d;
+#pragma unroll
+    for (int i = 0; i < MAX_VPT; ++i) {
+      const int vi = tr + i * TPR;
+      if (live && vi < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - xh[i][j] * dot);
+        if (dsum != nullptr) {
+          float e[8];
+          load8(dsum + odx + vi * 8, e);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += e[j];
+        }
+        store8(dx + odx + vi * 8, o);
+      }
+    }
+  }
+  if (dw == nullptr) return;
+  // combine the row groups of this block in shared memory, then one atomic per element per block
+  for (int i = threadIdx.x; i < d; i += NORM_THREADS) dw_part[i] = 0.f;
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < MAX_VPT; ++i) {
+    const int vi = tr + i * TPR;
+    if (vi < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (ROWS_PER_BLOCK > 1) atomicAdd(&dw_part[vi * 8 + j], dwacc[i][j]);
+        else dw_part[vi * 8 + j] = dwacc[i][j];
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < d; i += NORM_THREADS) atomicAdd(dw + i, dw_part[i] * dw_scale);
+}
+
+// Rotary embedding, rotate-half convention: out = x * cos + rotate_half(x) * sin, cos/sin tables [S, D/2] fp32.
+// sign = +1 forward, -1 backward (the transpose of a rotation).  One thread per 8 elements of the first half.
+__global__ void rope_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, const float* __restrict__ cos_t,
+                            const float* __restrict__ sin_t, int B, int S, int H, int D, long long sb, long long ss,
+                            long long sh, long long ysb, long long yss, long long ysh, float sign, int pos_offset) {
+  const int half = D / 2;
+  const int vec_per_head = half / 8;
+  const long long total = (long long)B * S * H * vec_per_head;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int vi = (int)(idx % vec_per_head);
+    const int h = (int)((idx / vec_per_head) % H);
+    const int s = (int)((idx / ((long long)vec_per_head * H)) % S);
+    const int b = (int)(idx / ((long long)vec_per_head * H * S));
+    const bf16* px = x + b * sb + s * ss + h * sh + vi * 8;
+    bf16* py = y + b * ysb + s * yss + h * ysh + vi * 8;
+    float lo[8], hi[8], c[8], sn[8], olo[8], ohi[8];
+    load8(px, lo);
+    load8(px + half, hi);
+    load8f(cos_t + (long long)(s + pos_offset) * half + vi * 8, c);
+    load8f(sin_t + (long long)(s + pos_offset) * half + vi * 8, sn);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sj = sn[j] * sign;
+      olo[j] = lo[j] * c[j] - hi[j] * sj;
+      ohi[j] = hi[j] * c[j] + lo[j] * sj;
+    }
+    store8(py, olo);
+    store8(py + half, ohi);
+  }
+}
+
+__device__ __forceinline__ float act_silu(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float act_silu_grad(float x) {
+  const float s = 1.f / (1.f + __expf(-x));
+  return s * (1.f + x * (1.f - s));
+}
+__device__ __forceinline__ float act_gelu_tanh(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  return 0.5f * x * (1.f + tanhf(k0 * (x + k1 * x * x * x)));
+}
+__device__ __forceinline__ float act_gelu_tanh_grad(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float t = tanhf(k0 * (x + k1 * x * x * x));
+  return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * k0 * (1.f + 3.f * k1 * x * x);
+}
+
+// a = act(g) * u
+__global__ void glu_fwd_kernel(const bf16* __restrict__ g, const bf16* __restrict__ u, bf16* __restrict__ a,
+                               long long n8, int gelu) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float gv[8], uv[8], o[8];
+    load8(g + i * 8, gv);
+    load8(u + i * 8, uv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = (gelu ? act_gelu_tanh(gv[j]) : act_silu(gv[j])) * uv[j];
+    store8(a + i * 8, o);
+  }
+}
+// dg = da * u * act'(g); du = da * act(g); optionally a = act(g) * u recomputed (for the down-projection wgrad)
+__global__ void glu_bwd_kernel(const bf16* __restrict__ g, const bf16* __restrict__ u, const bf16* __restrict__ da,
+                               bf16* __restrict__ dg, bf16* __restrict__ du, bf16* __restrict__ a_out, long long n8,
+                               int gelu) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float gv[8], uv[8], dv[8], og[8], ou[8], oa[8];
+    load8(g + i * 8, gv);
+    load8(u + i * 8, uv);
+    load8(da + i * 8, dv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float act = gelu ? act_gelu_tanh(gv[j]) : act_silu(gv[j]);
+      const float dact = gelu ? act_gelu_tanh_grad(gv[j]) : act_silu_grad(gv[j]);
+      og[j] = dv[j] * uv[j] * dact;
+      ou[j] = dv[j] * act;
+      oa[j] = act * uv[j];
+    }
+    store8(dg + i * 8, og);
+    store8(du + i * 8, ou);
+    if (a_out != nullptr) store8(a_out + i * 8, oa);
+  }
+}
+
+// out[t, :] = scale * W[ids[t], :], the table being R row-shards (pointers in `shards`, rows_per_shard rows each);
+// a shard pointer may address another GPU's memory (plain loads over NVLink).  One warp per token.
+__global__ void embed_gather_kernel(const long long* __restrict__ ids, const bf16* const* __restrict__ shards,
+                                    int rows_per_shard, int n_shards, bf16* __restrict__ out, long long tokens, int d,
+                                    float scale) {
+  const long long t = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (t >= tokens) return;
+  long long id = ids[t];
+  const long long vocab = (long long)rows_per_shard * n_shards;
+  if (id < 0 || id >= vocab) id = 0;  // out-of-range ids read row 0 instead of faulting
+  const bf16* src = shards[id / rows_per_shard] + (id % rows_per_shard) * (long long)d;
+  bf16* dst = out + t * d;
+  for (int v = lane; v < d / 8; v += 32) {
+    float f[8];
+    load8(src + v * 8, f);
+    if (scale != 1.f) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] *= scale;
+    }
+    store8(dst + v * 8, f);
+  }
+}
+// dW[ids[t], :] += scale * dout[t, :] into fp32 gradient shards (red.global.add, possibly to a peer GPU)
+__global__ void embed_scatter_kernel(const long long* __restrict__ ids, float* const* __restrict__ grad_shards,
+                                     int rows_per_shard, int n_shards, const bf16* __restrict__ dout, long long tokens,
+                                     int d, float scale) {
+  const long long t = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (t >= tokens) return;
+  const long long id = ids[t];
+  const long long vocab = (long long)rows_per_shard * n_shards;
+  if (id < 0 || id >= vocab) return;
+  float* dst = grad_shards[id / rows_per_shard] + (id % rows_per_shard) * (long long)d;
+  const bf16* src = dout + t * d;
+  for (int v = lane; v < d / 8; v += 32) {
+    float f[8];
+    load8(src + v * 8, f);
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + v * 8), "f"(f[0] * scale),
+                 "f"(f[1] * scale), "f"(f[2] * scale), "f"(f[3] * scale)
+                 : "memory");
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + v * 8 + 4), "f"(f[4] * scale),
+                 "f"(f[5] * scale), "f"(f[6] * scale), "f"(f[7] * scale)
+                 : "memory");
+  }
+}
+
+static inline int grid_for(long long work_items, int threads, int max_blocks_per_sm = 8) {
+  long long blocks = (work_items + threads - 1) / threads;
+  long long cap = (long long)sm_count() * max_blocks_per_sm;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+}  // namespace ob
+
+using namespace ob;
+
+extern "C" int ob_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* sum_out, float* rstd,
+                              long long rows, int d, int heads, long long ld_x, long long ld_res, long long ld_y,
+                              int add_before, float eps, cudaStream_t stream) {
+  if (d % 8 != 0) OB_FAIL(-1, "rmsnorm: d (%d) must be a multiple of 8", d);
+  if (rows <= 0) return 0;
+  const bf16* xp = (const bf16*)x; const bf16* rp = (const bf16*)res; const bf16* wp = (const bf16*)w;
+  bf16* yp = (bf16*)y; bf16* sp = (bf16*)sum_out;
+  if (d <= 512) {
+    constexpr int TPR = 16;
+    const int rpb = NORM_THREADS / TPR;
+    const int grid = grid_for((rows + rpb - 1) / rpb, 1);
+    rmsnorm_fwd_kernel<TPR><<<grid, NORM_THREADS, 0, stream>>>(xp, rp, wp, yp, sp, rstd, rows, d, heads, ld_x, ld_res,
+                                                                ld_y, add_before, eps);
+  } else {
+    if (d > NORM_THREADS * 8 * MAX_VPT) OB_FAIL(-2, "rmsnorm: d (%d) too large (max %d)", d, NORM_THREADS * 8 * MAX_VPT);
+    const int grid = grid_for(rows, 1);
+    rmsnorm_fwd_kernel<NORM_THREADS><<<grid, NORM_THREADS, 0, stream>>>(xp, rp, wp, yp, sp, rstd, rows, d, heads, ld_x,
+                                                                        ld_res, ld_y, add_before, eps);
+  }
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dsum,
+                              void* dx, float* dw, long long rows, int d, int heads, long long ld_dy, long long ld_x,
+                              long long ld_dx, float dw_scale, cudaStream_t stream) {
+  if (d % 8 != 0) OB_FAIL(-1, "rmsnorm: d (%d) must be a multiple of 8", d);
+  if (rows <= 0) return 0;
+  const size_t smem = (size_t)d * sizeof(float);
+  if (d <= 512) {
+    constexpr int TPR = 16;
+    const int rpb = NORM_THREADS / TPR;
+    int grid = grid_for((rows + rpb - 1) / rpb, 1, 4);
+    rmsnorm_bwd_kernel<TPR><<<grid, NORM_THREADS, smem, stream>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
+                                                                   (const bf16*)dsum, (bf16*)dx, dw, rows, d, heads,
+                                                                   ld_dy, ld_x, ld_dx, dw_scale);
+  } else {
+    if (d > NORM_THREADS * 8 * MAX_VPT) OB_FAIL(-2, "rmsnorm: d (%d) too large", d);
+    int grid = grid_for(rows, 1, 4);
+    rmsnorm_bwd_kernel<NORM_THREADS><<<grid, NORM_THREADS, smem, stream>>>(
+        (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dsum, (bf16*)dx, dw, rows, d, heads, ld_dy,
+        ld_x, ld_dx, dw_scale);
+  }
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_rope(const void* x, void* y, const float* cos_t, const float* sin_t, int B, int S, int H, int D,
+                       long long sb, long long ss, long long sh, long long ysb, long long yss, long long ysh,
+                       float sign, int pos_offset, cudaStream_t stream) {
+  if (D % 16 != 0) OB_FAIL(-1, "rope: head dim (%d) must be a multiple of 16", D);
+  const long long total = (long long)B * S * H * (D / 16);
+  if (total <= 0) return 0;
+  rope_kernel<<<grid_for(total, 256), 256, 0, stream>>>((const bf16*)x, (bf16*)y, cos_t, sin_t, B, S, H, D, sb, ss, sh,
+                                                        ysb, yss, ysh, sign, pos_offset);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_glu_fwd(const void* g, const void* u, void* a, long long n, int gelu, cudaStream_t stream) {
+  if (n % 8 != 0) OB_FAIL(-1, "glu: element count must be a multiple of 8");
+  if (n == 0) return 0;
+  glu_fwd_kernel<<<grid_for(n / 8, 256), 256, 0, stream>>>((const bf16*)g, (const bf16*)u, (bf16*)a, n / 8, gelu);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_glu_bwd(const void* g, const void* u, const void* da, void* dg, void* du, void* a_out, long long n,
+                          int gelu, cudaStream_t stream) {
+  if (n % 8 != 0) OB_FAIL(-1, "glu: element count must be a multiple of 8");
+  if (n == 0) return 0;
+  glu_bwd_kernel<<<grid_for(n / 8, 256), 256, 0, stream>>>((const bf16*)g, (const bf16*)u, (const bf16*)da, (bf16*)dg,
+                                                           (bf16*)du, (bf16*)a_out, n / 8, gelu);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_embed_gather(const long long* ids, const void* const* shards, int rows_per_shard, int n_shards,
+                               void* out, long long tokens, int d, float scale, cudaStream_t stream) {
+  if (d % 8 != 0) OB_FAIL(-1, "embedding: d must be a multiple of 8");
+  if (tokens == 0) return 0;
+  const int threads = 256;
+  const long long blocks = (tokens * 32 + threads - 1) / threads;
+  embed_gather_kernel<<<(unsigned)blocks, threads, 0, stream>>>(ids, (const bf16* const*)shards, rows_per_shard,
+                                                                n_shards, (bf16*)out, tokens, d, scale);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_embed_scatter(const long long* ids, float* const* grad_shards, int rows_per_shard, int n_shards,
+                                const void* dout, long long tokens, int d, float scale, cudaStream_t stream) {
+  if (d % 8 != 0) OB_FAIL(-1, "embedding: d must be a multiple of 8");
+  if (tokens == 0) return 0;
+  const int threads = 256;
+  const long long blocks = (tokens * 32 + threads - 1) / threads;
+  embed_scatter_kernel<<<(unsigned)blocks, threads, 0, stream>>>(ids, grad_shards, rows_per_shard, n_shards,
+                                                                 (const bf16*)dout, tokens, d, scale);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}

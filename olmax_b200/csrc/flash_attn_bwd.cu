@@ -1,0 +1,499 @@
+// Flash-attention backward for sm_100a (head_dim 128).
+//
+// One CTA owns one 128-key tile of one (batch, kv-head) and loops over every query head of the group and every
+// query tile that can see those keys.  Per (query tile, key tile) it runs five tcgen05 MMAs:
+//     S  = Q K^T          dP = dO V^T          dV += P^T dO          dK += dS^T Q          dQ_part = dS K
+// with S / dP / dK / dV in the four 128-column quarters of TMEM.  dK and dV stay in TMEM for the whole CTA lifetime
+// (no atomics, GQA heads accumulate in place); the dQ partial is produced in the S columns once S has been consumed
+// and is added to an fp32 scratch tensor with red.global.add, which a small kernel converts to bf16 at the end.
+// P and dS are formed by 128 threads that each own one query row, written as bf16 to one shared 32 KiB buffer in
+// the 128-byte-swizzled layout the MMAs read (P^T / dS^T as an MN-major A operand, dS as a K-major A operand).
+// Q and dO tiles stream through a 2-stage TMA ring; K and V stay resident in shared memory.
+//
+// The math is the standard recompute form: P = exp(S - lse), dS = P * (dP - delta) * scale, with
+// delta = rowsum(dO * O) from a pre-pass; a tanh soft-cap multiplies dS by (1 - tanh^2).
+//
+// Counterpart of the autodiff of `olmax/nn/attention.py:96-103` (cuDNN backward in the reference).
+#include "flash_attn.h"
+#include "host_common.h"
+#include "sm100.cuh"
+
+namespace ob {
+
+int encode_bshd_map(CUtensorMap* m, const void* ptr, int B, int S, int H, long long sb, long long ss, long long sh,
+                    int box_rows);
+
+namespace fa_bwd {
+
+constexpr int T = 128;    // tile (queries and keys)
+constexpr int HD = 128;
+constexpr int BLK = 128 * 64 * 2;   // 16 KiB swizzled block [128 rows][64 elems]
+constexpr int TILE = 2 * BLK;       // 32 KiB
+constexpr int STAGES = 2;
+constexpr int OFF_K = 0;
+constexpr int OFF_V = TILE;
+constexpr int OFF_Q = 2 * TILE;                    // STAGES tiles
+constexpr int OFF_DO = OFF_Q + STAGES * TILE;      // STAGES tiles
+constexpr int OFF_P = OFF_DO + STAGES * TILE;      // P, later dS
+constexpr int OFF_BAR = OFF_P + TILE;
+constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int C_S = 0, C_DP = 128, C_DK = 256, C_DV = 384;
+
+struct Params {
+  int B, S, H, Hkv;
+  int causal, window;
+  float scale, scale_log2, softcap, scale_over_cap, cap_log2;
+  const float* lse;
+  const float* delta;
+  float* dq_accum;   // [B, S, H, 128] fp32 contiguous
+  bf16* dk; long long dk_sb, dk_ss, dk_sh;
+  bf16* dv; long long dv_sb, dv_ss, dv_sh;
+  int* status;
+};
+
+__device__ __forceinline__ float fast_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+    flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                     const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* full = bars + 1;       // [STAGES]
+  uint64_t* empty = bars + 3;      // [STAGES]
+  uint64_t* s_full = bars + 5;
+  uint64_t* dp_full = bars + 6;
+  uint64_t* p_ready = bars + 7;    // 128 arrivals
+  uint64_t* pv_done = bars + 8;
+  uint64_t* ds_ready = bars + 9;   // 128 arrivals
+  uint64_t* dq_full = bars + 10;
+  uint64_t* dq_read = bars + 11;   // 128 arrivals
+  uint64_t* all_done = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_tiles = (p.S + T - 1) / T;
+  const int kv_tile = blockIdx.x;
+  const int hkv = blockIdx.y;
+  const int b = blockIdx.z;
+  const int G = p.H / p.Hkv;
+  const int kv0 = kv_tile * T;
+
+  int i_lo = 0, i_hi = n_tiles - 1;
+  if (p.causal) i_lo = kv0 / T;
+  if (p.window >= 0) i_hi = min(i_hi, (kv0 + T - 1 + p.window) / T);
+  const int n_q = max(0, i_hi - i_lo + 1);
+  const int n_iters = n_q * G;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(p_ready, 128);
+    mbar_init(pv_done, 1);
+    mbar_init(ds_ready, 128);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_read, 128);
+    mbar_init(all_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0 && n_iters > 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      tma_prefetch_desc(&tmDO);
+      mbar_arrive_expect_tx(kv_full, 2 * TILE);
+      tma_load_4d(smem + OFF_K, &tmK, kv_full, 0, hkv, kv0, b);
+      tma_load_4d(smem + OFF_K + BLK, &tmK, kv_full, 64, hkv, kv0, b);
+      tma_load_4d(smem + OFF_V, &tmV, kv_full, 0, hkv, kv0, b);
+      tma_load_4d(smem + OFF_V + BLK, &tmV, kv_full, 64, hkv, kv0, b);
+      bool ok = true;
+      for (int it = 0; it < n_iters && ok; ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+        const int h = hkv * G + it / n_q;
+        const int q0 = (i_lo + it % n_q) * T;
+        ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag, p.status, 700);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&full[s], 2 * TILE);
+        uint8_t* sq = smem + OFF_Q + s * TILE;
+        uint8_t* sdo = smem + OFF_DO + s * TILE;
+        tma_load_4d(sq, &tmQ, &full[s], 0, h, q0, b);
+        tma_load_4d(sq + BLK, &tmQ, &full[s], 64, h, q0, b);
+        tma_load_4d(sdo, &tmDO, &full[s], 0, h, q0, b);
+        tma_load_4d(sdo + BLK, &tmDO, &full[s], 64, h, q0, b);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && n_iters > 0) {
+      constexpr uint32_t id_kk = make_idesc_bf16(T, T, 0, 0);    // both K-major
+      constexpr uint32_t id_mm = make_idesc_bf16(T, HD, 1, 1);   // both MN-major
+      constexpr uint32_t id_km = make_idesc_bf16(T, HD, 0, 1);   // A K-major, B MN-major
+      const uint32_t aK = smem_u32(smem + OFF_K), aV = smem_u32(smem + OFF_V), aP = smem_u32(smem + OFF_P);
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, 800);
+      auto issue_s = [&](uint32_t aQ) {
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * BLK + (uint32_t)(kk & 3) * 32;
+          umma_ss(tmem_base + C_S, make_smem_desc(aQ + off, 0, 1024), make_smem_desc(aK + off, 0, 1024), id_kk,
+                  kk != 0 ? 1u : 0u);
+        }
+      };
+      auto issue_dp = [&](uint32_t aDO) {
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * BLK + (uint32_t)(kk & 3) * 32;
+          umma_ss(tmem_base + C_DP, make_smem_desc(aDO + off, 0, 1024), make_smem_desc(aV + off, 0, 1024), id_kk,
+                  kk != 0 ? 1u : 0u);
+        }
+      };
+      if (ok) ok = mbar_wait(&full[0], 0, abort_flag, p.status, 801);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_s(smem_u32(smem + OFF_Q));
+        umma_commit(s_full);
+        issue_dp(smem_u32(smem + OFF_DO));
+        umma_commit(dp_full);
+      }
+      for (int it = 0; it < n_iters && ok; ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph1 = (uint32_t)it & 1u;
+        const uint32_t aQ = smem_u32(smem + OFF_Q + s * TILE);
+        const uint32_t aDO = smem_u32(smem + OFF_DO + s * TILE);
+        // dV += P^T dO
+        ok = mbar_wait(p_ready, ph1, abort_flag, p.status, 802);
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < T / 16; ++kk) {
+          umma_ss(tmem_base + C_DV, make_smem_desc(aP + (uint32_t)kk * 2048, BLK, 1024),
+                  make_smem_desc(aDO + (uint32_t)kk * 2048, BLK, 1024), id_mm, (it | kk) != 0 ? 1u : 0u);
+        }
+        umma_commit(pv_done);
+        // dK += dS^T Q ; dQ_part = dS K
+        ok = mbar_wait(ds_ready, ph1, abort_flag, p.status, 803);
+        if (!ok) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < T / 16; ++kk) {
+          umma_ss(tmem_base + C_DK, make_smem_desc(aP + (uint32_t)kk * 2048, BLK, 1024),
+                  make_smem_desc(aQ + (uint32_t)kk * 2048, BLK, 1024), id_mm, (it | kk) != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < T / 16; ++kk) {
+          const uint32_t off = (uint32_t)(kk >> 2) * BLK + (uint32_t)(kk & 3) * 32;
+          umma_ss(tmem_base + C_S, make_smem_desc(aP + off, 0, 1024),
+                  make_smem_desc(aK + (uint32_t)kk * 2048, BLK, 1024), id_km, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(dq_full);
+        umma_commit(&empty[s]);
+        if (it + 1 < n_iters) {
+          const int s2 = (it + 1) % STAGES;
+          const uint32_t ph2 = (uint32_t)((it + 1) / STAGES) & 1u;
+          ok = mbar_wait(&full[s2], ph2, abort_flag, p.status, 804);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_dp(smem_u32(smem + OFF_DO + s2 * TILE));
+          umma_commit(dp_full);
+          ok = mbar_wait(dq_read, ph1, abort_flag, p.status, 805);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_s(smem_u32(smem + OFF_Q + s2 * TILE));
+          umma_commit(s_full);
+        }
+      }
+      if (ok) umma_commit(all_done);
+    }
+    __syncwarp();
+  } else {
+    const int qd = warp & 3;
+    const int row = qd * 32 + lane;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16);
+    uint8_t* sP = smem + OFF_P;
+    const float LOG2E = 1.4426950408889634f;
+    bool ok = true;
+    for (int it = 0; it < n_iters && ok; ++it) {
+      const uint32_t ph1 = (uint32_t)it & 1u;
+      const int h = hkv * G + it / n_q;
+      const int q0 = (i_lo + it % n_q) * T;
+      const int q_idx = q0 + row;
+      const bool q_ok = q_idx < p.S;
+      const long long stat_idx = ((long long)b * p.H + h) * p.S + q_idx;
+      const float lse2 = q_ok ? p.lse[stat_idx] * LOG2E : INFINITY;
+      const float dl = q_ok ? p.delta[stat_idx] : 0.f;
+      const bool need_mask = (kv0 + T > p.S) || (p.causal && kv0 + T - 1 > q0) ||
+                             (p.window >= 0 && kv0 < q0 + T - 1 - p.window);
+      const int kv_hi = p.causal ? min(q_idx, p.S - 1) : p.S - 1;
+      const int kv_lo = p.window >= 0 ? q_idx - p.window : 0;
+
+      ok = mbar_wait(s_full, ph1, abort_flag, p.status, 900);
+      if (!ok) break;
+      tc_fence_after_sync();
+      uint32_t pp[64];  // P of this row, bf16x2
+#pragma unroll
+      for (int c = 0; c < T; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(t_lane + C_S + (uint32_t)c, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float s0 = __uint_as_float(r[i]), s1 = __uint_as_float(r[i + 1]);
+          if (p.softcap > 0.f) {
+            s0 = p.cap_log2 * fast_tanh(s0 * p.scale_over_cap);
+            s1 = p.cap_log2 * fast_tanh(s1 * p.scale_over_cap);
+          } else {
+            s0 *= p.scale_log2;
+            s1 *= p.scale_log2;
+          }
+          float e0 = fast_exp2(s0 - lse2), e1 = fast_exp2(s1 - lse2);
+          if (need_mask) {
+            const int kv = kv0 + c + i;
+            if (kv > kv_hi || kv < kv_lo) e0 = 0.f;
+            if (kv + 1 > kv_hi || kv + 1 < kv_lo) e1 = 0.f;
+          }
+          pp[(c + i) >> 1] = pack_bf16x2(e0, e1);
+        }
+        // 32 keys = four 16-byte chunks of this row; chunk index within the 128-byte row is XOR-swizzled by row % 8
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int kvc = c + g * 8;  // first key of the chunk
+          const int blk = kvc >> 6, ch = (kvc & 63) >> 3;
+          uint4 v = make_uint4(pp[(kvc >> 1) + 0], pp[(kvc >> 1) + 1], pp[(kvc >> 1) + 2], pp[(kvc >> 1) + 3]);
+          *reinterpret_cast<uint4*>(sP + blk * BLK + row * 128 + ((ch ^ (row & 7)) << 4)) = v;
+        }
+      }
+      fence_proxy_async();
+      mbar_arrive(p_ready);
+
+      ok = mbar_wait(dp_full, ph1, abort_flag, p.status, 901);
+      if (!ok) break;
+      ok = mbar_wait(pv_done, ph1, abort_flag, p.status, 902);
+      if (!ok) break;
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < T; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(t_lane + C_DP + (uint32_t)c, r);
+        uint32_t sr[32];
+        if (p.softcap > 0.f) tmem_ld32(t_lane + C_S + (uint32_t)c, sr);
+        tmem_ld_wait();
+        uint32_t ds[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float2 pv = unpack_bf16x2(pp[(c + i) >> 1]);
+          float d0 = pv.x * (__uint_as_float(r[i]) - dl) * p.scale;
+          float d1 = pv.y * (__uint_as_float(r[i + 1]) - dl) * p.scale;
+          if (p.softcap > 0.f) {
+            const float t0 = fast_tanh(__uint_as_float(sr[i]) * p.scale_over_cap);
+            const float t1 = fast_tanh(__uint_as_float(sr[i + 1]) * p.scale_over_cap);
+            d0 *= (1.f - t0 * t0);
+            d1 *= (1.f - t1 * t1);
+          }
+          ds[i >> 1] = pack_bf16x2(d0, d1);
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int kvc = c + g * 8;
+          const int blk = kvc >> 6, ch = (kvc & 63) >> 3;
+          uint4 v = make_uint4(ds[g * 4 + 0], ds[g * 4 + 1], ds[g * 4 + 2], ds[g * 4 + 3]);
+          *reinterpret_cast<uint4*>(sP + blk * BLK + row * 128 + ((ch ^ (row & 7)) << 4)) = v;
+        }
+      }
+      fence_proxy_async();
+      mbar_arrive(ds_ready);
+
+      ok = mbar_wait(dq_full, ph1, abort_flag, p.status, 903);
+      if (!ok) break;
+      tc_fence_after_sync();
+      float* dq_row = p.dq_accum + (((long long)b * p.S + q_idx) * p.H + h) * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(t_lane + C_S + (uint32_t)c, r);
+        tmem_ld_wait();
+        if (q_ok) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + c + g * 4),
+                         "f"(__uint_as_float(r[g * 4 + 0])), "f"(__uint_as_float(r[g * 4 + 1])),
+                         "f"(__uint_as_float(r[g * 4 + 2])), "f"(__uint_as_float(r[g * 4 + 3]))
+                         : "memory");
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(dq_read);
+    }
+    // dK, dV out (thread <-> key row)
+    const int kv_idx = kv0 + row;
+    const bool kv_ok = kv_idx < p.S;
+    bf16* dk_row = p.dk + (long long)b * p.dk_sb + (long long)kv_idx * p.dk_ss + (long long)hkv * p.dk_sh;
+    bf16* dv_row = p.dv + (long long)b * p.dv_sb + (long long)kv_idx * p.dv_ss + (long long)hkv * p.dv_sh;
+    if (n_iters == 0) {
+      if (kv_ok) {
+        for (int c = 0; c < HD; c += 8) {
+          *reinterpret_cast<uint4*>(dk_row + c) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(dv_row + c) = make_uint4(0, 0, 0, 0);
+        }
+      }
+    } else {
+      if (ok) ok = mbar_wait(all_done, 0, abort_flag, p.status, 904);
+      if (ok) {
+        tc_fence_after_sync();
+#pragma unroll 1
+        for (int c = 0; c < HD; c += 32) {
+          uint32_t r[32], r2[32];
+          tmem_ld32(t_lane + C_DK + (uint32_t)c, r);
+          tmem_ld32(t_lane + C_DV + (uint32_t)c, r2);
+          tmem_ld_wait();
+          if (kv_ok) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 v, w;
+              v.x = pack_bf16x2(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
+              v.y = pack_bf16x2(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
+              v.z = pack_bf16x2(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
+              v.w = pack_bf16x2(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
+              w.x = pack_bf16x2(__uint_as_float(r2[g * 8 + 0]), __uint_as_float(r2[g * 8 + 1]));
+              w.y = pack_bf16x2(__uint_as_float(r2[g * 8 + 2]), __uint_as_float(r2[g * 8 + 3]));
+              w.z = pack_bf16x2(__uint_as_float(r2[g * 8 + 4]), __uint_as_float(r2[g * 8 + 5]));
+              w.w = pack_bf16x2(__uint_as_float(r2[g * 8 + 6]), __uint_as_float(r2[g * 8 + 7]));
+              *reinterpret_cast<uint4*>(dk_row + c + g * 8) = v;
+              *reinterpret_cast<uint4*>(dv_row + c + g * 8) = w;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// delta[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d]; one warp per (b, s, h) row
+__global__ void attn_delta_kernel(const bf16* __restrict__ o, long long o_sb, long long o_ss, long long o_sh,
+                                  const bf16* __restrict__ d_o, long long do_sb, long long do_ss, long long do_sh,
+                                  float* __restrict__ delta, int B, int S, int H) {
+  const long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)B * S * H;
+  if (gw >= total) return;
+  const int h = (int)(gw % H);
+  const int s = (int)((gw / H) % S);
+  const int b = (int)(gw / ((long long)H * S));
+  const uint2 a = *reinterpret_cast<const uint2*>(o + b * o_sb + s * o_ss + h * o_sh + lane * 4);
+  const uint2 g = *reinterpret_cast<const uint2*>(d_o + b * do_sb + s * do_ss + h * do_sh + lane * 4);
+  const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y);
+  float acc = a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) delta[((long long)b * H + h) * S + s] = acc;
+}
+
+// dq[b, s, h, :] (bf16, strided) = dq_accum[b, s, h, :] (fp32 contiguous); one warp per row
+__global__ void attn_dq_convert_kernel(const float* __restrict__ acc, bf16* __restrict__ dq, long long sb,
+                                       long long ss, long long sh, int B, int S, int H) {
+  const long long gw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)B * S * H;
+  if (gw >= total) return;
+  const int h = (int)(gw % H);
+  const int s = (int)((gw / H) % S);
+  const int b = (int)(gw / ((long long)H * S));
+  const float4 v = *reinterpret_cast<const float4*>(acc + gw * 128 + lane * 4);
+  uint2 o;
+  o.x = pack_bf16x2(v.x, v.y);
+  o.y = pack_bf16x2(v.z, v.w);
+  *reinterpret_cast<uint2*>(dq + b * sb + s * ss + h * sh + lane * 4) = o;
+}
+
+}  // namespace fa_bwd
+}  // namespace ob
+
+using namespace ob;
+
+extern "C" int ob_flash_attn_bwd(const ObAttnArgs* a, cudaStream_t stream) {
+  if (a == nullptr) OB_FAIL(-1, "null args");
+  if (a->D != 128) OB_FAIL(-2, "flash attention kernels are built for head_dim 128 (got %d)", a->D);
+  if (a->H % a->Hkv != 0) OB_FAIL(-3, "H (%d) must be a multiple of Hkv (%d)", a->H, a->Hkv);
+  if (a->delta == nullptr || a->dq_accum == nullptr) OB_FAIL(-4, "backward needs the delta and dq_accum scratch buffers");
+  CUtensorMap tq, tk, tv, tdo;
+  int rc;
+  if ((rc = encode_bshd_map(&tq, a->q, a->B, a->S, a->H, a->q_sb, a->q_ss, a->q_sh, 128))) return rc;
+  if ((rc = encode_bshd_map(&tk, a->k, a->B, a->S, a->Hkv, a->k_sb, a->k_ss, a->k_sh, 128))) return rc;
+  if ((rc = encode_bshd_map(&tv, a->v, a->B, a->S, a->Hkv, a->v_sb, a->v_ss, a->v_sh, 128))) return rc;
+  if ((rc = encode_bshd_map(&tdo, a->d_o, a->B, a->S, a->H, a->do_sb, a->do_ss, a->do_sh, 128))) return rc;
+
+  const long long rows = (long long)a->B * a->S * a->H;
+  const int wpb = 8;  // warps per block
+  const unsigned nblk = (unsigned)((rows + wpb - 1) / wpb);
+  fa_bwd::attn_delta_kernel<<<nblk, wpb * 32, 0, stream>>>(
+      reinterpret_cast<const bf16*>(a->o), a->o_sb, a->o_ss, a->o_sh, reinterpret_cast<const bf16*>(a->d_o), a->do_sb,
+      a->do_ss, a->do_sh, a->delta, a->B, a->S, a->H);
+  OB_CUDA_OK(cudaGetLastError());
+  OB_CUDA_OK(cudaMemsetAsync(a->dq_accum, 0, (size_t)rows * 128 * sizeof(float), stream));
+
+  fa_bwd::Params p;
+  p.B = a->B; p.S = a->S; p.H = a->H; p.Hkv = a->Hkv;
+  p.causal = a->causal; p.window = a->window;
+  const float LOG2E = 1.4426950408889634f;
+  p.scale = a->scale;
+  p.scale_log2 = a->scale * LOG2E;
+  p.softcap = a->softcap;
+  p.scale_over_cap = a->softcap > 0.f ? a->scale / a->softcap : 0.f;
+  p.cap_log2 = a->softcap * LOG2E;
+  p.lse = a->lse;
+  p.delta = a->delta;
+  p.dq_accum = a->dq_accum;
+  p.dk = reinterpret_cast<bf16*>(a->dk); p.dk_sb = a->dk_sb; p.dk_ss = a->dk_ss; p.dk_sh = a->dk_sh;
+  p.dv = reinterpret_cast<bf16*>(a->dv); p.dv_sb = a->dv_sb; p.dv_ss = a->dv_ss; p.dv_sh = a->dv_sh;
+  p.status = a->status;
+  static bool attr_set = false;
+  if (!attr_set) {
+    OB_CUDA_OK(cudaFuncSetAttribute(fa_bwd::flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    fa_bwd::SMEM_BYTES));
+    attr_set = true;
+  }
+  dim3 grid((a->S + 127) / 128, a->Hkv, a->B);
+  fa_bwd::flash_bwd_kernel<<<grid, fa_bwd::THREADS, fa_bwd::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+  OB_CUDA_OK(cudaGetLastError());
+  fa_bwd::attn_dq_convert_kernel<<<nblk, wpb * 32, 0, stream>>>(a->dq_accum, reinterpret_cast<bf16*>(a->dq), a->dq_sb,
+                                                               a->dq_ss, a->dq_sh, a->B, a->S, a->H);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}

@@ -59,6 +59,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.ob_last_error.restype = ctypes.c_char_p
     lib.ob_gemm_bf16.restype = ctypes.c_int
     lib.ob_gemm_bf16.argtypes = [ctypes.POINTER(ObGemmArgs), ctypes.c_void_p]
+    for name in ("ob_flash_attn_fwd", "ob_flash_attn_bwd"):
+        if hasattr(lib, name):
+            getattr(lib, name).restype = ctypes.c_int
+            getattr(lib, name).argtypes = [ctypes.POINTER(ObAttnArgs), ctypes.c_void_p]
     for name, sig in _SIGNATURES.items():
         fn = getattr(lib, name, None)
         if fn is None:
@@ -143,3 +147,21 @@ def check_status(device: Optional[torch.device] = None) -> None:
         raise KernelError(
             f"kernel reported '{names.get(vals[0], vals[0])}' at site {vals[1]}, block {vals[2]}, extra {vals[3]}"
         )
+
+
+class ObAttnArgs(ctypes.Structure):
+    _fields_ = (
+        [("q", ctypes.c_void_p), ("q_sb", ctypes.c_longlong), ("q_ss", ctypes.c_longlong), ("q_sh", ctypes.c_longlong)]
+        + [("k", ctypes.c_void_p), ("k_sb", ctypes.c_longlong), ("k_ss", ctypes.c_longlong), ("k_sh", ctypes.c_longlong)]
+        + [("v", ctypes.c_void_p), ("v_sb", ctypes.c_longlong), ("v_ss", ctypes.c_longlong), ("v_sh", ctypes.c_longlong)]
+        + [("o", ctypes.c_void_p), ("o_sb", ctypes.c_longlong), ("o_ss", ctypes.c_longlong), ("o_sh", ctypes.c_longlong)]
+        + [("lse", ctypes.c_void_p)]
+        + [("d_o", ctypes.c_void_p), ("do_sb", ctypes.c_longlong), ("do_ss", ctypes.c_longlong), ("do_sh", ctypes.c_longlong)]
+        + [("dq", ctypes.c_void_p), ("dq_sb", ctypes.c_longlong), ("dq_ss", ctypes.c_longlong), ("dq_sh", ctypes.c_longlong)]
+        + [("dk", ctypes.c_void_p), ("dk_sb", ctypes.c_longlong), ("dk_ss", ctypes.c_longlong), ("dk_sh", ctypes.c_longlong)]
+        + [("dv", ctypes.c_void_p), ("dv_sb", ctypes.c_longlong), ("dv_ss", ctypes.c_longlong), ("dv_sh", ctypes.c_longlong)]
+        + [("delta", ctypes.c_void_p), ("dq_accum", ctypes.c_void_p)]
+        + [("B", ctypes.c_int), ("S", ctypes.c_int), ("H", ctypes.c_int), ("Hkv", ctypes.c_int), ("D", ctypes.c_int)]
+        + [("causal", ctypes.c_int), ("window", ctypes.c_int), ("scale", ctypes.c_float), ("softcap", ctypes.c_float)]
+        + [("status", ctypes.c_void_p)]
+    )
