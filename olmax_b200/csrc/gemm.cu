@@ -45,6 +45,7 @@ struct KernelParams {
   void* c2;
   void* c3;
   void* const* c_shards;
+  long long c_shard_stride;
   long long ldc;
   int* status;
 };
@@ -217,6 +218,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       if (p.c_shards != nullptr) {
         cbase = reinterpret_cast<uint8_t*>(p.c_shards[m_shard]);
         row_off = (long long)(m_local0 + row_in_tile) * p.ldc + n_glob0;
+      } else if (p.c_shard_stride > 0) {
+        cbase = reinterpret_cast<uint8_t*>(p.c);
+        row_off = (long long)m_shard * p.c_shard_stride + (long long)(m_local0 + row_in_tile) * p.ldc + n_glob0;
       } else {
         cbase = reinterpret_cast<uint8_t*>(p.c);
         row_off = (long long)(m_shard * p.M_s + m_local0 + row_in_tile) * p.ldc + n_glob0;
@@ -229,8 +233,30 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           tmem_ld_wait();
           if (row_ok) {
             const int nv = min(32, n_valid - c0);
-            if (p.epi == EPI_BF16) {
+            if (p.epi == EPI_BF16 || p.epi == EPI_BF16_ACC) {
               bf16* dst = reinterpret_cast<bf16*>(cbase) + row_off + c0;
+              if (p.epi == EPI_BF16_ACC) {
+                // fold the existing C into the accumulator registers, then fall through to the plain store
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                  if (g * 8 + 8 <= nv) {
+                    const uint4 o = *reinterpret_cast<const uint4*>(dst + g * 8);
+                    const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                      const float2 f = unpack_bf16x2(ow[j]);
+                      r[g * 8 + 2 * j] = __float_as_uint(__uint_as_float(r[g * 8 + 2 * j]) + f.x / p.alpha);
+                      r[g * 8 + 2 * j + 1] = __float_as_uint(__uint_as_float(r[g * 8 + 2 * j + 1]) + f.y / p.alpha);
+                    }
+                  } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                      if (g * 8 + j < nv)
+                        r[g * 8 + j] = __float_as_uint(__uint_as_float(r[g * 8 + j]) +
+                                                       __bfloat162float(dst[g * 8 + j]) / p.alpha);
+                  }
+                }
+              }
 #pragma unroll
               for (int g = 0; g < 4; ++g) {
                 if (g * 8 + 8 <= nv) {
@@ -397,6 +423,7 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
   kp.alpha = a->alpha;
   kp.c = a->c; kp.c2 = a->c2; kp.c3 = a->c3;
   kp.c_shards = a->c_shards;
+  kp.c_shard_stride = a->c_shard_stride;
   kp.ldc = a->ldc;
   kp.status = a->status;
 

@@ -13,6 +13,7 @@ enum ObGemmEpilogue {
   EPI_F32_RED = 3,  // C(fp32) += alpha * A.B        (red.global.add; destination may be a peer GPU's memory)
   EPI_SWIGLU = 4,   // C(bf16)  = silu(A.B) * (A.B2); optionally c2 = A.B, c3 = A.B2
   EPI_GEGLU = 5,    // C(bf16)  = gelu_tanh(A.B) * (A.B2)
+  EPI_BF16_ACC = 6, // C(bf16) += alpha * A.B        (read-modify-write, local memory)
 };
 
 // C[M, N] = A[M, Kc] . B[Kc, N]  with bf16 operands and fp32 accumulation.
@@ -22,7 +23,7 @@ enum ObGemmEpilogue {
 //   N_s:  with b_mn = 0, output columns [s*N_s, (s+1)*N_s) use the B rows at b + s*b_shard_stride
 //   Kc_s: with b_mn = 1, contraction block s uses the B rows at b + s*b_shard_stride
 //   M_s:  output rows [s*M_s, (s+1)*M_s) are written to c_shards[s] (row index local to the shard) when c_shards is
-//         given, otherwise to c
+//         given, to c + s*c_shard_stride when c_shard_stride > 0, otherwise to c as one [M, N] matrix
 // All extents that are sharded, and lda/ldb/ldc, must be multiples of 8 elements; all base pointers 16-byte aligned.
 typedef struct ObGemmArgs {
   const void* a;
@@ -35,7 +36,8 @@ typedef struct ObGemmArgs {
   long long ldc;
   void* c2;
   void* c3;
-  void* const* c_shards;  // DEVICE array of base pointers, one per M shard
+  void* const* c_shards;  // DEVICE array of base pointers, one per M shard (or null)
+  long long c_shard_stride;  // with c_shards null and M_s set: rows of shard s start at c + s * c_shard_stride elements
   int M, N, Kc;
   int M_s, N_s, Kc_s;
   int a_mn, b_mn;

@@ -1,0 +1,45 @@
+"""Rotary position embedding (``olmax/nn/rope.py:1-145``), rotate-half convention, tables precomputed in fp32."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from ..ops import functional as F
+from ..ops import reference as ref
+
+__all__ = ["RotaryPositionalEmbedding", "RotaryPositionalEmbeddingConfig", "BufferCache"]
+
+
+class BufferCache(dict):
+    """Precomputed (cos, sin) tables keyed by ``(head_dim, seq_len, theta)`` (``olmax/nn/rope.py:91-97``)."""
+
+
+class RotaryPositionalEmbedding(torch.nn.Module):
+    def __init__(self, head_dim: int, theta: float = 10000.0):
+        super().__init__()
+        self.head_dim, self.theta = head_dim, float(theta)
+
+    def get_tables(self, seq_len: int, device, cache: Optional[BufferCache] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        key = (self.head_dim, seq_len, self.theta, str(device))
+        if cache is not None and key in cache:
+            return cache[key]
+        cos, sin = ref.rope_tables(seq_len, self.head_dim, self.theta, device=device)
+        if cache is not None:
+            cache[key] = (cos, sin)
+        return cos, sin
+
+    def forward(self, x: torch.Tensor, cache: Optional[BufferCache] = None) -> torch.Tensor:
+        """x: [B, S, H, D]."""
+        cos, sin = self.get_tables(x.shape[1], x.device, cache)
+        return F.rope(x, cos, sin)
+
+
+@dataclass
+class RotaryPositionalEmbeddingConfig:
+    theta: float = 10000.0
+
+    def build(self, head_dim: int) -> RotaryPositionalEmbedding:
+        return RotaryPositionalEmbedding(head_dim, self.theta)

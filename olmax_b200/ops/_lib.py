@@ -40,6 +40,7 @@ class ObGemmArgs(ctypes.Structure):
         ("c2", ctypes.c_void_p),
         ("c3", ctypes.c_void_p),
         ("c_shards", ctypes.c_void_p),
+        ("c_shard_stride", ctypes.c_longlong),
         ("M", ctypes.c_int),
         ("N", ctypes.c_int),
         ("Kc", ctypes.c_int),

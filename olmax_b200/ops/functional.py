@@ -1,0 +1,510 @@
+"""
+Differentiable ops of the transformer, as ``torch.autograd.Function``s over *activations*.  Weights are not autograd
+leaves: an op receives a :class:`~olmax_b200.parallel.param_store.ParamHandle`, reads the gathered weight through
+it and writes the weight gradient straight into the sharded fp32 accumulator (through the weight-gradient GEMM's
+epilogue on the GPU).  This is what lets the FSDP all-gather / reduce-scatter be fused with, or overlapped around,
+the GEMMs instead of being inferred by a compiler.
+
+On CUDA tensors (bf16) every op launches the hand-written sm_100a kernels from :mod:`olmax_b200.ops.kernels`; on CPU
+tensors it evaluates the PyTorch restatement in :mod:`olmax_b200.ops.reference` (backward through autograd of that
+restatement), which is the path the gloo multi-process tests use.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import kernels as K
+from . import reference as ref
+
+__all__ = [
+    "linear", "gated_mlp", "rms_norm", "rope", "attention", "embedding", "linear_cross_entropy", "glu",
+]
+
+
+def _on_gpu(x: torch.Tensor) -> bool:
+    if x.is_cuda:
+        if x.dtype != torch.bfloat16:
+            raise K.KernelError(f"the CUDA path computes in bf16; got {x.dtype}")
+        return True
+    return False
+
+
+def _b_operand(handle):
+    """(first piece, kwargs for an N-sharded K-major B) of a gathered weight."""
+    first, stride = handle.pieces()
+    R = handle.shard_count
+    if R == 1:
+        return first, {}
+    return first, {"N_s": handle.rows_local, "b_shard_stride": stride}
+
+
+def _gemm_fwd(x2: torch.Tensor, handle, out: Optional[torch.Tensor] = None, epi: int = K.EPI_BF16) -> torch.Tensor:
+    """y[M, N] = x2[M, K] @ W[N, K]^T with W read from the gathered unit buffer."""
+    M, Kd = x2.shape
+    N = handle.tp_shape[0]
+    first, kw = _b_operand(handle)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32 if epi == K.EPI_F32 else torch.bfloat16, device=x2.device)
+    K.gemm(x2, first, out, M, N, Kd, epi=epi, ldb=Kd, **kw)
+    return out
+
+
+def _gemm_dgrad(dy2: torch.Tensor, handle, out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
+    """dx[M, K] (+)= dy2[M, N] @ W[N, K], the contraction running over the weight's row shards."""
+    M, N = dy2.shape
+    Kd = handle.tp_shape[1]
+    first, stride = handle.pieces()
+    R = handle.shard_count
+    kw = {} if R == 1 else {"Kc_s": handle.rows_local, "b_shard_stride": stride}
+    if out is None:
+        out = torch.empty((M, Kd), dtype=torch.bfloat16, device=dy2.device)
+    K.gemm(dy2, first, out, M, Kd, N, b_mn=True, ldb=Kd, epi=K.EPI_BF16_ACC if accumulate else K.EPI_BF16, **kw)
+    return out
+
+
+def _gemm_wgrad(dy2: torch.Tensor, x2: torch.Tensor, handle) -> None:
+    """dW[N, K] += scale * dy2[M, N]^T @ x2[M, K], written into the handle's gradient destination."""
+    M, N = dy2.shape
+    Kd = x2.shape[1]
+    dst, gstride, scale = handle.grad_pieces()
+    R = handle.shard_count
+    kw = {} if R == 1 else {"M_s": handle.rows_local, "c_shard_stride": gstride}
+    peer = handle.store.symm.grad_pointer_table(handle) if getattr(handle.store, "symm", None) is not None else None
+    if peer is not None:
+        K.gemm(dy2, x2, dst, N, Kd, M, a_mn=True, b_mn=True, epi=K.EPI_F32_RED, alpha=handle.store.grad_scale,
+               ldc=Kd, M_s=handle.rows_local, c_shards=peer)
+    else:
+        K.gemm(dy2, x2, dst, N, Kd, M, a_mn=True, b_mn=True, epi=K.EPI_F32_ACC, alpha=scale, ldc=Kd, **kw)
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# Linear
+# ----------------------------------------------------------------------------------------------------------------------
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, handle, bias_handle):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        ctx.handle, ctx.bias_handle, ctx.shape = handle, bias_handle, shp
+        if _on_gpu(x):
+            x2 = x2.contiguous()
+            y = _gemm_fwd(x2, handle)
+            if bias_handle is not None:
+                y = y + bias_handle.full()
+        else:
+            y = x2 @ handle.full().t()
+            if bias_handle is not None:
+                y = y + bias_handle.full()
+        ctx.save_for_backward(x2)
+        return y.view(*shp[:-1], y.shape[-1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x2,) = ctx.saved_tensors
+        handle = ctx.handle
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        dx = None
+        if _on_gpu(dy2):
+            dy2 = dy2.contiguous()
+            if ctx.needs_input_grad[0]:
+                dx = _gemm_dgrad(dy2, handle)
+            _gemm_wgrad(dy2, x2, handle)
+        else:
+            if ctx.needs_input_grad[0]:
+                dx = dy2 @ handle.full()
+            handle.add_grad(dy2.t() @ x2)
+        if ctx.bias_handle is not None:
+            ctx.bias_handle.add_grad(dy2.float().sum(0))
+        return (dx.view(ctx.shape) if dx is not None else None), None, None
+
+
+def linear(x: torch.Tensor, handle, bias_handle=None) -> torch.Tensor:
+    """``x @ W^T (+ b)`` with W ``(out, in)`` (``olmax/nn/functional.py:14-27``)."""
+    return _LinearFn.apply(x, handle, bias_handle)
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# Gated MLP: down(act(gate(x)) * up(x)) in one autograd node so that act(g)*u is never kept for backward
+# ----------------------------------------------------------------------------------------------------------------------
+class _GatedMLPFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gate, up, down, act):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        ctx.handles, ctx.act, ctx.shape = (gate, up, down), act, shp
+        if _on_gpu(x):
+            x2 = x2.contiguous()
+            M, d = x2.shape
+            h = gate.tp_shape[0]
+            a = torch.empty((M, h), dtype=torch.bfloat16, device=x.device)
+            g = torch.empty_like(a)
+            u = torch.empty_like(a)
+            gfirst, kw = _b_operand(gate)
+            ufirst, _ = up.pieces()
+            K.gemm(x2, gfirst, a, M, h, d, epi=K.EPI_GEGLU if act != "silu" else K.EPI_SWIGLU, b2=ufirst, c2=g, c3=u,
+                   ldb=d, **kw)
+            y = _gemm_fwd(a, down)
+            del a
+        else:
+            g = x2 @ gate.full().t()
+            u = x2 @ up.full().t()
+            a = ref.glu(g, u, act)
+            y = a @ down.full().t()
+        ctx.save_for_backward(x2, g, u)
+        return y.view(*shp[:-1], y.shape[-1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, g, u = ctx.saved_tensors
+        gate, up, down = ctx.handles
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if _on_gpu(dy2):
+            dy2 = dy2.contiguous()
+            da = _gemm_dgrad(dy2, down)
+            dg = torch.empty_like(g)
+            du = torch.empty_like(u)
+            a = torch.empty_like(g)
+            K.glu_bwd(g, u, da, dg, du, a, gelu=ctx.act != "silu")
+            del da
+            _gemm_wgrad(dy2, a, down)
+            del a
+            _gemm_wgrad(dg, x2, gate)
+            _gemm_wgrad(du, x2, up)
+            dx = None
+            if ctx.needs_input_grad[0]:
+                dx = _gemm_dgrad(dg, gate)
+                _gemm_dgrad(du, up, out=dx, accumulate=True)
+        else:
+            with torch.enable_grad():
+                gg = g.detach().requires_grad_(True)
+                uu = u.detach().requires_grad_(True)
+                a = ref.glu(gg, uu, ctx.act)
+            da = dy2 @ down.full()
+            dg, du = torch.autograd.grad(a, (gg, uu), da)
+            down.add_grad(dy2.t() @ a.detach())
+            gate.add_grad(dg.t() @ x2)
+            up.add_grad(du.t() @ x2)
+            dx = dg @ gate.full() + du @ up.full() if ctx.needs_input_grad[0] else None
+        return (dx.view(ctx.shape) if dx is not None else None), None, None, None, None
+
+
+def gated_mlp(x: torch.Tensor, gate, up, down, act: str = "silu") -> torch.Tensor:
+    return _GatedMLPFn.apply(x, gate, up, down, act)
+
+
+def glu(g: torch.Tensor, u: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """Stand-alone ``act(g) * u`` (not differentiable through the kernels; use :func:`gated_mlp` in models)."""
+    if _on_gpu(g):
+        a = torch.empty_like(g)
+        K.glu_fwd(g.contiguous(), u.contiguous(), a, gelu=act != "silu")
+        return a
+    return ref.glu(g, u, act)
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# RMSNorm (+ residual variants, + per-head mode)
+# ----------------------------------------------------------------------------------------------------------------------
+class _RMSNormFn(torch.autograd.Function):
+    """
+    mode None : y = norm(x) * w
+    mode post : y = residual + norm(x) * w                      (OLMo2 / Gemma post-norms)
+    mode pre  : h = x + residual ; y = norm(h) * w ; returns (h, y)   (pre-norm residual stream)
+    """
+
+    @staticmethod
+    def forward(ctx, x, residual, handle, eps, mode, heads):
+        shp = x.shape
+        w = handle.full()
+        d = w.numel()
+        ctx.handle, ctx.mode, ctx.heads, ctx.eps, ctx.shape = handle, mode, heads, eps, shp
+        if _on_gpu(x):
+            xc = x.contiguous()
+            rows = xc.numel() // d
+            y = torch.empty_like(xc)
+            rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+            ld = d * heads if heads > 1 else d
+            if mode == "pre":
+                h = torch.empty_like(xc)
+                K.rmsnorm_fwd(xc, w, y, rows=rows, d=d, eps=eps, res=residual.contiguous(), sum_out=h, rstd=rstd,
+                              heads=heads, ld_x=ld, ld_res=ld, ld_y=ld, add_before=True)
+                ctx.save_for_backward(h, w, rstd)
+                return h, y
+            res = residual.contiguous() if mode == "post" else None
+            K.rmsnorm_fwd(xc, w, y, rows=rows, d=d, eps=eps, res=res, rstd=rstd, heads=heads, ld_x=ld, ld_res=ld, ld_y=ld)
+            ctx.save_for_backward(xc, w, rstd)
+            return y
+        # CPU
+        xin = x + residual if mode == "pre" else x
+        xv = xin.reshape(-1, d) if heads == 1 else xin.reshape(-1, heads, d)
+        y = ref.rms_norm(xv, w, eps).reshape(shp)
+        ctx.save_for_backward(xin, w)
+        if mode == "pre":
+            return xin, y
+        if mode == "post":
+            return residual + y
+        return y
+
+    @staticmethod
+    def backward(ctx, *grads):
+        handle, mode, heads, eps, shp = ctx.handle, ctx.mode, ctx.heads, ctx.eps, ctx.shape
+        if mode == "pre":
+            dh, dy = grads
+        else:
+            (dy,) = grads
+            dh = None
+        saved = ctx.saved_tensors
+        w = saved[1]
+        d = w.numel()
+        if _on_gpu(dy):
+            xin, _, rstd = saved
+            dyc = dy.contiguous()
+            rows = dyc.numel() // d
+            dx = torch.empty_like(dyc)
+            ld = d * heads if heads > 1 else d
+            R = handle.shard_count
+            if R == 1 and getattr(handle.store, "symm", None) is None:
+                dw, dw_scale = handle.local_grad, handle.store.grad_scale
+            else:
+                dw, dw_scale = torch.zeros(d, dtype=torch.float32, device=dy.device), 1.0
+            K.rmsnorm_bwd(dyc, xin, w, rstd, dx, rows=rows, d=d, dw=dw, dsum=dh.contiguous() if dh is not None else None,
+                          heads=heads, ld_dy=ld, ld_x=ld, ld_dx=ld, dw_scale=dw_scale)
+            if dw is not handle.local_grad:
+                handle.add_grad(dw)
+        else:
+            xin = saved[0]
+            with torch.enable_grad():
+                xx = xin.detach().requires_grad_(True)
+                ww = w.detach().requires_grad_(True)
+                xv = xx.reshape(-1, d) if heads == 1 else xx.reshape(-1, heads, d)
+                y = ref.rms_norm(xv, ww, eps).reshape(shp)
+            dx, dw = torch.autograd.grad(y, (xx, ww), dy)
+            handle.add_grad(dw)
+            if dh is not None:
+                dx = dx + dh
+        dx = dx.view(shp)
+        if mode == "pre":
+            return dx, dx, None, None, None, None
+        if mode == "post":
+            return dx, dy, None, None, None, None
+        return dx, None, None, None, None, None
+
+
+def rms_norm(x: torch.Tensor, handle, eps: float = 1e-5, residual: Optional[torch.Tensor] = None,
+             mode: Optional[str] = None, heads: int = 1):
+    """See :class:`_RMSNormFn`.  ``heads > 1`` normalises every ``d``-wide head of the last dimension separately."""
+    if mode is None:
+        residual = None
+    return _RMSNormFn.apply(x, residual, handle, eps, mode, heads)
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# RoPE
+# ----------------------------------------------------------------------------------------------------------------------
+class _RopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        ctx.save_for_backward(cos, sin)
+        if _on_gpu(x):
+            y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+            K.rope(x, y, cos, sin, sign=1.0)
+            return y
+        return ref.apply_rope(x, cos, sin, 1.0)
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin = ctx.saved_tensors
+        if _on_gpu(dy):
+            dyc = dy if dy.stride(-1) == 1 else dy.contiguous()
+            dx = torch.empty(dy.shape, dtype=dy.dtype, device=dy.device)
+            K.rope(dyc, dx, cos, sin, sign=-1.0)
+            return dx, None, None
+        return ref.apply_rope(dy, cos, sin, -1.0), None, None
+
+
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x: [B, S, H, D]; cos/sin fp32 [>= S, D/2]."""
+    return _RopeFn.apply(x, cos, sin)
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# Attention
+# ----------------------------------------------------------------------------------------------------------------------
+class _AttentionFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, window, softcap, scale):
+        ctx.cfg = (causal, window, softcap, scale)
+        if _on_gpu(q):
+            o, lse = K.flash_attn_fwd(q, k, v, causal=causal, window=window, softcap=softcap, scale=scale)
+            ctx.save_for_backward(q, k, v, o, lse)
+            return o
+        o, _ = ref.attention(q, k, v, causal, window, softcap, scale)
+        ctx.save_for_backward(q, k, v)
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        causal, window, softcap, scale = ctx.cfg
+        if _on_gpu(d_o):
+            q, k, v, o, lse = ctx.saved_tensors
+            d_o = d_o if d_o.stride(-1) == 1 else d_o.contiguous()
+            dq, dk, dv = K.flash_attn_bwd(q, k, v, o, lse, d_o, causal=causal, window=window, softcap=softcap, scale=scale)
+            return dq, dk, dv, None, None, None, None
+        q, k, v = ctx.saved_tensors
+        with torch.enable_grad():
+            qq, kk, vv = (t.detach().requires_grad_(True) for t in (q, k, v))
+            o, _ = ref.attention(qq, kk, vv, causal, window, softcap, scale)
+        dq, dk, dv = torch.autograd.grad(o, (qq, kk, vv), d_o)
+        return dq, dk, dv, None, None, None, None
+
+
+def attention(q, k, v, causal: bool = True, window: int = -1, softcap: float = 0.0, scale: Optional[float] = None):
+    """q [B,S,H,D], k/v [B,S,Hkv,D] -> [B,S,H,D]."""
+    return _AttentionFn.apply(q, k, v, causal, window if window is not None else -1, softcap or 0.0, scale)
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# Embedding
+# ----------------------------------------------------------------------------------------------------------------------
+_PTR_CACHE: dict = {}
+
+
+def _piece_pointer_table(first: torch.Tensor, stride: int, R: int) -> torch.Tensor:
+    key = (first.data_ptr(), stride, R, first.device.index)
+    t = _PTR_CACHE.get(key)
+    if t is None:
+        es = first.element_size()
+        t = K.pointer_table([first.data_ptr() + r * stride * es for r in range(R)], first.device)
+        if len(_PTR_CACHE) > 256:
+            _PTR_CACHE.clear()
+        _PTR_CACHE[key] = t
+    return t
+
+
+class _EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, handle, scale, anchor):
+        ctx.handle, ctx.scale = handle, scale
+        ctx.save_for_backward(ids)
+        d = handle.tp_shape[1]
+        if ids.is_cuda:
+            first, stride = handle.pieces()
+            R = handle.shard_count
+            table = _piece_pointer_table(first, stride, R)
+            out = torch.empty(ids.shape + (d,), dtype=torch.bfloat16, device=ids.device)
+            K.embed_gather(ids.contiguous(), table, handle.rows_local, R, out, d, scale)
+            return out
+        w = handle.full()
+        out = w[ids]
+        return out * scale if scale != 1.0 else out
+
+    @staticmethod
+    def backward(ctx, dout):
+        (ids,) = ctx.saved_tensors
+        handle = ctx.handle
+        d = handle.tp_shape[1]
+        if dout.is_cuda:
+            dst, gstride, gscale = handle.grad_pieces()
+            R = handle.shard_count
+            symm = getattr(handle.store, "symm", None)
+            if symm is not None:
+                table, gscale = symm.grad_pointer_table(handle), handle.store.grad_scale
+            else:
+                table = _piece_pointer_table(dst, gstride, R)
+            K.embed_scatter(ids.contiguous(), table, handle.rows_local, R, dout.contiguous(), d, ctx.scale * gscale)
+        else:
+            g = torch.zeros(handle.tp_shape, dtype=torch.float32, device=dout.device)
+            g.index_add_(0, ids.reshape(-1), dout.reshape(-1, d).float() * ctx.scale)
+            handle.add_grad(g)
+        return None, None, None, None
+
+
+def embedding(ids: torch.Tensor, handle, scale: float = 1.0, anchor: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Row gather ``W[ids] * scale`` (``olmax/nn/embedding.py:30-32``).  ``anchor`` is any tensor that requires grad;
+    passing it makes the output part of the autograd graph although ids and weights are not autograd leaves."""
+    return _EmbeddingFn.apply(ids, handle, float(scale), anchor)
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# LM head + cross entropy, never materialising [tokens, vocab] logits for the whole micro-batch
+# ----------------------------------------------------------------------------------------------------------------------
+class _LinearCrossEntropyFn(torch.autograd.Function):
+    """
+    loss = mean over counted tokens of CE(x @ W^T, labels) (+ z-loss).  The gradient w.r.t. x and W is computed during
+    the forward pass, one chunk of rows at a time (logits chunk -> soft-max statistics -> d logits -> two GEMMs), so
+    only ``chunk_rows x vocab`` logits exist at any time.  The weight gradient is accumulated immediately, therefore
+    the returned loss must be back-propagated with a unit gradient (what ``loss.backward()`` does).
+    """
+
+    @staticmethod
+    def forward(ctx, x, handle, labels, ignore_index, softcap, z_loss, chunk_rows):
+        shp = x.shape
+        d = shp[-1]
+        x2 = x.reshape(-1, d)
+        lab = labels.reshape(-1)
+        V = handle.tp_shape[0]
+        need_grad = bool(ctx.needs_input_grad[0])
+        if _on_gpu(x):
+            x2 = x2.contiguous()
+            lab = lab.contiguous()
+            M = x2.shape[0]
+            dev = x.device
+            stats = torch.zeros(2, dtype=torch.float32, device=dev)
+            inv = torch.empty(2, dtype=torch.float32, device=dev)
+            counter = torch.zeros(2, dtype=torch.int32, device=dev)
+            K.count_valid(lab, ignore_index, V, inv, counter)
+            dx = torch.empty_like(x2) if need_grad else None
+            rc = min(chunk_rows, M)
+            logits = torch.empty((rc, V), dtype=torch.float32, device=dev)
+            dlogits = torch.empty((rc, V), dtype=torch.bfloat16, device=dev) if need_grad else None
+            for r0 in range(0, M, rc):
+                r1 = min(M, r0 + rc)
+                n = r1 - r0
+                xc = x2[r0:r1]
+                _gemm_fwd(xc, handle, out=logits[:n], epi=K.EPI_F32)
+                K.ce_fwd_bwd(logits[:n], lab[r0:r1], dlogits[:n] if need_grad else None, stats, inv, V=V,
+                             ignore_index=ignore_index, softcap=softcap, z_loss=z_loss)
+                if need_grad:
+                    _gemm_dgrad(dlogits[:n], handle, out=dx[r0:r1])
+                    _gemm_wgrad(dlogits[:n], xc, handle)
+            loss = stats[0] * inv[0]
+            zl = stats[1] * inv[0] * z_loss
+            ctx.save_for_backward(dx if need_grad else torch.empty(0))
+            ctx.shape = shp
+            ctx.mark_non_differentiable(zl)
+            return loss + zl if z_loss else loss, zl
+        # CPU: autograd through the restatement
+        w = handle.full()
+        with torch.enable_grad():
+            xx = x2.detach().requires_grad_(need_grad)
+            ww = w.detach().requires_grad_(need_grad)
+            logits = (xx @ ww.t()).float()
+            loss, zl = ref.fused_cross_entropy(logits, lab, ignore_index=ignore_index, z_loss_multiplier=z_loss,
+                                               logit_softcap=softcap)
+            total = loss + zl if z_loss else loss
+        if need_grad:
+            dx, dw = torch.autograd.grad(total, (xx, ww))
+            handle.add_grad(dw)
+            ctx.save_for_backward(dx)
+        else:
+            ctx.save_for_backward(torch.empty(0))
+        ctx.shape = shp
+        zl = zl.detach()
+        ctx.mark_non_differentiable(zl)
+        return total.detach(), zl
+
+    @staticmethod
+    def backward(ctx, dloss, _dz):
+        (dx,) = ctx.saved_tensors
+        # dloss is 1 for loss.backward(); the weight gradient was already accumulated under that assumption
+        return dx.view(ctx.shape) * dloss.to(dx.dtype), None, None, None, None, None, None
+
+
+def linear_cross_entropy(x: torch.Tensor, handle, labels: torch.Tensor, ignore_index: int = -100,
+                         logit_softcap: float = 0.0, z_loss_multiplier: float = 0.0, chunk_rows: int = 2048):
+    """(loss, z_loss) of the LM head fused with the cross entropy; ``handle`` is the ``(vocab, d)`` head weight."""
+    return _LinearCrossEntropyFn.apply(x, handle, labels, ignore_index, float(logit_softcap or 0.0),
+                                       float(z_loss_multiplier or 0.0), int(chunk_rows))

@@ -1,0 +1,282 @@
+"""
+Thin Python wrappers around the C entry points of the sm_100a kernel library.  They take CUDA tensors, check the
+layout rules the kernels rely on (bf16, 16-byte alignment, strides that are multiples of 8 elements), build the
+argument structs and launch on the current stream.  No math happens here and there is no PyTorch fallback: on a
+machine with a GPU a missing library raises.
+
+A launch counter (:func:`launch_count`) records how many of our kernels were enqueued, which the benchmark reports.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import KernelError, ObAttnArgs, ObGemmArgs, check, lib, register_signature, status_buffer, stream_ptr
+
+__all__ = [
+    "EPI_BF16", "EPI_F32", "EPI_F32_ACC", "EPI_F32_RED", "EPI_SWIGLU", "EPI_GEGLU", "EPI_BF16_ACC",
+    "gemm", "flash_attn_fwd", "flash_attn_bwd", "rmsnorm_fwd", "rmsnorm_bwd", "rope", "glu_fwd", "glu_bwd",
+    "embed_gather", "embed_scatter", "ce_fwd_bwd", "count_valid", "adamw", "sumsq", "clip_coef", "cast_f32_bf16",
+    "launch_count", "reset_launch_count", "pointer_table",
+]
+
+EPI_BF16, EPI_F32, EPI_F32_ACC, EPI_F32_RED, EPI_SWIGLU, EPI_GEGLU, EPI_BF16_ACC = range(7)
+
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    return _LAUNCHES
+
+
+def reset_launch_count() -> None:
+    global _LAUNCHES
+    _LAUNCHES = 0
+
+
+def _count(n: int = 1) -> None:
+    global _LAUNCHES
+    _LAUNCHES += n
+
+
+_vp = ctypes.c_void_p
+_ll = ctypes.c_longlong
+_i = ctypes.c_int
+_f = ctypes.c_float
+
+register_signature("ob_rmsnorm_fwd", [_vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _ll, _ll, _ll, _i, _f, _vp])
+register_signature("ob_rmsnorm_bwd", [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _ll, _ll, _ll, _f, _vp])
+register_signature("ob_rope", [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp])
+register_signature("ob_glu_fwd", [_vp, _vp, _vp, _ll, _i, _vp])
+register_signature("ob_glu_bwd", [_vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _vp])
+register_signature("ob_embed_gather", [_vp, _vp, _i, _i, _vp, _ll, _i, _f, _vp])
+register_signature("ob_embed_scatter", [_vp, _vp, _i, _i, _vp, _ll, _i, _f, _vp])
+register_signature("ob_ce_fwd_bwd", [_vp, _ll, _vp, _vp, _ll, _vp, _vp, _vp, _ll, _i, _i, _f, _f, _f, _vp])
+register_signature("ob_count_valid", [_vp, _ll, _i, _i, _vp, _vp, _vp])
+register_signature("ob_adamw", [_vp, _vp, _vp, _vp, _vp, _ll, _f, _f, _f, _f, _f, _f, _f, _vp, _i, _vp])
+register_signature("ob_sumsq", [_vp, _ll, _vp, _vp])
+register_signature("ob_clip_coef", [_vp, _f, _f, _vp, _vp])
+register_signature("ob_cast_f32_bf16", [_vp, _vp, _ll, _vp])
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _req_bf16(*ts: Optional[torch.Tensor]) -> None:
+    for t in ts:
+        if t is not None and (t.dtype != torch.bfloat16 or not t.is_cuda):
+            raise KernelError(f"expected a CUDA bf16 tensor, got {t.dtype} on {t.device}")
+
+
+def pointer_table(ptrs: Sequence[int], device: torch.device) -> torch.Tensor:
+    """int64 CUDA tensor holding raw pointers (what the kernels take as ``T* const*``)."""
+    return torch.tensor(list(ptrs), dtype=torch.int64, device=device)
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    c: torch.Tensor,
+    M: int,
+    N: int,
+    K: int,
+    *,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    epi: int = EPI_BF16,
+    alpha: float = 1.0,
+    lda: Optional[int] = None,
+    ldb: Optional[int] = None,
+    ldc: Optional[int] = None,
+    b_shard_stride: int = 0,
+    N_s: int = 0,
+    Kc_s: int = 0,
+    M_s: int = 0,
+    b2: Optional[torch.Tensor] = None,
+    c2: Optional[torch.Tensor] = None,
+    c3: Optional[torch.Tensor] = None,
+    c_shards: Optional[torch.Tensor] = None,
+    c_shard_stride: int = 0,
+    max_ctas: int = 0,
+) -> None:
+    """``C[M, N] (+)= alpha * A[M, K] . B[K, N]``; see ``csrc/gemm.h`` for operand layouts and sharding."""
+    _req_bf16(a, b, b2)
+    args = ObGemmArgs()
+    args.a = a.data_ptr()
+    args.lda = lda if lda is not None else a.stride(0)
+    args.b = b.data_ptr()
+    args.ldb = ldb if ldb is not None else b.stride(0)
+    args.b_shard_stride = b_shard_stride
+    args.b2 = _ptr(b2)
+    args.c = c.data_ptr()
+    args.ldc = ldc if ldc is not None else c.stride(0)
+    args.c2 = _ptr(c2)
+    args.c3 = _ptr(c3)
+    args.c_shards = _ptr(c_shards)
+    args.c_shard_stride = c_shard_stride
+    args.M, args.N, args.Kc = M, N, K
+    args.M_s, args.N_s, args.Kc_s = M_s, N_s, Kc_s
+    args.a_mn, args.b_mn, args.epi, args.alpha = int(a_mn), int(b_mn), epi, alpha
+    args.status = status_buffer(a.device).data_ptr()
+    args.max_ctas = max_ctas
+    check(lib().ob_gemm_bf16(ctypes.byref(args), stream_ptr(a.device)), "gemm")
+    _count()
+
+
+def _set_bshd(args: ObAttnArgs, field: str, t: torch.Tensor, prefix: Optional[str] = None) -> None:
+    prefix = prefix or field
+    if t.stride(-1) != 1:
+        raise KernelError("attention tensors need a contiguous head dimension")
+    setattr(args, field, t.data_ptr())
+    setattr(args, prefix + "_sb", t.stride(0))
+    setattr(args, prefix + "_ss", t.stride(1))
+    setattr(args, prefix + "_sh", t.stride(2))
+
+
+def flash_attn_fwd(q, k, v, *, causal=True, window=-1, softcap=0.0, scale=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """q [B,S,H,128], k/v [B,S,Hkv,128] -> (o [B,S,H,128] bf16, lse [B,H,S] fp32)."""
+    _req_bf16(q, k, v)
+    B, S, H, D = q.shape
+    o = torch.empty((B, S, H, D), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+    a = ObAttnArgs()
+    _set_bshd(a, "q", q)
+    _set_bshd(a, "k", k)
+    _set_bshd(a, "v", v)
+    _set_bshd(a, "o", o)
+    a.lse = lse.data_ptr()
+    a.B, a.S, a.H, a.Hkv, a.D = B, S, H, k.shape[2], D
+    a.causal, a.window = int(causal), int(window)
+    a.scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    a.softcap = float(softcap)
+    a.status = status_buffer(q.device).data_ptr()
+    check(lib().ob_flash_attn_fwd(ctypes.byref(a), stream_ptr(q.device)), "flash_attn_fwd")
+    _count()
+    return o, lse
+
+
+def flash_attn_bwd(q, k, v, o, lse, d_o, *, causal=True, window=-1, softcap=0.0, scale=None,
+                   dq=None, dk=None, dv=None):
+    _req_bf16(q, k, v, o, d_o)
+    B, S, H, D = q.shape
+    dq = torch.empty_like(q) if dq is None else dq
+    dk = torch.empty_like(k) if dk is None else dk
+    dv = torch.empty_like(v) if dv is None else dv
+    delta = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+    acc = torch.empty((B, S, H, D), dtype=torch.float32, device=q.device)
+    a = ObAttnArgs()
+    _set_bshd(a, "q", q)
+    _set_bshd(a, "k", k)
+    _set_bshd(a, "v", v)
+    _set_bshd(a, "o", o)
+    _set_bshd(a, "d_o", d_o, "do")
+    _set_bshd(a, "dq", dq)
+    _set_bshd(a, "dk", dk)
+    _set_bshd(a, "dv", dv)
+    a.lse = lse.data_ptr()
+    a.delta = delta.data_ptr()
+    a.dq_accum = acc.data_ptr()
+    a.B, a.S, a.H, a.Hkv, a.D = B, S, H, k.shape[2], D
+    a.causal, a.window = int(causal), int(window)
+    a.scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    a.softcap = float(softcap)
+    a.status = status_buffer(q.device).data_ptr()
+    check(lib().ob_flash_attn_bwd(ctypes.byref(a), stream_ptr(q.device)), "flash_attn_bwd")
+    _count(3)
+    return dq, dk, dv
+
+
+def rmsnorm_fwd(x, w, y, *, rows, d, eps, res=None, sum_out=None, rstd=None, heads=1, ld_x=None, ld_res=None,
+                ld_y=None, add_before=False) -> None:
+    _req_bf16(x, w, y, res, sum_out)
+    check(lib().ob_rmsnorm_fwd(x.data_ptr(), _ptr(res), w.data_ptr(), y.data_ptr(), _ptr(sum_out), _ptr(rstd), rows, d,
+                               heads, ld_x if ld_x is not None else d, ld_res if ld_res is not None else d,
+                               ld_y if ld_y is not None else d, int(add_before), eps, stream_ptr(x.device)), "rmsnorm_fwd")
+    _count()
+
+
+def rmsnorm_bwd(dy, x, w, rstd, dx, *, rows, d, dw=None, dsum=None, heads=1, ld_dy=None, ld_x=None, ld_dx=None,
+                dw_scale=1.0) -> None:
+    _req_bf16(dy, x, w, dx, dsum)
+    check(lib().ob_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), _ptr(dsum), dx.data_ptr(),
+                               _ptr(dw), rows, d, heads, ld_dy if ld_dy is not None else d,
+                               ld_x if ld_x is not None else d, ld_dx if ld_dx is not None else d, dw_scale,
+                               stream_ptr(x.device)), "rmsnorm_bwd")
+    _count()
+
+
+def rope(x, y, cos, sin, *, sign=1.0, pos_offset=0) -> None:
+    """x, y: [B, S, H, D] bf16 (head dim contiguous); cos/sin fp32 [>= S, D/2]."""
+    _req_bf16(x, y)
+    B, S, H, D = x.shape
+    check(lib().ob_rope(x.data_ptr(), y.data_ptr(), cos.data_ptr(), sin.data_ptr(), B, S, H, D, x.stride(0), x.stride(1),
+                        x.stride(2), y.stride(0), y.stride(1), y.stride(2), sign, pos_offset, stream_ptr(x.device)), "rope")
+    _count()
+
+
+def glu_fwd(g, u, a, gelu: bool) -> None:
+    _req_bf16(g, u, a)
+    check(lib().ob_glu_fwd(g.data_ptr(), u.data_ptr(), a.data_ptr(), g.numel(), int(gelu), stream_ptr(g.device)), "glu_fwd")
+    _count()
+
+
+def glu_bwd(g, u, da, dg, du, a_out, gelu: bool) -> None:
+    _req_bf16(g, u, da, dg, du, a_out)
+    check(lib().ob_glu_bwd(g.data_ptr(), u.data_ptr(), da.data_ptr(), dg.data_ptr(), du.data_ptr(), _ptr(a_out), g.numel(),
+                           int(gelu), stream_ptr(g.device)), "glu_bwd")
+    _count()
+
+
+def embed_gather(ids, shard_ptrs, rows_per_shard, n_shards, out, d, scale=1.0) -> None:
+    check(lib().ob_embed_gather(ids.data_ptr(), shard_ptrs.data_ptr(), rows_per_shard, n_shards, out.data_ptr(),
+                                ids.numel(), d, scale, stream_ptr(out.device)), "embed_gather")
+    _count()
+
+
+def embed_scatter(ids, grad_ptrs, rows_per_shard, n_shards, dout, d, scale=1.0) -> None:
+    check(lib().ob_embed_scatter(ids.data_ptr(), grad_ptrs.data_ptr(), rows_per_shard, n_shards, dout.data_ptr(),
+                                 ids.numel(), d, scale, stream_ptr(dout.device)), "embed_scatter")
+    _count()
+
+
+def ce_fwd_bwd(logits, labels, dlogits, stats, inv_count, *, V, ignore_index=-100, softcap=0.0, z_loss=0.0,
+               grad_scale=1.0, lse=None) -> None:
+    rows = logits.shape[0]
+    check(lib().ob_ce_fwd_bwd(logits.data_ptr(), logits.stride(0), labels.data_ptr(), _ptr(dlogits),
+                              dlogits.stride(0) if dlogits is not None else 0, _ptr(lse), stats.data_ptr(),
+                              inv_count.data_ptr(), rows, V, ignore_index, softcap, z_loss, grad_scale,
+                              stream_ptr(logits.device)), "ce_fwd_bwd")
+    _count()
+
+
+def count_valid(labels, ignore_index, V, out, counter) -> None:
+    check(lib().ob_count_valid(labels.data_ptr(), labels.numel(), ignore_index, V, out.data_ptr(), counter.data_ptr(),
+                               stream_ptr(labels.device)), "count_valid")
+    _count()
+
+
+def adamw(p, m, v, g, shadow, *, lr, b1, b2, eps, wd, bias_corr1, bias_corr2, gscale=None, zero_grad=False) -> None:
+    check(lib().ob_adamw(p.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), _ptr(shadow), p.numel(), lr, b1, b2, eps,
+                         wd, bias_corr1, bias_corr2, _ptr(gscale), int(zero_grad), stream_ptr(p.device)), "adamw")
+    _count()
+
+
+def sumsq(x, out) -> None:
+    check(lib().ob_sumsq(x.data_ptr(), x.numel(), out.data_ptr(), stream_ptr(x.device)), "sumsq")
+    _count()
+
+
+def clip_coef(sumsq_t, max_norm, pre_scale, out) -> None:
+    check(lib().ob_clip_coef(sumsq_t.data_ptr(), max_norm, pre_scale, out.data_ptr(), stream_ptr(out.device)), "clip_coef")
+    _count()
+
+
+def cast_f32_bf16(src, dst) -> None:
+    check(lib().ob_cast_f32_bf16(src.data_ptr(), dst.data_ptr(), src.numel(), stream_ptr(src.device)), "cast")
+    _count()
