@@ -266,13 +266,14 @@ class _RMSNormFn(torch.autograd.Function):
             dx = torch.empty_like(dyc)
             ld = d * heads if heads > 1 else d
             R = handle.shard_count
-            if R == 1 and getattr(handle.store, "symm", None) is None:
+            direct = R == 1 and getattr(handle.store, "symm", None) is None
+            if direct:
                 dw, dw_scale = handle.local_grad, handle.store.grad_scale
             else:
                 dw, dw_scale = torch.zeros(d, dtype=torch.float32, device=dy.device), 1.0
             K.rmsnorm_bwd(dyc, xin, w, rstd, dx, rows=rows, d=d, dw=dw, dsum=dh.contiguous() if dh is not None else None,
                           heads=heads, ld_dy=ld, ld_x=ld, ld_dx=ld, dw_scale=dw_scale)
-            if dw is not handle.local_grad:
+            if not direct:
                 handle.add_grad(dw)
         else:
             xin = saved[0]

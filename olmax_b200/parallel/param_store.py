@@ -408,7 +408,14 @@ class ParamStore:
             u.release()
 
     def finish_backward(self) -> None:
-        """Wait for in-flight reduce-scatters and fold them into the fp32 accumulators."""
+        """Reduce any unit whose gradient is still un-reduced (embedding: its backward runs last), wait for the
+        in-flight reduce-scatters, fold them into the fp32 accumulators and drop gathered weights."""
+        for u in self.units:
+            if u._full_grad is not None:
+                u.reduce_grads()
+        if self.reshard_after_forward and self.mesh.shard.size > 1:
+            for u in self.units:
+                u.release()
         for unit, work, buf, out in self._pending_reduce:
             if work is not None:
                 work.wait()

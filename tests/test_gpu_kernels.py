@@ -1,0 +1,270 @@
+"""GPU numerics: every CUDA kernel against the PyTorch fp32 restatement of the same op."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from olmax_b200.ops import reference as ref
+from olmax_b200.testing import rel_err
+
+
+@pytest.fixture(scope="module")
+def K():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from olmax_b200.ops import kernels
+
+    return kernels
+
+
+def _check_status():
+    from olmax_b200.ops import _lib
+
+    torch.cuda.synchronize()
+    _lib.check_status()
+
+
+@pytest.mark.parametrize("M,N,Kd", [(128, 256, 64), (1000, 776, 520), (2048, 1376, 1024)])
+def test_gemm_layouts(K, M, N, Kd):
+    dev = "cuda"
+    torch.manual_seed(0)
+    a = torch.randn(M, Kd, device=dev, dtype=torch.bfloat16)
+    b = torch.randn(N, Kd, device=dev, dtype=torch.bfloat16)
+    want = a.float() @ b.float().t()
+    c = torch.zeros(M, N, device=dev, dtype=torch.bfloat16)
+    K.gemm(a, b, c, M, N, Kd)
+    assert rel_err(c, want) < 5e-3
+    bt = b.t().contiguous()
+    c.zero_()
+    K.gemm(a, bt, c, M, N, Kd, b_mn=True)
+    assert rel_err(c, want) < 5e-3
+    at = a.t().contiguous()
+    cf = torch.zeros(M, N, device=dev, dtype=torch.float32)
+    K.gemm(at, bt, cf, M, N, Kd, a_mn=True, b_mn=True, epi=K.EPI_F32)
+    assert rel_err(cf, want) < 1e-4
+    K.gemm(at, bt, cf, M, N, Kd, a_mn=True, b_mn=True, epi=K.EPI_F32_ACC, alpha=0.5)
+    assert rel_err(cf, 1.5 * want) < 1e-4
+    K.gemm(at, bt, cf, M, N, Kd, a_mn=True, b_mn=True, epi=K.EPI_F32_RED, alpha=0.5)
+    assert rel_err(cf, 2.0 * want) < 1e-4
+    c.copy_(want.to(torch.bfloat16))
+    K.gemm(a, b, c, M, N, Kd, epi=K.EPI_BF16_ACC)
+    assert rel_err(c, 2.0 * want) < 8e-3
+    _check_status()
+
+
+def test_gemm_sharded_operands(K):
+    dev = "cuda"
+    torch.manual_seed(1)
+    M, N, Kd, R = 512, 1024, 512, 4
+    a = torch.randn(M, Kd, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(N, Kd, device=dev, dtype=torch.bfloat16)
+    stage = torch.zeros(R, (N // R) * Kd + 64, device=dev, dtype=torch.bfloat16)
+    for r in range(R):
+        stage[r, : (N // R) * Kd] = w[r * (N // R) : (r + 1) * (N // R)].reshape(-1)
+    c = torch.zeros(M, N, device=dev, dtype=torch.bfloat16)
+    K.gemm(a, stage, c, M, N, Kd, ldb=Kd, N_s=N // R, b_shard_stride=stage.stride(0))
+    assert rel_err(c, a.float() @ w.float().t()) < 5e-3
+    dy = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
+    dx = torch.zeros(M, Kd, device=dev, dtype=torch.bfloat16)
+    K.gemm(dy, stage, dx, M, Kd, N, b_mn=True, ldb=Kd, Kc_s=N // R, b_shard_stride=stage.stride(0))
+    assert rel_err(dx, dy.float() @ w.float()) < 5e-3
+    # weight gradient written as R row blocks `stride` apart
+    g = torch.zeros(R, (N // R) * Kd + 64, device=dev, dtype=torch.float32)
+    K.gemm(dy, a, g, N, Kd, M, a_mn=True, b_mn=True, epi=K.EPI_F32_ACC, ldc=Kd, M_s=N // R, c_shard_stride=g.stride(0))
+    got = torch.cat([g[r, : (N // R) * Kd].view(N // R, Kd) for r in range(R)])
+    assert rel_err(got, dy.float().t() @ a.float()) < 1e-4
+    # the same through a device pointer table (the form used for peer GPUs' buffers)
+    g.zero_()
+    table = K.pointer_table([g[r].data_ptr() for r in range(R)], torch.device(dev))
+    K.gemm(dy, a, g, N, Kd, M, a_mn=True, b_mn=True, epi=K.EPI_F32_RED, ldc=Kd, M_s=N // R, c_shards=table)
+    got = torch.cat([g[r, : (N // R) * Kd].view(N // R, Kd) for r in range(R)])
+    assert rel_err(got, dy.float().t() @ a.float()) < 1e-4
+    _check_status()
+
+
+@pytest.mark.parametrize("gelu", [False, True])
+def test_gemm_gated_epilogue(K, gelu):
+    dev = "cuda"
+    torch.manual_seed(2)
+    M, N, Kd = 512, 384, 256
+    a = torch.randn(M, Kd, device=dev, dtype=torch.bfloat16) * 0.5
+    wg = torch.randn(N, Kd, device=dev, dtype=torch.bfloat16) * 0.1
+    wu = torch.randn(N, Kd, device=dev, dtype=torch.bfloat16) * 0.1
+    g = a.float() @ wg.float().t()
+    u = a.float() @ wu.float().t()
+    act = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    cg, cu = torch.empty_like(act), torch.empty_like(act)
+    K.gemm(a, wg, act, M, N, Kd, epi=K.EPI_GEGLU if gelu else K.EPI_SWIGLU, b2=wu, c2=cg, c3=cu)
+    want = ref.activation("gelu_tanh" if gelu else "silu", g) * u
+    assert rel_err(act, want) < 8e-3
+    assert rel_err(cg, g) < 5e-3 and rel_err(cu, u) < 5e-3
+    _check_status()
+
+
+@pytest.mark.parametrize("B,S,H,Hkv,causal,window,softcap", [
+    (1, 256, 2, 2, True, -1, 0.0),
+    (2, 512, 4, 2, True, -1, 0.0),
+    (1, 333, 2, 1, True, -1, 0.0),
+    (1, 640, 2, 2, True, 200, 0.0),
+    (1, 384, 2, 2, True, -1, 20.0),
+    (1, 256, 2, 2, False, -1, 0.0),
+])
+def test_flash_attention(K, B, S, H, Hkv, causal, window, softcap):
+    dev = "cuda"
+    torch.manual_seed(3)
+    q = torch.randn(B, S, H, 128, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(B, S, Hkv, 128, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(B, S, Hkv, 128, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    o, lse = K.flash_attn_fwd(q.detach(), k.detach(), v.detach(), causal=causal, window=window, softcap=softcap)
+    o_ref, lse_ref = ref.attention(q.float(), k.float(), v.float(), causal, window, softcap)
+    assert rel_err(o, o_ref) < 6e-3
+    assert rel_err(lse, lse_ref) < 1e-3
+    d_o = torch.randn_like(o)
+    gq, gk, gv = torch.autograd.grad(o_ref, (q, k, v), d_o.float())
+    dq, dk, dv = K.flash_attn_bwd(q.detach(), k.detach(), v.detach(), o, lse, d_o, causal=causal, window=window, softcap=softcap)
+    assert rel_err(dq, gq) < 1e-2 and rel_err(dk, gk) < 1e-2 and rel_err(dv, gv) < 1e-2
+    _check_status()
+
+
+@pytest.mark.parametrize("rows,d,heads", [(300, 512, 1), (64, 4096, 1), (100, 128, 6)])
+def test_rmsnorm(K, rows, d, heads):
+    dev = "cuda"
+    torch.manual_seed(4)
+    width = d * heads
+    x = torch.randn(rows, width, device=dev, dtype=torch.bfloat16)
+    res = torch.randn(rows, width, device=dev, dtype=torch.bfloat16)
+    w = (torch.randn(d, device=dev) * 0.1 + 1).to(torch.bfloat16)
+    n_rows = rows * heads
+    xv = x.view(rows, heads, d)
+
+    def want(t):
+        return ref.rms_norm(t.float().view(rows, heads, d), w.float(), 1e-5).view(rows, width)
+
+    y = torch.empty_like(x)
+    rstd = torch.empty(n_rows, device=dev, dtype=torch.float32)
+    K.rmsnorm_fwd(x, w, y, rows=n_rows, d=d, eps=1e-5, rstd=rstd, heads=heads, ld_x=width, ld_y=width)
+    assert rel_err(y, want(x)) < 5e-3
+    K.rmsnorm_fwd(x, w, y, rows=n_rows, d=d, eps=1e-5, res=res, heads=heads, ld_x=width, ld_res=width, ld_y=width)
+    assert rel_err(y, want(x) + res.float()) < 5e-3
+    h = torch.empty_like(x)
+    K.rmsnorm_fwd(x, w, y, rows=n_rows, d=d, eps=1e-5, res=res, sum_out=h, rstd=rstd, heads=heads, ld_x=width,
+                  ld_res=width, ld_y=width, add_before=True)
+    hs = (x.float() + res.float()).to(torch.bfloat16)
+    assert rel_err(h, hs) < 1e-3 and rel_err(y, want(hs)) < 5e-3
+    # backward of the plain form
+    xf = x.float().requires_grad_(True)
+    wf = w.float().requires_grad_(True)
+    yy = ref.rms_norm(xf.view(rows, heads, d), wf, 1e-5).view(rows, width)
+    dy = torch.randn_like(x)
+    gx, gw = torch.autograd.grad(yy, (xf, wf), dy.float())
+    K.rmsnorm_fwd(x, w, y, rows=n_rows, d=d, eps=1e-5, rstd=rstd, heads=heads, ld_x=width, ld_y=width)
+    dx = torch.empty_like(x)
+    dw = torch.zeros(d, device=dev, dtype=torch.float32)
+    K.rmsnorm_bwd(dy, x, w, rstd, dx, rows=n_rows, d=d, dw=dw, heads=heads, ld_dy=width, ld_x=width, ld_dx=width)
+    assert rel_err(dx, gx) < 6e-3 and rel_err(dw, gw) < 6e-3
+    _check_status()
+
+
+def test_rope_and_glu(K):
+    dev = "cuda"
+    torch.manual_seed(5)
+    x = torch.randn(2, 96, 3, 128, device=dev, dtype=torch.bfloat16)
+    cos, sin = ref.rope_tables(96, 128, 500000.0, device=dev)
+    y = torch.empty_like(x)
+    K.rope(x, y, cos, sin)
+    assert rel_err(y, ref.apply_rope(x.float(), cos, sin)) < 4e-3
+    back = torch.empty_like(x)
+    K.rope(y, back, cos, sin, sign=-1.0)
+    assert rel_err(back, x) < 8e-3
+    g = torch.randn(64, 512, device=dev, dtype=torch.bfloat16)
+    u = torch.randn_like(g)
+    da = torch.randn_like(g)
+    for gelu, name in ((False, "silu"), (True, "gelu_tanh")):
+        a = torch.empty_like(g)
+        K.glu_fwd(g, u, a, gelu)
+        gf, uf = g.float().requires_grad_(True), u.float().requires_grad_(True)
+        want = ref.activation(name, gf) * uf
+        assert rel_err(a, want) < 5e-3
+        wg, wu = torch.autograd.grad(want, (gf, uf), da.float())
+        dg, du, a2 = torch.empty_like(g), torch.empty_like(g), torch.empty_like(g)
+        K.glu_bwd(g, u, da, dg, du, a2, gelu)
+        assert rel_err(dg, wg) < 6e-3 and rel_err(du, wu) < 6e-3 and rel_err(a2, want) < 5e-3
+    _check_status()
+
+
+def test_embedding_kernels(K):
+    dev = torch.device("cuda")
+    torch.manual_seed(6)
+    V, d, R = 512, 256, 4
+    w = torch.randn(V, d, device=dev, dtype=torch.bfloat16)
+    ids = torch.randint(0, V, (300,), device=dev)
+    shards = [w[r * (V // R) : (r + 1) * (V // R)].contiguous() for r in range(R)]
+    table = K.pointer_table([s.data_ptr() for s in shards], dev)
+    out = torch.empty(300, d, device=dev, dtype=torch.bfloat16)
+    K.embed_gather(ids, table, V // R, R, out, d, 2.0)
+    assert rel_err(out, w[ids].float() * 2.0) < 1e-3
+    grads = [torch.zeros(V // R, d, device=dev, dtype=torch.float32) for _ in range(R)]
+    gtable = K.pointer_table([g.data_ptr() for g in grads], dev)
+    dout = torch.randn(300, d, device=dev, dtype=torch.bfloat16)
+    K.embed_scatter(ids, gtable, V // R, R, dout, d, 0.5)
+    want = torch.zeros(V, d, device=dev)
+    want.index_add_(0, ids, dout.float() * 0.5)
+    assert rel_err(torch.cat(grads), want) < 1e-5
+    _check_status()
+
+
+@pytest.mark.parametrize("softcap,z", [(0.0, 0.0), (30.0, 1e-4)])
+def test_cross_entropy_kernel(K, softcap, z):
+    dev = "cuda"
+    torch.manual_seed(7)
+    rows, V = 200, 4104
+    logits = (torch.randn(rows, V, device=dev) * 3).contiguous()
+    labels = torch.randint(0, V, (rows,), device=dev)
+    labels[::7] = -100
+    lf = logits.clone().requires_grad_(True)
+    loss, zl = ref.fused_cross_entropy(lf, labels, z_loss_multiplier=z, logit_softcap=softcap)
+    (gl,) = torch.autograd.grad(loss + zl, lf)
+    stats = torch.zeros(2, device=dev)
+    inv = torch.empty(2, device=dev)
+    counter = torch.zeros(2, device=dev, dtype=torch.int32)
+    K.count_valid(labels, -100, V, inv, counter)
+    dl = torch.empty(rows, V, device=dev, dtype=torch.bfloat16)
+    K.ce_fwd_bwd(logits, labels, dl, stats, inv, V=V, softcap=softcap, z_loss=z)
+    got = stats[0] * inv[0]
+    assert abs(got.item() - loss.item()) < 2e-3 * max(1.0, abs(loss.item()))
+    assert rel_err(dl, gl) < 8e-3
+    _check_status()
+
+
+def test_adamw_and_norm_kernels(K):
+    dev = "cuda"
+    torch.manual_seed(8)
+    n = 100003
+    p = torch.randn(n, device=dev)
+    g = torch.randn(n, device=dev) * 0.1
+    m = torch.zeros(n, device=dev)
+    v = torch.zeros(n, device=dev)
+    shadow = torch.empty(n, device=dev, dtype=torch.bfloat16)
+    ss = torch.zeros(1, device=dev, dtype=torch.float64)
+    K.sumsq(g, ss)
+    assert abs(ss.item() - g.double().pow(2).sum().item()) < 1e-6 * ss.item() + 1e-9
+    coef = torch.empty(2, device=dev)
+    K.clip_coef(ss, 1.0, 1.0, coef)
+    norm = g.norm().item()
+    assert abs(coef[1].item() - norm) < 1e-4 * norm and abs(coef[0].item() - 1.0 / max(1.0, norm)) < 1e-5
+    pr, mr, vr = p.clone(), m.clone(), v.clone()
+    lr, b1, b2, eps, wd = 1e-2, 0.9, 0.95, 1e-8, 0.1
+    for t in range(1, 4):
+        ge = g * coef[0]
+        mr = b1 * mr + (1 - b1) * ge
+        vr = b2 * vr + (1 - b2) * ge * ge
+        pr = pr - lr * ((mr / (1 - b1**t)) / ((vr / (1 - b2**t)).sqrt() + eps) + wd * pr)
+        gg = g.clone()
+        K.adamw(p, m, v, gg, shadow, lr=lr, b1=b1, b2=b2, eps=eps, wd=wd, bias_corr1=1 - b1**t, bias_corr2=1 - b2**t,
+                gscale=coef, zero_grad=True)
+        assert gg.abs().max().item() == 0.0
+    assert rel_err(p, pr) < 1e-5 and rel_err(shadow, pr) < 4e-3
+    _check_status()
