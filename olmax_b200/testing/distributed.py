@@ -8,6 +8,7 @@ parent with the rank's traceback; a rank that hangs is killed after ``timeout`` 
 from __future__ import annotations
 
 import datetime
+import io
 import os
 import socket
 import sys
@@ -44,7 +45,11 @@ def _worker(rank: int, world_size: int, port: int, backend: str, fn: Callable, a
 
         dist_utils.init_distributed()  # attaches the host-side control group
         result = fn(*args, **kwargs)
-        queue.put((rank, "ok", result))
+        # tensors are serialised to bytes here: handing live tensors through a queue shares file descriptors that die
+        # with this process
+        buf = io.BytesIO()
+        torch.save(result, buf)
+        queue.put((rank, "ok", buf.getvalue()))
         dist.barrier()
         dist.destroy_process_group()
     except BaseException:  # noqa: BLE001
@@ -84,7 +89,7 @@ def run_distributed_test(fn: Callable, world_size: int = 2, backend: str = "gloo
                 break
             continue
         if status == "ok":
-            results[rank] = payload
+            results[rank] = torch.load(io.BytesIO(payload), weights_only=False)
         else:
             errors.append((rank, payload))
             break

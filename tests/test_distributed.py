@@ -1,0 +1,139 @@
+"""
+Multi-process (gloo, CPU) tests of the sharding layer: the loss and the gradients of a model sharded over a mesh equal
+those of the same model on one process, for FSDP, HSDP, DDP and FSDP x TP (with sequence parallelism); initialisation
+is independent of the sharding; collectives and host-side synchronisation helpers behave.
+"""
+
+import pytest
+import torch
+
+from olmax_b200.testing import run_distributed_test
+
+
+def _model(mesh_resource, seed=0, layer="default", tie=False, kv=None):
+    from olmax_b200.models import (DefaultTransformerConfig, DefaultTransformerLayerConfig, GemmaTransformerLayerConfig,
+                                   ReorderedNormTransformerLayerConfig)
+    from olmax_b200.nn import MultiheadSelfAttentionConfig, RMSNormConfig
+
+    layer_cls = {"default": DefaultTransformerLayerConfig, "reordered_norm": ReorderedNormTransformerLayerConfig,
+                 "gemma": GemmaTransformerLayerConfig}[layer]
+    attn = MultiheadSelfAttentionConfig(n_heads=4, n_kv_heads=kv, head_dim=16,
+                                        qk_norm=RMSNormConfig() if layer != "default" else None, use_head_qk_norm=True)
+    cfg = DefaultTransformerConfig(vocab_size=64, d_model=64, hidden_size=96, num_layers=2, layer=layer_cls(attention=attn),
+                                   tie_embeddings=tie, scale_embeddings=tie, ce_chunk_rows=16)
+    return cfg.build(seed=seed, mesh_resource=mesh_resource)
+
+
+def _global_batch():
+    g = torch.Generator().manual_seed(123)
+    ids = torch.randint(0, 64, (8, 16), generator=g)
+    labels = torch.roll(ids, -1, 1)
+    labels[:, -1] = -100
+    return ids, labels
+
+
+def _single_process_reference(layer, tie, kv):
+    from olmax_b200.parallel import MeshResource
+
+    model = _model(MeshResource.FSDP(1), layer=layer, tie=tie, kv=kv)
+    ids, labels = _global_batch()
+    model.store.set_grad_scale(1.0)
+    loss, _ = model(ids, labels)
+    loss.backward()
+    model.store.finish_backward()
+    grads = {n: model.store.full_gradient(n) for n, _ in model.store.named_parameters()}
+    params = {n: model.store.full_parameter(n) for n, _ in model.store.named_parameters()}
+    return loss.item(), grads, params
+
+
+def _sharded_worker(mesh_kind, layer, tie, kv):
+    import torch.distributed as dist
+
+    from olmax_b200.parallel import MeshResource, dist_utils
+
+    world = dist_utils.get_world_size()
+    res = {"fsdp": lambda: MeshResource.FSDP(world), "hsdp": lambda: MeshResource.HSDP(2, world, 2),
+           "ddp": lambda: MeshResource.DDP(world), "tp": lambda: MeshResource.FSDP_with_TP(2, world)}[mesh_kind]()
+    model = _model(res, layer=layer, tie=tie, kv=kv)
+    mesh = model.mesh
+    ids, labels = _global_batch()
+    dp, r = mesh.data_parallel_size, mesh.data_parallel_rank
+    per = ids.shape[0] // dp
+    model.store.set_grad_scale(1.0 / world)
+    loss, _ = model(ids[r * per : (r + 1) * per], labels[r * per : (r + 1) * per])
+    loss.backward()
+    model.store.finish_backward()
+    model.store.reduce_replicated_grads()
+    t = loss.detach().clone()
+    dist.all_reduce(t, group=dist_utils.control_group())
+    grads = {n: model.store.full_gradient(n) for n, _ in model.store.named_parameters()}
+    params = {n: model.store.full_parameter(n) for n, _ in model.store.named_parameters()}
+    return (t / world).item(), grads, params, dict(model.store.stats)
+
+
+@pytest.mark.parametrize("mesh_kind,world,layer,tie,kv", [
+    ("fsdp", 2, "default", False, None),
+    ("fsdp", 4, "reordered_norm", False, 2),
+    ("hsdp", 4, "default", False, None),
+    ("ddp", 2, "gemma", True, 2),
+    ("tp", 2, "default", False, None),
+    ("tp", 4, "gemma", True, 2),
+])
+def test_sharded_model_matches_single_process(mesh_kind, world, layer, tie, kv):
+    want_loss, want_grads, want_params = _single_process_reference(layer, tie, kv)
+    results = run_distributed_test(_sharded_worker, world_size=world, func_args=(mesh_kind, layer, tie, kv))
+    for loss, grads, params, stats in results:
+        assert loss == pytest.approx(want_loss, rel=1e-5)
+        for n in want_grads:
+            assert torch.equal(params[n], want_params[n]), f"init of {n} depends on the sharding"
+            assert torch.allclose(grads[n], want_grads[n], rtol=1e-3, atol=1e-6), n
+    if mesh_kind == "fsdp":
+        assert results[0][3]["all_gather_bytes"] > 0 and results[0][3]["reduce_scatter_bytes"] > 0
+
+
+def _collectives_worker():
+    import torch.distributed as dist
+
+    from olmax_b200.parallel import MeshResource, collectives as coll, dist_utils
+
+    rank, world = dist_utils.get_rank(), dist_utils.get_world_size()
+    mesh = MeshResource.HSDP(2, world, 2).build()
+    assert mesh.shard.size == 2 and mesh.replicate.size == world // 2
+    assert mesh.shard.ranks == [rank - rank % 2, rank - rank % 2 + 1]
+    x = torch.full((2, 3), float(rank))
+    g = coll.all_gather(x, mesh.shard, dim=0)
+    assert g.shape == (4, 3) and g[0, 0] == mesh.shard.ranks[0] and g[2, 0] == mesh.shard.ranks[1]
+    full = torch.arange(8.0).view(4, 2) + rank
+    rs = coll.reduce_scatter(full.clone(), mesh.shard, dim=0)
+    want = sum(torch.arange(8.0).view(4, 2) + r for r in mesh.shard.ranks)[mesh.shard.rank * 2 : mesh.shard.rank * 2 + 2]
+    assert torch.equal(rs, want)
+    h = torch.full((4,), 1.0 + rank, dtype=torch.bfloat16)
+    coll.all_reduce(h, mesh.world, mean=True)
+    assert torch.allclose(h.float(), torch.full((4,), sum(1.0 + r for r in range(world)) / world), rtol=1e-2)
+    # host-side helpers
+    dist_utils.barrier("t")
+    assert dist_utils.synchronize_value({"a": rank}, src=0) == {"a": 0}
+    assert dist_utils.allgather_value(rank * 10) == [r * 10 for r in range(world)]
+    assert dist_utils.get_process_filesystem_rank() == rank  # OLMAX_SHARED_FS_DIRS is set by the harness
+    return True
+
+
+def test_collectives_and_host_sync():
+    assert all(run_distributed_test(_collectives_worker, world_size=4))
+
+
+def test_reduce_divide_factor_and_mesh_math():
+    from olmax_b200.parallel import MeshResource, get_reduce_divide_factor
+
+    assert [get_reduce_divide_factor(n) for n in (1, 2, 4, 8, 16, 32, 64)] == [1, 2, 2, 4, 4, 8, 8]
+    m = MeshResource.FSDP_with_TP(2, 8)
+    assert m.data_parallel_size == 4 and m.fsdp_size == 4 and m.tp_size == 2
+    assert m.coordinates(5) == {"fsdp": 2, "tp": 1} and m.rank_of({"fsdp": 2, "tp": 1}) == 5
+    assert m.group_ranks("tp", 5) == [4, 5] and m.group_ranks("fsdp", 5) == [1, 3, 5, 7]
+    h = MeshResource.HSDP(4, 8, 8)
+    assert h.replicate_axes == ("fsdp_replicate",) and h.group_ranks("fsdp_shard", 6) == [4, 5, 6, 7]
+    assert MeshResource.DDP(4).replicate_axes == ("data",) and MeshResource.DDP(4).fsdp_size == 1
+    cp = MeshResource.FSDP_with_CP(8, 2)
+    assert cp.data_parallel_size == 4 and cp.fsdp_size == 8 and cp.cp_size == 2
+    with pytest.raises(Exception):
+        MeshResource(axes=((2, "a"),), batch_sharding_axis="b")
