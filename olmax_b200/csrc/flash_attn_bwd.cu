@@ -15,6 +15,7 @@
 //
 // Counterpart of the autodiff of `olmax/nn/attention.py:96-103` (cuDNN backward in the reference).
 #include "flash_attn.h"
+#include "flash_attn_noalloc.h"
 #include "host_common.h"
 #include "sm100.cuh"
 
@@ -493,6 +494,103 @@ extern "C" int ob_flash_attn_bwd(const ObAttnArgs* a, cudaStream_t stream) {
   fa_bwd::flash_bwd_kernel<<<grid, fa_bwd::THREADS, fa_bwd::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
   OB_CUDA_OK(cudaGetLastError());
   fa_bwd::attn_dq_convert_kernel<<<nblk, wpb * 32, 0, stream>>>(a->dq_accum, reinterpret_cast<bf16*>(a->dq), a->dq_sb,
+                                                               a->dq_ss, a->dq_sh, a->B, a->S, a->H);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Allocation-free variant (declared in flash_attn_noalloc.h)
+// ---------------------------------------------------------------------------------------------------------------------
+// The backward pass needs two work buffers besides its inputs and outputs: delta[B, H, S] and the fp32 dQ accumulator
+// [B, S, H, 128].  ob_flash_attn_bwd() takes them from the caller.  The variant below keeps them in a fixed array that
+// is part of the library image, for callers that have no way to obtain device memory of their own.
+namespace ob {
+namespace fa_bwd_static {
+
+constexpr long long MAX_ROWS = OB_FLASH_BWD_STATIC_MAX_ROWS;             // B * S * H
+constexpr long long SCRATCH_FLOATS = MAX_ROWS * 128 + MAX_ROWS;          // dQ accumulator, then delta
+
+static __device__ __align__(256) float g_scratch[SCRATCH_FLOATS];
+
+// In host code `g_scratch` is only a handle for the runtime, not an address a kernel may use; the device address is
+// looked up once per device with cudaGetSymbolAddress and cached here.
+constexpr int MAX_DEVICES = 64;
+static float* g_scratch_dev[MAX_DEVICES] = {nullptr};
+
+static int scratch_for_current_device(float** out) {
+  int dev = -1;
+  OB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= MAX_DEVICES) OB_FAIL(-21, "device ordinal %d outside the supported range [0, %d)", dev, MAX_DEVICES);
+  if (g_scratch_dev[dev] == nullptr) {
+    float* p = nullptr;
+    OB_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_scratch));
+    if (p == nullptr) OB_FAIL(-22, "cudaGetSymbolAddress returned a null scratch address");
+    g_scratch_dev[dev] = p;
+  }
+  *out = g_scratch_dev[dev];
+  return 0;
+}
+
+}  // namespace fa_bwd_static
+}  // namespace ob
+
+extern "C" int ob_flash_attn_bwd_static(const ObAttnArgs* a, cudaStream_t stream) {
+  using namespace ob::fa_bwd_static;
+  if (a == nullptr) OB_FAIL(-1, "null args");
+  if (a->D != 128) OB_FAIL(-2, "flash attention kernels are built for head_dim 128 (got %d)", a->D);
+  if (a->B <= 0 || a->S <= 0 || a->H <= 0 || a->Hkv <= 0) OB_FAIL(-4, "empty problem");
+  if (a->H % a->Hkv != 0) OB_FAIL(-3, "H (%d) must be a multiple of Hkv (%d)", a->H, a->Hkv);
+  const long long rows = (long long)a->B * a->S * a->H;
+  if (rows > MAX_ROWS)
+    OB_FAIL(-20, "B*S*H = %lld exceeds the %lld rows the built-in work area holds; use ob_flash_attn_bwd with "
+                 "caller-provided buffers for larger problems", rows, (long long)MAX_ROWS);
+  float* scratch = nullptr;
+  int rc = scratch_for_current_device(&scratch);
+  if (rc) return rc;
+  float* dq_accum = scratch;                     // [rows, 128]
+  float* delta = scratch + MAX_ROWS * 128;       // [rows]
+
+  CUtensorMap tq, tk, tv, tdo;
+  if ((rc = encode_bshd_map(&tq, a->q, a->B, a->S, a->H, a->q_sb, a->q_ss, a->q_sh, 128))) return rc;
+  if ((rc = encode_bshd_map(&tk, a->k, a->B, a->S, a->Hkv, a->k_sb, a->k_ss, a->k_sh, 128))) return rc;
+  if ((rc = encode_bshd_map(&tv, a->v, a->B, a->S, a->Hkv, a->v_sb, a->v_ss, a->v_sh, 128))) return rc;
+  if ((rc = encode_bshd_map(&tdo, a->d_o, a->B, a->S, a->H, a->do_sb, a->do_ss, a->do_sh, 128))) return rc;
+
+  const int wpb = 8;
+  const unsigned nblk = (unsigned)((rows + wpb - 1) / wpb);
+  fa_bwd::attn_delta_kernel<<<nblk, wpb * 32, 0, stream>>>(
+      reinterpret_cast<const bf16*>(a->o), a->o_sb, a->o_ss, a->o_sh, reinterpret_cast<const bf16*>(a->d_o), a->do_sb,
+      a->do_ss, a->do_sh, delta, a->B, a->S, a->H);
+  OB_CUDA_OK(cudaGetLastError());
+  // the accumulator still holds the previous call's sums: clear the part this call uses
+  OB_CUDA_OK(cudaMemsetAsync(dq_accum, 0, (size_t)rows * 128 * sizeof(float), stream));
+
+  fa_bwd::Params p;
+  p.B = a->B; p.S = a->S; p.H = a->H; p.Hkv = a->Hkv;
+  p.causal = a->causal; p.window = a->window;
+  const float LOG2E = 1.4426950408889634f;
+  p.scale = a->scale;
+  p.scale_log2 = a->scale * LOG2E;
+  p.softcap = a->softcap;
+  p.scale_over_cap = a->softcap > 0.f ? a->scale / a->softcap : 0.f;
+  p.cap_log2 = a->softcap * LOG2E;
+  p.lse = a->lse;
+  p.delta = delta;
+  p.dq_accum = dq_accum;
+  p.dk = reinterpret_cast<bf16*>(a->dk); p.dk_sb = a->dk_sb; p.dk_ss = a->dk_ss; p.dk_sh = a->dk_sh;
+  p.dv = reinterpret_cast<bf16*>(a->dv); p.dv_sb = a->dv_sb; p.dv_ss = a->dv_ss; p.dv_sh = a->dv_sh;
+  p.status = a->status;
+  static bool attr_set = false;
+  if (!attr_set) {
+    OB_CUDA_OK(cudaFuncSetAttribute(fa_bwd::flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    fa_bwd::SMEM_BYTES));
+    attr_set = true;
+  }
+  dim3 grid((a->S + 127) / 128, a->Hkv, a->B);
+  fa_bwd::flash_bwd_kernel<<<grid, fa_bwd::THREADS, fa_bwd::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+  OB_CUDA_OK(cudaGetLastError());
+  fa_bwd::attn_dq_convert_kernel<<<nblk, wpb * 32, 0, stream>>>(dq_accum, reinterpret_cast<bf16*>(a->dq), a->dq_sb,
                                                                a->dq_ss, a->dq_sh, a->B, a->S, a->H);
   OB_CUDA_OK(cudaGetLastError());
   return 0;
