@@ -332,6 +332,28 @@ __global__ void embed_scatter_kernel(const long long* __restrict__ ids, float* c
   }
 }
 
+// dst[r * stride + i] = src_shards[r][i] for every shard r != skip (small tensors: norm weights, biases)
+__global__ void gather_shards_kernel(const uint16_t* const* __restrict__ src_shards, uint16_t* __restrict__ dst,
+                                     long long stride, long long n_per_shard, int n_shards, int skip) {
+  const long long total = n_per_shard * n_shards;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / n_per_shard);
+    const long long j = i % n_per_shard;
+    if (r == skip) continue;
+    dst[r * stride + j] = src_shards[r][j];
+  }
+}
+// dst_shards[r][i] += scale * src[r * n_per_shard + i]  (fp32, red.add; destinations may be peer GPUs)
+__global__ void scatter_add_shards_kernel(const float* __restrict__ src, float* const* __restrict__ dst_shards,
+                                          long long n_per_shard, int n_shards, float scale) {
+  const long long total = n_per_shard * n_shards;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / n_per_shard);
+    const long long j = i % n_per_shard;
+    atomicAdd(dst_shards[r] + j, src[i] * scale);
+  }
+}
+
 static inline int grid_for(long long work_items, int threads, int max_blocks_per_sm = 8) {
   long long blocks = (work_items + threads - 1) / threads;
   long long cap = (long long)sm_count() * max_blocks_per_sm;
@@ -441,6 +463,24 @@ extern "C" int ob_embed_scatter(const long long* ids, float* const* grad_shards,
   const long long blocks = (tokens * 32 + threads - 1) / threads;
   embed_scatter_kernel<<<(unsigned)blocks, threads, 0, stream>>>(ids, grad_shards, rows_per_shard, n_shards,
                                                                  (const bf16*)dout, tokens, d, scale);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_gather_shards(const void* const* src_shards, void* dst, long long stride, long long n_per_shard,
+                                int n_shards, int skip, cudaStream_t stream) {
+  if (n_per_shard <= 0) return 0;
+  gather_shards_kernel<<<grid_for(n_per_shard * n_shards, 256), 256, 0, stream>>>(
+      (const uint16_t* const*)src_shards, (uint16_t*)dst, stride, n_per_shard, n_shards, skip);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_scatter_add_shards(const float* src, float* const* dst_shards, long long n_per_shard, int n_shards,
+                                     float scale, cudaStream_t stream) {
+  if (n_per_shard <= 0) return 0;
+  scatter_add_shards_kernel<<<grid_for(n_per_shard * n_shards, 256), 256, 0, stream>>>(src, dst_shards, n_per_shard,
+                                                                                       n_shards, scale);
   OB_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -32,6 +32,14 @@ int ob_embed_gather(const long long* ids, const void* const* shards, int rows_pe
 int ob_embed_scatter(const long long* ids, float* const* grad_shards, int rows_per_shard, int n_shards,
                      const void* dout, long long tokens, int d, float scale, cudaStream_t stream);
 
+// Small-tensor helpers over R shards whose base pointers (DEVICE array) may address peer GPUs (plain loads / red.add):
+// gather 16-bit elements of every shard but `skip` into dst (shard r at dst + r*stride), and add a full fp32 vector
+// into the shards that own its slices.
+int ob_gather_shards(const void* const* src_shards, void* dst, long long stride, long long n_per_shard, int n_shards,
+                     int skip, cudaStream_t stream);
+int ob_scatter_add_shards(const float* src, float* const* dst_shards, long long n_per_shard, int n_shards, float scale,
+                          cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -30,7 +30,9 @@ constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int MN_BLOCK_BYTES = 64 * BK * 2;  // one 64(MN) x 64(K) MN-major block: 8 KiB
 constexpr int TMEM_COLS = 512;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 256;  // warp 0 TMA, 1 MMA, 2-5 epilogue, 6-7 peer-copy (fused all-gather)
+constexpr int COPY_WARPS = 2;
+constexpr int AG_BLOCK_ROWS = 256;  // granularity of the all-gather ready flags
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 
 struct KernelParams {
@@ -48,7 +50,40 @@ struct KernelParams {
   long long c_shard_stride;
   long long ldc;
   int* status;
+  // FSDP all-gather fused into the GEMM: the B operand's remote shards are pulled from peer GPUs (plain loads over
+  // NVLink) into the local staging buffer by the copy warps while the tensor cores work on tiles already present.
+  int ag_shards;               // 0: off
+  int ag_rank;                 // this GPU's shard index (its slot of the staging buffer is filled by the host)
+  int ag_rows;                 // rows of one shard piece
+  int ag_blocks;               // AG_BLOCK_ROWS-row blocks per shard piece
+  long long ag_row_bytes;      // bytes of one piece row
+  const uint8_t* const* ag_src;    // [ag_shards] piece base in each GPU's memory
+  const uint8_t* const* ag_src2;   // second operand of the gated epilogue, or null
+  uint8_t* ag_dst;             // staging piece of shard 0 (shard s at + s * ag_dst_stride)
+  uint8_t* ag_dst2;
+  long long ag_dst_stride;     // bytes
+  unsigned* ag_flags;          // [ag_shards * ag_blocks] arrival counters, monotonic across launches
+  unsigned ag_target;          // counter value that means "block present" for this launch
 };
+
+// Bounded wait for an all-gather block; returns false (and records the error) when it does not arrive.
+__device__ __forceinline__ bool ag_wait(const KernelParams& p, int shard, int block, volatile int* abort_flag) {
+  if (p.ag_shards == 0 || shard == p.ag_rank) return true;
+  const unsigned* f = p.ag_flags + shard * p.ag_blocks + block;
+  for (unsigned it = 0; it < (1u << 26); ++it) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+    if ((int)(v - p.ag_target) >= 0) {
+      asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy stores -> async-proxy (TMA) reads
+      return true;
+    }
+    if ((it & 255u) == 255u && *abort_flag) return false;
+    __nanosleep(64);
+  }
+  *abort_flag = 1;
+  report_error(p.status, ERR_PEER_TIMEOUT, 110, shard * 1000 + block);
+  return false;
+}
 
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
@@ -101,6 +136,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   const int total_tiles = m_tiles * n_tiles;
   const int k_iters = p.k_shards * p.k_iters_per_shard;
   const bool glu = (p.epi == EPI_SWIGLU || p.epi == EPI_GEGLU);
+  // With a fused all-gather the tile order is rotated so that work on the local shard comes first and the other
+  // shards follow in the order the copy warps fetch them (rank+1, rank+2, ...).
+  const int n_rot = (p.ag_shards > 0 && !B_MN) ? p.ag_rank * p.n_tiles_per_shard : 0;
+  const int k_rot = (p.ag_shards > 0 && B_MN) ? p.ag_rank * p.k_iters_per_shard : 0;
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
@@ -112,16 +151,22 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int mt = tile % m_tiles, nt = tile / m_tiles;
+        const int mt = tile % m_tiles, nt = (tile / m_tiles + n_rot) % n_tiles;
         const int m0 = (mt / p.m_tiles_per_shard) * p.M_s + (mt % p.m_tiles_per_shard) * BM;
         const int n_shard = nt / p.n_tiles_per_shard;
         const int n_local0 = (nt % p.n_tiles_per_shard) * p.bn_out;
-        for (int kit = 0; kit < k_iters; ++kit) {
+        for (int kit0 = 0; kit0 < k_iters; ++kit0) {
+          const int kit = (kit0 + k_rot) % k_iters;
           const int k_shard = kit / p.k_iters_per_shard;
           const int k_local = (kit % p.k_iters_per_shard) * BK;
           const int k_glob = k_shard * p.Kc_s + k_local;
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 100);
           if (!ok) break;
+          if (p.ag_shards > 0) {
+            ok = B_MN ? ag_wait(p, k_shard, k_local / AG_BLOCK_ROWS, abort_flag)
+                      : ag_wait(p, n_shard, n_local0 / AG_BLOCK_ROWS, abort_flag);
+            if (!ok) break;
+          }
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
           mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
@@ -190,6 +235,40 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       }
     }
     __syncwarp();
+  } else if (warp >= 6) {
+    // ------------------------------- peer-copy warps (fused all-gather) -------------------------------
+    if (p.ag_shards > 0) {
+      const int cw = (int)blockIdx.x * COPY_WARPS + (warp - 6);      // this copy warp's index
+      const int n_cw = (int)gridDim.x * COPY_WARPS;
+      for (int ds = 1; ds < p.ag_shards; ++ds) {
+        const int s = (p.ag_rank + ds) % p.ag_shards;
+        for (int b = 0; b < p.ag_blocks; ++b) {
+          const int rows = min(AG_BLOCK_ROWS, p.ag_rows - b * AG_BLOCK_ROWS);
+          const long long bytes = (long long)rows * p.ag_row_bytes;           // multiple of 16
+          const long long off = (long long)b * AG_BLOCK_ROWS * p.ag_row_bytes;
+          const long long n16 = bytes >> 4;
+          // each copy warp moves an interleaved slice of the block, 4 x 16 bytes per lane in flight
+          for (int which = 0; which < (p.ag_src2 != nullptr ? 2 : 1); ++which) {
+            const uint4* src = reinterpret_cast<const uint4*>((which ? p.ag_src2[s] : p.ag_src[s]) + off);
+            uint4* dst = reinterpret_cast<uint4*>((which ? p.ag_dst2 : p.ag_dst) + (long long)s * p.ag_dst_stride + off);
+            long long i = (long long)cw * 32 + lane;
+            const long long step = (long long)n_cw * 32;
+            for (; i + 3 * step < n16; i += 4 * step) {
+              const uint4 v0 = __ldcg(src + i), v1 = __ldcg(src + i + step), v2 = __ldcg(src + i + 2 * step),
+                          v3 = __ldcg(src + i + 3 * step);
+              dst[i] = v0; dst[i + step] = v1; dst[i + 2 * step] = v2; dst[i + 3 * step] = v3;
+            }
+            for (; i < n16; i += step) dst[i] = __ldcg(src + i);
+          }
+          __syncwarp();
+          if (lane == 0) {
+            __threadfence();
+            asm volatile("fence.proxy.async;" ::: "memory");
+            asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.ag_flags + s * p.ag_blocks + b) : "memory");
+          }
+        }
+      }
+    }
   } else {
     // ------------------------------- epilogue (warps 2..5) -------------------------------
     const int q = warp & 3;  // TMEM lane quarter this warp may access
@@ -199,7 +278,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
       const int buf = it & 1;
       const uint32_t tphase = (uint32_t)(it >> 1) & 1u;
-      const int mt = tile % m_tiles, nt = tile / m_tiles;
+      const int mt = tile % m_tiles, nt = (tile / m_tiles + n_rot) % n_tiles;
       const int m_shard = mt / p.m_tiles_per_shard;
       const int m_local0 = (mt % p.m_tiles_per_shard) * BM;
       const int n_shard = nt / p.n_tiles_per_shard;
@@ -426,6 +505,10 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
   kp.c_shard_stride = a->c_shard_stride;
   kp.ldc = a->ldc;
   kp.status = a->status;
+  kp.ag_shards = 0;
+  kp.ag_rank = 0; kp.ag_rows = 0; kp.ag_blocks = 0; kp.ag_row_bytes = 0;
+  kp.ag_src = nullptr; kp.ag_src2 = nullptr; kp.ag_dst = nullptr; kp.ag_dst2 = nullptr; kp.ag_dst_stride = 0;
+  kp.ag_flags = nullptr; kp.ag_target = 0;
 
   CUtensorMap tA, tB, tB2;
   memset(&tB2, 0, sizeof(tB2));
@@ -467,6 +550,26 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
   const int total = kp.m_shards * kp.m_tiles_per_shard * kp.n_shards * kp.n_tiles_per_shard;
   int cap = a->max_ctas > 0 ? a->max_ctas : sm_count();
   int grid = total < cap ? total : cap;
+  if (a->ag_src != nullptr) {
+    const int shards = a->b_mn ? kp.k_shards : kp.n_shards;
+    if (shards < 2 || bss <= 0) OB_FAIL(-10, "fused all-gather needs a sharded B operand");
+    if (a->ag_flags == nullptr) OB_FAIL(-11, "fused all-gather needs a flags buffer");
+    if (a->ag_rank < 0 || a->ag_rank >= shards) OB_FAIL(-12, "ag_rank %d outside [0, %d)", a->ag_rank, shards);
+    kp.ag_shards = shards;
+    kp.ag_rank = a->ag_rank;
+    kp.ag_rows = a->b_mn ? Kc_s : N_s;
+    kp.ag_blocks = (kp.ag_rows + AG_BLOCK_ROWS - 1) / AG_BLOCK_ROWS;
+    kp.ag_row_bytes = (long long)a->ldb * 2;
+    if (kp.ag_row_bytes % 16 != 0) OB_FAIL(-13, "fused all-gather needs 16-byte aligned rows");
+    kp.ag_src = reinterpret_cast<const uint8_t* const*>(a->ag_src);
+    kp.ag_src2 = reinterpret_cast<const uint8_t* const*>(a->ag_src2);
+    kp.ag_dst = reinterpret_cast<uint8_t*>(const_cast<void*>(a->b));
+    kp.ag_dst2 = reinterpret_cast<uint8_t*>(const_cast<void*>(a->b2));
+    kp.ag_dst_stride = bss * 2;
+    kp.ag_flags = a->ag_flags;
+    kp.ag_target = (unsigned)(grid * COPY_WARPS);
+    OB_CUDA_OK(cudaMemsetAsync(a->ag_flags, 0, sizeof(unsigned) * (size_t)shards * kp.ag_blocks, stream));
+  }
   if (a->a_mn) {
     return a->b_mn ? launch<true, true>(tA, tB, tB2, kp, grid, stream) : launch<true, false>(tA, tB, tB2, kp, grid, stream);
   }

@@ -45,6 +45,14 @@ typedef struct ObGemmArgs {
   float alpha;
   int* status;   // device int[4]: a kernel-side wait that ran out writes its code here (may be null)
   int max_ctas;  // 0 = one CTA per SM
+  // Fused FSDP all-gather (optional).  With ag_src set, B is a staging buffer of R shard slots (N_s / Kc_s rows each,
+  // b_shard_stride apart) of which only slot ag_rank is filled; the kernel's copy warps fetch the other slots from
+  // ag_src[s] (DEVICE array of R base pointers into the peer GPUs' memory, read with plain loads over NVLink) while
+  // the tensor cores start on the local slot, and tiles of slot s wait for its blocks to land (bounded wait).
+  const void* const* ag_src;
+  const void* const* ag_src2;  // same for b2 (gated epilogue)
+  unsigned* ag_flags;          // device scratch, >= R * ceil(rows_per_shard / 256) words; cleared by the launcher
+  int ag_rank;
 } ObGemmArgs;
 
 int ob_gemm_bf16(const ObGemmArgs* args, cudaStream_t stream);

@@ -244,6 +244,7 @@ class TransformerConfig(Registrable):
         compute_dtype: Optional[torch.dtype] = None,
         device: Optional[torch.device] = None,
         reshard_after_forward: bool = True,
+        comm_backend: Optional[str] = None,
         init: bool = True,
         **overrides,
     ) -> Transformer:
@@ -257,7 +258,7 @@ class TransformerConfig(Registrable):
         if compute_dtype is None:
             compute_dtype = torch.bfloat16 if torch.device(device).type == "cuda" else param_dtype
         store = ParamStore(mesh, param_dtype=param_dtype, compute_dtype=compute_dtype, device=torch.device(device),
-                           reshard_after_forward=reshard_after_forward)
+                           reshard_after_forward=reshard_after_forward, comm_backend=comm_backend)
         with BuildContext(store):
             model = Transformer(cfg)
         store.finalize(seed=seed, init=init)

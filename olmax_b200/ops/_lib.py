@@ -53,6 +53,10 @@ class ObGemmArgs(ctypes.Structure):
         ("alpha", ctypes.c_float),
         ("status", ctypes.c_void_p),
         ("max_ctas", ctypes.c_int),
+        ("ag_src", ctypes.c_void_p),
+        ("ag_src2", ctypes.c_void_p),
+        ("ag_flags", ctypes.c_void_p),
+        ("ag_rank", ctypes.c_int),
     ]
 
 

@@ -42,11 +42,27 @@ def _b_operand(handle):
     return first, {"N_s": handle.rows_local, "b_shard_stride": stride}
 
 
+def _ag_kwargs(handle, second=None) -> dict:
+    """GEMM arguments that fuse the FSDP all-gather of ``handle`` (and ``second``, the up-projection of a gated
+    MLP) into the launch, when the peer-memory backend still has to fetch their remote shards."""
+    ag = handle.take_ag()
+    if ag is None:
+        return {}
+    table, flags, rank = ag
+    out = {"ag_src": table, "ag_flags": flags, "ag_rank": rank}
+    if second is not None:
+        ag2 = second.take_ag()
+        if ag2 is not None:
+            out["ag_src2"] = ag2[0]
+    return out
+
+
 def _gemm_fwd(x2: torch.Tensor, handle, out: Optional[torch.Tensor] = None, epi: int = K.EPI_BF16) -> torch.Tensor:
     """y[M, N] = x2[M, K] @ W[N, K]^T with W read from the gathered unit buffer."""
     M, Kd = x2.shape
     N = handle.tp_shape[0]
     first, kw = _b_operand(handle)
+    kw.update(_ag_kwargs(handle))
     if out is None:
         out = torch.empty((M, N), dtype=torch.float32 if epi == K.EPI_F32 else torch.bfloat16, device=x2.device)
     K.gemm(x2, first, out, M, N, Kd, epi=epi, ldb=Kd, **kw)
@@ -60,6 +76,7 @@ def _gemm_dgrad(dy2: torch.Tensor, handle, out: Optional[torch.Tensor] = None, a
     first, stride = handle.pieces()
     R = handle.shard_count
     kw = {} if R == 1 else {"Kc_s": handle.rows_local, "b_shard_stride": stride}
+    kw.update(_ag_kwargs(handle))
     if out is None:
         out = torch.empty((M, Kd), dtype=torch.bfloat16, device=dy2.device)
     K.gemm(dy2, first, out, M, Kd, N, b_mn=True, ldb=Kd, epi=K.EPI_BF16_ACC if accumulate else K.EPI_BF16, **kw)
@@ -70,14 +87,15 @@ def _gemm_wgrad(dy2: torch.Tensor, x2: torch.Tensor, handle) -> None:
     """dW[N, K] += scale * dy2[M, N]^T @ x2[M, K], written into the handle's gradient destination."""
     M, N = dy2.shape
     Kd = x2.shape[1]
-    dst, gstride, scale = handle.grad_pieces()
     R = handle.shard_count
-    kw = {} if R == 1 else {"M_s": handle.rows_local, "c_shard_stride": gstride}
-    peer = handle.store.symm.grad_pointer_table(handle) if getattr(handle.store, "symm", None) is not None else None
+    symm = getattr(handle.store, "symm", None)
+    peer = symm.grad_pointer_table(handle) if (symm is not None and R > 1) else None
     if peer is not None:
-        K.gemm(dy2, x2, dst, N, Kd, M, a_mn=True, b_mn=True, epi=K.EPI_F32_RED, alpha=handle.store.grad_scale,
+        K.gemm(dy2, x2, handle.local_grad, N, Kd, M, a_mn=True, b_mn=True, epi=K.EPI_F32_RED, alpha=handle.store.grad_scale,
                ldc=Kd, M_s=handle.rows_local, c_shards=peer)
     else:
+        dst, gstride, scale = handle.grad_pieces()
+        kw = {} if R == 1 else {"M_s": handle.rows_local, "c_shard_stride": gstride}
         K.gemm(dy2, x2, dst, N, Kd, M, a_mn=True, b_mn=True, epi=K.EPI_F32_ACC, alpha=scale, ldc=Kd, **kw)
 
 
@@ -145,6 +163,7 @@ class _GatedMLPFn(torch.autograd.Function):
             u = torch.empty_like(a)
             gfirst, kw = _b_operand(gate)
             ufirst, _ = up.pieces()
+            kw.update(_ag_kwargs(gate, up))
             K.gemm(x2, gfirst, a, M, h, d, epi=K.EPI_GEGLU if act != "silu" else K.EPI_SWIGLU, b2=ufirst, c2=g, c3=u,
                    ldb=d, **kw)
             y = _gemm_fwd(a, down)
@@ -392,9 +411,13 @@ class _EmbeddingFn(torch.autograd.Function):
         ctx.save_for_backward(ids)
         d = handle.tp_shape[1]
         if ids.is_cuda:
-            first, stride = handle.pieces()
             R = handle.shard_count
-            table = _piece_pointer_table(first, stride, R)
+            symm = getattr(handle.store, "symm", None)
+            if symm is not None and R > 1:
+                table = symm.shadow_pointer_table(handle)   # rows are read from the GPU that owns them
+            else:
+                first, stride = handle.pieces()
+                table = _piece_pointer_table(first, stride, R)
             out = torch.empty(ids.shape + (d,), dtype=torch.bfloat16, device=ids.device)
             K.embed_gather(ids.contiguous(), table, handle.rows_local, R, out, d, scale)
             return out
@@ -408,12 +431,12 @@ class _EmbeddingFn(torch.autograd.Function):
         handle = ctx.handle
         d = handle.tp_shape[1]
         if dout.is_cuda:
-            dst, gstride, gscale = handle.grad_pieces()
             R = handle.shard_count
             symm = getattr(handle.store, "symm", None)
-            if symm is not None:
+            if symm is not None and R > 1:
                 table, gscale = symm.grad_pointer_table(handle), handle.store.grad_scale
             else:
+                dst, gstride, gscale = handle.grad_pieces()
                 table = _piece_pointer_table(dst, gstride, R)
             K.embed_scatter(ids.contiguous(), table, handle.rows_local, R, dout.contiguous(), d, ctx.scale * gscale)
         else:

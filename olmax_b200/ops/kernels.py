@@ -62,6 +62,8 @@ register_signature("ob_adamw", [_vp, _vp, _vp, _vp, _vp, _ll, _f, _f, _f, _f, _f
 register_signature("ob_sumsq", [_vp, _ll, _vp, _vp])
 register_signature("ob_clip_coef", [_vp, _f, _f, _vp, _vp])
 register_signature("ob_cast_f32_bf16", [_vp, _vp, _ll, _vp])
+register_signature("ob_gather_shards", [_vp, _vp, _ll, _ll, _i, _i, _vp])
+register_signature("ob_scatter_add_shards", [_vp, _vp, _ll, _i, _f, _vp])
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -104,6 +106,10 @@ def gemm(
     c_shards: Optional[torch.Tensor] = None,
     c_shard_stride: int = 0,
     max_ctas: int = 0,
+    ag_src: Optional[torch.Tensor] = None,
+    ag_src2: Optional[torch.Tensor] = None,
+    ag_flags: Optional[torch.Tensor] = None,
+    ag_rank: int = 0,
 ) -> None:
     """``C[M, N] (+)= alpha * A[M, K] . B[K, N]``; see ``csrc/gemm.h`` for operand layouts and sharding."""
     _req_bf16(a, b, b2)
@@ -125,6 +131,10 @@ def gemm(
     args.a_mn, args.b_mn, args.epi, args.alpha = int(a_mn), int(b_mn), epi, alpha
     args.status = status_buffer(a.device).data_ptr()
     args.max_ctas = max_ctas
+    args.ag_src = _ptr(ag_src)
+    args.ag_src2 = _ptr(ag_src2)
+    args.ag_flags = _ptr(ag_flags)
+    args.ag_rank = ag_rank
     check(lib().ob_gemm_bf16(ctypes.byref(args), stream_ptr(a.device)), "gemm")
     _count()
 
@@ -279,4 +289,18 @@ def clip_coef(sumsq_t, max_norm, pre_scale, out) -> None:
 
 def cast_f32_bf16(src, dst) -> None:
     check(lib().ob_cast_f32_bf16(src.data_ptr(), dst.data_ptr(), src.numel(), stream_ptr(src.device)), "cast")
+    _count()
+
+
+def gather_shards(table, dst, stride, n_per_shard, n_shards, skip) -> None:
+    """dst[r * stride + i] = shard_r[i] for every r != skip; ``table``: device array of shard base pointers."""
+    check(lib().ob_gather_shards(table.data_ptr(), dst.data_ptr(), stride, n_per_shard, n_shards, skip,
+                                 stream_ptr(dst.device)), "gather_shards")
+    _count()
+
+
+def scatter_add_shards(src, table, n_per_shard, n_shards, scale=1.0) -> None:
+    """shard_r[i] += scale * src[r * n_per_shard + i] (fp32 red.add; shards may live on peer GPUs)."""
+    check(lib().ob_scatter_add_shards(src.data_ptr(), table.data_ptr(), n_per_shard, n_shards, scale,
+                                      stream_ptr(src.device)), "scatter_add_shards")
     _count()

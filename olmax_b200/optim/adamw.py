@@ -90,6 +90,7 @@ class AdamW:
                             st.shadow[s:e] if st.shadow is not st.master else None, lr=lr, b1=cfg.b1, b2=cfg.b2,
                             eps=cfg.eps, wd=wd, bias_corr1=bc1, bias_corr2=bc2, gscale=self._coef, zero_grad=True)
             st.invalidate_gathered()
+            st.sync_peers()  # peers may read the new weights / add into the cleared accumulator only after this
         else:
             norm = st.global_grad_sumsq().sqrt()
             coef = 1.0

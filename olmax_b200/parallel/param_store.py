@@ -25,6 +25,7 @@ from __future__ import annotations
 import fnmatch
 import logging
 import math
+import os
 import zlib
 from dataclasses import dataclass, field
 from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
@@ -33,6 +34,7 @@ import torch
 import torch.distributed as dist
 
 from ..exceptions import OLMaxConfigurationError
+from ..ops import kernels as K
 from ..utils.tree import fold_in
 from . import collectives as coll
 from .mesh import DeviceMesh
@@ -119,9 +121,24 @@ class ParamHandle:
             return buf[0, m.unit_offset : m.unit_offset + m.numel_local].view(m.local_shape)
         cached = self.unit._full_cache.get(m.name)
         if cached is None:
+            if m.name in self.unit._ag_pending:
+                # small tensors (norm weights, biases) read through full(): fetch the peers' shards with our own
+                # plain-load kernel
+                K.gather_shards(self.store.symm.shadow_pointer_table(self), buf[0, m.unit_offset:], buf.stride(0),
+                                m.numel_local, R, self.store.mesh.shard.rank)
+                self.unit._ag_pending.discard(m.name)
             cached = buf[:, m.unit_offset : m.unit_offset + m.numel_local].reshape(m.tp_shape)
             self.unit._full_cache[m.name] = cached
         return cached
+
+    def take_ag(self):
+        """(peer pointer table, flags, rank) when this weight's remote shards still have to be fetched into the
+        gathered buffer by the next GEMM, else None; marks the weight as fetched."""
+        if self.unit is None or self.name not in self.unit._ag_pending:
+            return None
+        self.unit._ag_pending.discard(self.name)
+        symm = self.store.symm
+        return symm.shadow_pointer_table(self), symm.flags, self.store.mesh.shard.rank
 
     # ---- gradients ---------------------------------------------------------------------------------------------
     def grad_pieces(self) -> Tuple[torch.Tensor, int, float]:
@@ -141,8 +158,12 @@ class ParamHandle:
 
     def add_grad(self, g_full: torch.Tensor) -> None:
         """Accumulate a full (TP-local) gradient computed with ordinary tensor math (CPU path, small params)."""
-        first, stride, scale = self.grad_pieces()
         m = self.meta
+        if self.store.symm is not None and self.shard_count > 1:
+            K.scatter_add_shards(g_full.reshape(-1).float().contiguous(), self.store.symm.grad_pointer_table(self),
+                                 m.numel_local, self.shard_count, self.store.grad_scale)
+            return
+        first, stride, scale = self.grad_pieces()
         if self.shard_count == 1:
             first.add_(g_full.reshape(m.local_shape).to(first.dtype), alpha=scale)
             return
@@ -165,6 +186,7 @@ class FSDPUnit:
         self._gather_work = None
         self._full_grad: Optional[torch.Tensor] = None
         self._full_cache: Dict[str, torch.Tensor] = {}
+        self._ag_pending: set = set()
 
     # ---- gather ------------------------------------------------------------------------------------------------
     def start_gather(self) -> None:
@@ -177,6 +199,13 @@ class FSDPUnit:
             self._gathered = local.view(1, -1)
             return
         buf = st._take_buffer("gather", R * self.numel_local, st.compute_dtype).view(R, self.numel_local)
+        if st.symm is not None:
+            # peer-memory backend: only the local slot is filled here; every weight's remote slots are fetched by the
+            # first GEMM that uses it (all-gather fused into the GEMM)
+            buf[st.mesh.shard.rank].copy_(local)
+            self._ag_pending = {h.name for h in self.params}
+            self._gathered = buf
+            return
         self._gather_work = coll.all_gather_into(buf, local, st.mesh.shard, async_op=True)
         self._gathered = buf
         st.stats["all_gather_bytes"] += (R - 1) * self.numel_local * local.element_size()
@@ -196,6 +225,7 @@ class FSDPUnit:
         if self._gathered is not None and self.store.mesh.shard.size > 1:
             self.store._give_buffer("gather", self._gathered)
         self._gathered = None
+        self._ag_pending = set()
         self._full_cache.clear()
 
     # ---- gradients ---------------------------------------------------------------------------------------------
@@ -234,8 +264,10 @@ class ParamStore:
         compute_dtype: torch.dtype = torch.bfloat16,
         device: Optional[torch.device] = None,
         reshard_after_forward: bool = True,
+        comm_backend: Optional[str] = None,
     ):
         self.mesh = mesh
+        self.comm_backend = comm_backend or os.environ.get("OLMAX_B200_COMM_BACKEND", "auto")
         self.param_dtype = param_dtype
         self.compute_dtype = compute_dtype
         self.grad_comm_dtype = torch.float32
@@ -318,11 +350,23 @@ class ParamStore:
         self.numel_local = off
         dev = self.device
         self.master = torch.zeros(off, dtype=self.param_dtype, device=dev)
-        self.grad = torch.zeros(off, dtype=torch.float32, device=dev)
-        if self.compute_dtype == self.param_dtype:
-            self.shadow = self.master
+        use_symm = False
+        if self.comm_backend in ("auto", "fused") and self.mesh.shard.size > 1 and self.compute_dtype != self.param_dtype:
+            from .symm import SymmContext, symm_available
+
+            use_symm = symm_available(dev)
+            if self.comm_backend == "fused" and not use_symm:
+                raise OLMaxConfigurationError("comm_backend='fused' needs CUDA, NCCL and torch symmetric memory")
+        if use_symm:
+            self.symm = SymmContext(self, off)
+            self.grad = self.symm.grad
+            self.shadow = self.symm.shadow
         else:
-            self.shadow = self._alloc_shadow(off)
+            self.grad = torch.zeros(off, dtype=torch.float32, device=dev)
+            if self.compute_dtype == self.param_dtype:
+                self.shadow = self.master
+            else:
+                self.shadow = self._alloc_shadow(off)
         self._finalized = True
         if init:
             self.init_parameters(seed)
@@ -374,6 +418,7 @@ class ParamStore:
         if self.shadow is not self.master:
             self.shadow.copy_(self.master)
         self.invalidate_gathered()
+        self.sync_peers()
 
     # ------------------------------------------------------------------ buffer pool
     def _take_buffer(self, kind: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
@@ -431,6 +476,7 @@ class ParamStore:
         cross-replica all-reduce after every micro-batch; doing it once is mathematically identical because the
         accumulator is linear in the micro-batch gradients.
         """
+        self.sync_peers()
         rep = self.mesh.replicate
         if rep.size > 1:
             coll.all_reduce(self.grad, rep)
@@ -442,6 +488,12 @@ class ParamStore:
 
     def zero_grad(self) -> None:
         self.grad.zero_()
+
+    def sync_peers(self) -> None:
+        """With the peer-memory backend: stream-ordered barrier over the shard group.  It separates the phases in
+        which ranks write into each other's gradient shards / read each other's weights from the optimizer step."""
+        if self.symm is not None:
+            self.symm.sync_peers()
 
     def _runs(self, pred: Callable[[ParamMeta], bool]) -> List[Tuple[int, int]]:
         """Maximal contiguous [start, end) ranges of the flat buffer whose parameters satisfy ``pred``."""

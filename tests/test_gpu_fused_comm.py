@@ -1,0 +1,149 @@
+"""
+Fused compute + communication paths.
+
+* The all-gather fused into the GEMM is exercised on ONE GPU by letting the "peer" shard pointers address other local
+  buffers: the staging buffer holds only this rank's slot, the kernel's copy warps fetch the rest while tiles of the
+  local slot compute, and the result must equal a plain GEMM on the assembled weight.
+* On two GPUs (skipped when fewer are visible) a sharded model trained through the peer-memory backend (all-gather in
+  the GEMM, reduce-scatter in the weight-gradient epilogue, embedding rows read from their owner) must match the NCCL
+  backend.
+"""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from olmax_b200.testing import rel_err, run_distributed_test
+
+
+def _check():
+    from olmax_b200.ops import _lib
+
+    torch.cuda.synchronize()
+    _lib.check_status()
+
+
+@pytest.mark.parametrize("rank", [0, 2])
+def test_all_gather_fused_gemm_single_gpu_emulation(rank):
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from olmax_b200.ops import kernels as K
+
+    dev = torch.device("cuda")
+    torch.manual_seed(20)
+    M, N, Kd, R = 1024, 2048, 512, 4
+    rows = N // R
+    w = torch.randn(N, Kd, device=dev, dtype=torch.bfloat16)
+    a = torch.randn(M, Kd, device=dev, dtype=torch.bfloat16)
+    peers = [w[r * rows : (r + 1) * rows].clone() for r in range(R)]          # what each "GPU" owns
+    table = K.pointer_table([p.data_ptr() for p in peers], dev)
+    flags = torch.zeros(R * 64, dtype=torch.int32, device=dev)
+
+    def staging():
+        buf = torch.full((R, rows * Kd + 128), float("nan"), device=dev, dtype=torch.bfloat16)
+        buf[rank, : rows * Kd] = peers[rank].reshape(-1)
+        return buf
+
+    # forward: N-sharded K-major B
+    st = staging()
+    c = torch.zeros(M, N, device=dev, dtype=torch.bfloat16)
+    K.gemm(a, st, c, M, N, Kd, ldb=Kd, N_s=rows, b_shard_stride=st.stride(0), ag_src=table, ag_flags=flags, ag_rank=rank)
+    assert rel_err(c, a.float() @ w.float().t()) < 5e-3
+    assert not torch.isnan(st[:, : rows * Kd].float()).any()       # every slot was filled
+    got = torch.cat([st[r, : rows * Kd].view(rows, Kd) for r in range(R)])
+    assert torch.equal(got, w)
+    # dgrad: contraction over the shards (MN-major B)
+    st = staging()
+    dy = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
+    dx = torch.zeros(M, Kd, device=dev, dtype=torch.bfloat16)
+    K.gemm(dy, st, dx, M, Kd, N, b_mn=True, ldb=Kd, Kc_s=rows, b_shard_stride=st.stride(0), ag_src=table,
+           ag_flags=flags, ag_rank=rank)
+    assert rel_err(dx, dy.float() @ w.float()) < 5e-3
+    # gated MLP: two operands fetched by the same launch
+    w2 = torch.randn(N, Kd, device=dev, dtype=torch.bfloat16) * 0.1
+    peers2 = [w2[r * rows : (r + 1) * rows].clone() for r in range(R)]
+    table2 = K.pointer_table([p.data_ptr() for p in peers2], dev)
+    st1, st2 = staging(), torch.full((R, rows * Kd + 128), float("nan"), device=dev, dtype=torch.bfloat16)
+    st2[rank, : rows * Kd] = peers2[rank].reshape(-1)
+    act = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    g, u = torch.empty_like(act), torch.empty_like(act)
+    K.gemm(a, st1, act, M, N, Kd, ldb=Kd, N_s=rows, b_shard_stride=st1.stride(0), epi=K.EPI_SWIGLU, b2=st2, c2=g, c3=u,
+           ag_src=table, ag_src2=table2, ag_flags=flags, ag_rank=rank)
+    gf, uf = a.float() @ w.float().t(), a.float() @ w2.float().t()
+    assert rel_err(g, gf) < 5e-3 and rel_err(u, uf) < 5e-3
+    assert rel_err(act, torch.nn.functional.silu(gf) * uf) < 1e-2
+    _check()
+
+
+def test_small_shard_helpers():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from olmax_b200.ops import kernels as K
+
+    dev = torch.device("cuda")
+    R, n = 4, 96
+    shards = [torch.randn(n, device=dev).to(torch.bfloat16) for _ in range(R)]
+    table = K.pointer_table([s.data_ptr() for s in shards], dev)
+    dst = torch.zeros(R, n + 32, device=dev, dtype=torch.bfloat16)
+    K.gather_shards(table, dst, dst.stride(0), n, R, 1)
+    for r in range(R):
+        assert torch.equal(dst[r, :n], shards[r] if r != 1 else torch.zeros_like(shards[r]))
+    grads = [torch.zeros(n, device=dev) for _ in range(R)]
+    gtable = K.pointer_table([g.data_ptr() for g in grads], dev)
+    src = torch.randn(R * n, device=dev)
+    K.scatter_add_shards(src, gtable, n, R, 0.5)
+    K.scatter_add_shards(src, gtable, n, R, 0.5)
+    assert torch.allclose(torch.cat(grads), src, rtol=1e-6)
+    _check()
+
+
+def _train_worker(backend):
+    import torch.distributed as dist
+
+    from olmax_b200.models import DefaultTransformerConfig, ReorderedNormTransformerLayerConfig
+    from olmax_b200.nn import MultiheadSelfAttentionConfig, RMSNormConfig
+    from olmax_b200.ops import _lib
+    from olmax_b200.optim import AdamWConfig, ConstantSchedule
+    from olmax_b200.parallel import MeshResource, dist_utils
+
+    world, rank = dist_utils.get_world_size(), dist_utils.get_rank()
+    dev = torch.device("cuda", rank)
+    attn = MultiheadSelfAttentionConfig(n_heads=4, head_dim=128, qk_norm=RMSNormConfig(), use_head_qk_norm=False)
+    cfg = DefaultTransformerConfig(vocab_size=4096, d_model=512, hidden_size=1408, num_layers=2,
+                                   layer=ReorderedNormTransformerLayerConfig(attention=attn), ce_chunk_rows=256)
+    model = cfg.build(seed=5, mesh_resource=MeshResource.FSDP(world), device=dev, comm_backend=backend)
+    assert (model.store.symm is not None) == (backend == "fused")
+    optim = AdamWConfig(lr=ConstantSchedule(1e-3), max_grad_norm=1.0).build(model, 2)
+    g = torch.Generator().manual_seed(100 + rank)
+    cache = model.get_buffer_cache(256, dev)
+    losses = []
+    for step in range(3):
+        for mb in range(2):
+            ids = torch.randint(0, 4096, (2, 256), generator=g).to(dev)
+            labels = torch.roll(ids, -1, 1)
+            loss, _ = model(ids, labels, cache)
+            loss.backward()
+            optim.accumulate()
+        if step == 0:
+            first_grads = model.store.grad.clone()
+        optim.step()
+        losses.append(loss.item())
+    torch.cuda.synchronize()
+    _lib.check_status(dev)
+    full = {n: model.store.full_parameter(n).cpu() for n, _ in model.store.named_parameters()}
+    return losses, first_grads.cpu(), full
+
+
+def test_peer_memory_backend_matches_nccl_on_two_gpus():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    fused = run_distributed_test(_train_worker, world_size=2, backend="nccl", func_args=("fused",), timeout=300)
+    nccl = run_distributed_test(_train_worker, world_size=2, backend="nccl", func_args=("nccl",), timeout=300)
+    for r in range(2):
+        lf, gf, pf = fused[r]
+        ln, gn, pn = nccl[r]
+        assert all(abs(a - b) < 2e-2 * abs(b) for a, b in zip(lf, ln)), (lf, ln)
+        assert rel_err(gf, gn) < 2e-2
+        for name in pn:
+            assert rel_err(pf[name], pn[name]) < 1e-2, name
