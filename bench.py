@@ -120,6 +120,8 @@ def main() -> int:
     ap.add_argument("--microbatches", type=int, default=2)
     ap.add_argument("--layers", type=int, default=None, help="debug only: truncate the model (makes the run INVALID as a benchmark)")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl"],
+                    help="fused: collectives inside our kernels over peer memory; nccl: the NCCL baseline path")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -163,7 +165,7 @@ def main() -> int:
     global_batch = inst_per_dp * dp * k
     tokens_per_step = global_batch * seq
 
-    model = model_cfg.build(seed=1, mesh=mesh, device=dev)
+    model = model_cfg.build(seed=1, mesh=mesh, device=dev, comm_backend=args.comm)
     cache = model.get_buffer_cache(seq, dev)
     lr = 1e-4
     optim_cfg = AdamWConfig(lr=WarmupCosineDecaySchedule(warmup_steps=20, decay_steps=80, peak_value=lr, init_value=0.01 * lr,
@@ -254,6 +256,7 @@ def main() -> int:
             "config": {
                 "model": args.recipe, "global_batch": global_batch, "seq_len": seq, "microbatches": k,
                 "parallelism": f"{args.mesh.lower()}{world}", "optimizer": "AdamW fp32 master/moments",
+                "comm": "fused peer-memory kernels" if model.store.symm is not None else ("nccl" if world > 1 else "none"),
                 "layers": model_cfg.num_layers, "params": model.num_params(),
                 "l2": "working set (>14 GB of weights per step) exceeds L2, no explicit flush",
             },

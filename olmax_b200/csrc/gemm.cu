@@ -64,7 +64,28 @@ struct KernelParams {
   long long ag_dst_stride;     // bytes
   unsigned* ag_flags;          // [ag_shards * ag_blocks] arrival counters, monotonic across launches
   unsigned ag_target;          // counter value that means "block present" for this launch
+  // Prefetch for LATER launches: copy bytes [pf_off, pf_off + pf_bytes) of every remote shard's slice of the next
+  // FSDP unit into that unit's staging buffer (consumers are later kernels in stream order, so no flags).
+  int pf_shards;               // 0: off
+  int pf_rank;
+  const uint8_t* const* pf_src;    // [pf_shards] base of the unit slice in each GPU's memory
+  uint8_t* pf_dst;             // staging slot of shard 0 (shard s at + s * pf_dst_stride)
+  long long pf_dst_stride;
+  long long pf_off, pf_bytes;  // multiples of 16
 };
+
+// One warp-interleaved copy of n16 16-byte words; cw = this copy warp's index among n_cw.
+__device__ __forceinline__ void warp_copy16(const uint4* __restrict__ src, uint4* __restrict__ dst, long long n16, int cw,
+                                            int n_cw, int lane) {
+  long long i = (long long)cw * 32 + lane;
+  const long long step = (long long)n_cw * 32;
+  for (; i + 3 * step < n16; i += 4 * step) {
+    const uint4 v0 = __ldcg(src + i), v1 = __ldcg(src + i + step), v2 = __ldcg(src + i + 2 * step),
+                v3 = __ldcg(src + i + 3 * step);
+    dst[i] = v0; dst[i + step] = v1; dst[i + 2 * step] = v2; dst[i + 3 * step] = v3;
+  }
+  for (; i < n16; i += step) dst[i] = __ldcg(src + i);
+}
 
 // Bounded wait for an all-gather block; returns false (and records the error) when it does not arrive.
 __device__ __forceinline__ bool ag_wait(const KernelParams& p, int shard, int block, volatile int* abort_flag) {
@@ -237,9 +258,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     __syncwarp();
   } else if (warp >= 6) {
     // ------------------------------- peer-copy warps (fused all-gather) -------------------------------
+    const int cw = (int)blockIdx.x * COPY_WARPS + (warp - 6);      // this copy warp's index
+    const int n_cw = (int)gridDim.x * COPY_WARPS;
     if (p.ag_shards > 0) {
-      const int cw = (int)blockIdx.x * COPY_WARPS + (warp - 6);      // this copy warp's index
-      const int n_cw = (int)gridDim.x * COPY_WARPS;
       for (int ds = 1; ds < p.ag_shards; ++ds) {
         const int s = (p.ag_rank + ds) % p.ag_shards;
         for (int b = 0; b < p.ag_blocks; ++b) {
@@ -251,14 +272,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           for (int which = 0; which < (p.ag_src2 != nullptr ? 2 : 1); ++which) {
             const uint4* src = reinterpret_cast<const uint4*>((which ? p.ag_src2[s] : p.ag_src[s]) + off);
             uint4* dst = reinterpret_cast<uint4*>((which ? p.ag_dst2 : p.ag_dst) + (long long)s * p.ag_dst_stride + off);
-            long long i = (long long)cw * 32 + lane;
-            const long long step = (long long)n_cw * 32;
-            for (; i + 3 * step < n16; i += 4 * step) {
-              const uint4 v0 = __ldcg(src + i), v1 = __ldcg(src + i + step), v2 = __ldcg(src + i + 2 * step),
-                          v3 = __ldcg(src + i + 3 * step);
-              dst[i] = v0; dst[i + step] = v1; dst[i + 2 * step] = v2; dst[i + 3 * step] = v3;
-            }
-            for (; i < n16; i += step) dst[i] = __ldcg(src + i);
+            warp_copy16(src, dst, n16, cw, n_cw, lane);
           }
           __syncwarp();
           if (lane == 0) {
@@ -267,6 +281,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.ag_flags + s * p.ag_blocks + b) : "memory");
           }
         }
+      }
+    }
+    if (p.pf_shards > 0 && p.pf_bytes > 0) {
+      for (int ds = 1; ds < p.pf_shards; ++ds) {
+        const int s = (p.pf_rank + ds) % p.pf_shards;
+        warp_copy16(reinterpret_cast<const uint4*>(p.pf_src[s] + p.pf_off),
+                    reinterpret_cast<uint4*>(p.pf_dst + (long long)s * p.pf_dst_stride + p.pf_off), p.pf_bytes >> 4, cw,
+                    n_cw, lane);
       }
     }
   } else {
@@ -509,6 +531,16 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
   kp.ag_rank = 0; kp.ag_rows = 0; kp.ag_blocks = 0; kp.ag_row_bytes = 0;
   kp.ag_src = nullptr; kp.ag_src2 = nullptr; kp.ag_dst = nullptr; kp.ag_dst2 = nullptr; kp.ag_dst_stride = 0;
   kp.ag_flags = nullptr; kp.ag_target = 0;
+  kp.pf_shards = 0; kp.pf_rank = 0; kp.pf_src = nullptr; kp.pf_dst = nullptr; kp.pf_dst_stride = 0; kp.pf_off = 0;
+  kp.pf_bytes = 0;
+  if (a->pf_src != nullptr && a->pf_bytes > 0) {
+    if (a->pf_shards < 2 || a->pf_dst == nullptr) OB_FAIL(-14, "prefetch needs >= 2 shards and a destination");
+    if ((a->pf_off | a->pf_bytes | a->pf_dst_stride) & 15) OB_FAIL(-15, "prefetch offsets must be multiples of 16 bytes");
+    kp.pf_shards = a->pf_shards; kp.pf_rank = a->pf_rank;
+    kp.pf_src = reinterpret_cast<const uint8_t* const*>(a->pf_src);
+    kp.pf_dst = reinterpret_cast<uint8_t*>(a->pf_dst);
+    kp.pf_dst_stride = a->pf_dst_stride; kp.pf_off = a->pf_off; kp.pf_bytes = a->pf_bytes;
+  }
 
   CUtensorMap tA, tB, tB2;
   memset(&tB2, 0, sizeof(tB2));

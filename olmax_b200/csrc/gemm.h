@@ -53,6 +53,13 @@ typedef struct ObGemmArgs {
   const void* const* ag_src2;  // same for b2 (gated epilogue)
   unsigned* ag_flags;          // device scratch, >= R * ceil(rows_per_shard / 256) words; cleared by the launcher
   int ag_rank;
+  // Prefetch for later launches (optional): while this GEMM computes, its copy warps also copy bytes
+  // [pf_off, pf_off + pf_bytes) of every OTHER GPU's slice (pf_src[s], DEVICE array of pf_shards peer pointers) into
+  // pf_dst + s * pf_dst_stride.  Used to stream the next FSDP unit's weights in under the current unit's GEMMs.
+  const void* const* pf_src;
+  void* pf_dst;
+  long long pf_dst_stride, pf_off, pf_bytes;  // bytes, multiples of 16
+  int pf_shards, pf_rank;
 } ObGemmArgs;
 
 int ob_gemm_bf16(const ObGemmArgs* args, cudaStream_t stream);

@@ -37,7 +37,7 @@ class _UnitEnter(torch.autograd.Function):
     def forward(ctx, x, delta, unit: FSDPUnit):
         ctx.unit = unit
         ctx.has_delta = delta is not None
-        unit.gathered()
+        unit.start_gather()
         unit.store.prefetch(unit.index + 1)
         if delta is None:
             return x.view_as(x)
@@ -70,7 +70,8 @@ class _UnitExit(torch.autograd.Function):
     @staticmethod
     def backward(ctx, *grads):
         unit = ctx.unit
-        unit.gathered()
+        unit.store._in_backward = True
+        unit.start_gather()
         unit.store.prefetch(unit.index - 1)
         if ctx.has_delta:
             return grads[0], grads[1], None
@@ -160,7 +161,7 @@ class Transformer(Module):
         if tp.size > 1:
             flat = flat.chunk(tp.size)[tp.rank]
         emb_unit = self._unit("embedding")
-        emb_unit.gathered()
+        emb_unit.start_gather()
         self.store.prefetch(emb_unit.index + 1)
         if self._anchor is None or self._anchor.device != ids.device:
             self._anchor = torch.zeros(1, device=ids.device, requires_grad=True)
@@ -262,6 +263,9 @@ class TransformerConfig(Registrable):
         with BuildContext(store):
             model = Transformer(cfg)
         store.finalize(seed=seed, init=init)
+        # With the peer-memory backend the embedding rows are read from the GPU that owns them, so the (large)
+        # embedding unit is only gathered when something else needs the full matrix (a tied LM head).
+        store.unit("embedding").lazy = store.symm_ag is not None
         return model
 
 

@@ -57,6 +57,13 @@ class ObGemmArgs(ctypes.Structure):
         ("ag_src2", ctypes.c_void_p),
         ("ag_flags", ctypes.c_void_p),
         ("ag_rank", ctypes.c_int),
+        ("pf_src", ctypes.c_void_p),
+        ("pf_dst", ctypes.c_void_p),
+        ("pf_dst_stride", ctypes.c_longlong),
+        ("pf_off", ctypes.c_longlong),
+        ("pf_bytes", ctypes.c_longlong),
+        ("pf_shards", ctypes.c_int),
+        ("pf_rank", ctypes.c_int),
     ]
 
 

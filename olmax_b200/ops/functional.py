@@ -63,6 +63,7 @@ def _gemm_fwd(x2: torch.Tensor, handle, out: Optional[torch.Tensor] = None, epi:
     N = handle.tp_shape[0]
     first, kw = _b_operand(handle)
     kw.update(_ag_kwargs(handle))
+    kw["prefetch"] = handle.store.prefetch_slice(N * Kd)
     if out is None:
         out = torch.empty((M, N), dtype=torch.float32 if epi == K.EPI_F32 else torch.bfloat16, device=x2.device)
     K.gemm(x2, first, out, M, N, Kd, epi=epi, ldb=Kd, **kw)
@@ -77,6 +78,7 @@ def _gemm_dgrad(dy2: torch.Tensor, handle, out: Optional[torch.Tensor] = None, a
     R = handle.shard_count
     kw = {} if R == 1 else {"Kc_s": handle.rows_local, "b_shard_stride": stride}
     kw.update(_ag_kwargs(handle))
+    kw["prefetch"] = handle.store.prefetch_slice(N * Kd)
     if out is None:
         out = torch.empty((M, Kd), dtype=torch.bfloat16, device=dy2.device)
     K.gemm(dy2, first, out, M, Kd, N, b_mn=True, ldb=Kd, epi=K.EPI_BF16_ACC if accumulate else K.EPI_BF16, **kw)
@@ -88,15 +90,16 @@ def _gemm_wgrad(dy2: torch.Tensor, x2: torch.Tensor, handle) -> None:
     M, N = dy2.shape
     Kd = x2.shape[1]
     R = handle.shard_count
-    symm = getattr(handle.store, "symm", None)
+    symm = getattr(handle.store, "symm_rs", None)
     peer = symm.grad_pointer_table(handle) if (symm is not None and R > 1) else None
+    pf = handle.store.prefetch_slice(N * Kd)
     if peer is not None:
         K.gemm(dy2, x2, handle.local_grad, N, Kd, M, a_mn=True, b_mn=True, epi=K.EPI_F32_RED, alpha=handle.store.grad_scale,
-               ldc=Kd, M_s=handle.rows_local, c_shards=peer)
+               ldc=Kd, M_s=handle.rows_local, c_shards=peer, prefetch=pf)
     else:
         dst, gstride, scale = handle.grad_pieces()
         kw = {} if R == 1 else {"M_s": handle.rows_local, "c_shard_stride": gstride}
-        K.gemm(dy2, x2, dst, N, Kd, M, a_mn=True, b_mn=True, epi=K.EPI_F32_ACC, alpha=scale, ldc=Kd, **kw)
+        K.gemm(dy2, x2, dst, N, Kd, M, a_mn=True, b_mn=True, epi=K.EPI_F32_ACC, alpha=scale, ldc=Kd, prefetch=pf, **kw)
 
 
 # ----------------------------------------------------------------------------------------------------------------------
@@ -164,6 +167,7 @@ class _GatedMLPFn(torch.autograd.Function):
             gfirst, kw = _b_operand(gate)
             ufirst, _ = up.pieces()
             kw.update(_ag_kwargs(gate, up))
+            kw["prefetch"] = gate.store.prefetch_slice(2 * h * d)
             K.gemm(x2, gfirst, a, M, h, d, epi=K.EPI_GEGLU if act != "silu" else K.EPI_SWIGLU, b2=ufirst, c2=g, c3=u,
                    ldb=d, **kw)
             y = _gemm_fwd(a, down)
@@ -285,7 +289,7 @@ class _RMSNormFn(torch.autograd.Function):
             dx = torch.empty_like(dyc)
             ld = d * heads if heads > 1 else d
             R = handle.shard_count
-            direct = R == 1 and getattr(handle.store, "symm", None) is None
+            direct = R == 1 and getattr(handle.store, "symm_rs", None) is None
             if direct:
                 dw, dw_scale = handle.local_grad, handle.store.grad_scale
             else:
@@ -412,7 +416,7 @@ class _EmbeddingFn(torch.autograd.Function):
         d = handle.tp_shape[1]
         if ids.is_cuda:
             R = handle.shard_count
-            symm = getattr(handle.store, "symm", None)
+            symm = getattr(handle.store, "symm_ag", None)
             if symm is not None and R > 1:
                 table = symm.shadow_pointer_table(handle)   # rows are read from the GPU that owns them
             else:
@@ -432,7 +436,7 @@ class _EmbeddingFn(torch.autograd.Function):
         d = handle.tp_shape[1]
         if dout.is_cuda:
             R = handle.shard_count
-            symm = getattr(handle.store, "symm", None)
+            symm = getattr(handle.store, "symm_rs", None)
             if symm is not None and R > 1:
                 table, gscale = symm.grad_pointer_table(handle), handle.store.grad_scale
             else:

@@ -110,6 +110,7 @@ def gemm(
     ag_src2: Optional[torch.Tensor] = None,
     ag_flags: Optional[torch.Tensor] = None,
     ag_rank: int = 0,
+    prefetch: Optional[tuple] = None,
 ) -> None:
     """``C[M, N] (+)= alpha * A[M, K] . B[K, N]``; see ``csrc/gemm.h`` for operand layouts and sharding."""
     _req_bf16(a, b, b2)
@@ -135,6 +136,10 @@ def gemm(
     args.ag_src2 = _ptr(ag_src2)
     args.ag_flags = _ptr(ag_flags)
     args.ag_rank = ag_rank
+    if prefetch is not None:
+        table, dst_ptr, dst_stride, off, nbytes, shards, rank = prefetch
+        args.pf_src, args.pf_dst, args.pf_dst_stride = table.data_ptr(), dst_ptr, dst_stride
+        args.pf_off, args.pf_bytes, args.pf_shards, args.pf_rank = off, nbytes, shards, rank
     check(lib().ob_gemm_bf16(ctypes.byref(args), stream_ptr(a.device)), "gemm")
     _count()
 

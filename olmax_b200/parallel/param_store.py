@@ -159,7 +159,7 @@ class ParamHandle:
     def add_grad(self, g_full: torch.Tensor) -> None:
         """Accumulate a full (TP-local) gradient computed with ordinary tensor math (CPU path, small params)."""
         m = self.meta
-        if self.store.symm is not None and self.shard_count > 1:
+        if self.store.symm_rs is not None and self.shard_count > 1:
             K.scatter_add_shards(g_full.reshape(-1).float().contiguous(), self.store.symm.grad_pointer_table(self),
                                  m.numel_local, self.shard_count, self.store.grad_scale)
             return
@@ -187,10 +187,13 @@ class FSDPUnit:
         self._full_grad: Optional[torch.Tensor] = None
         self._full_cache: Dict[str, torch.Tensor] = {}
         self._ag_pending: set = set()
+        self._pf_cursor = 0
+        self.numel_full_2d = 1
+        self.lazy = False  # True: only gather when a consumer actually asks for the gathered buffer
 
     # ---- gather ------------------------------------------------------------------------------------------------
-    def start_gather(self) -> None:
-        if self._gathered is not None:
+    def start_gather(self, force: bool = False) -> None:
+        if self._gathered is not None or (self.lazy and not force):
             return
         st = self.store
         R = st.mesh.shard.size
@@ -199,11 +202,12 @@ class FSDPUnit:
             self._gathered = local.view(1, -1)
             return
         buf = st._take_buffer("gather", R * self.numel_local, st.compute_dtype).view(R, self.numel_local)
-        if st.symm is not None:
+        if st.symm_ag is not None:
             # peer-memory backend: only the local slot is filled here; every weight's remote slots are fetched by the
             # first GEMM that uses it (all-gather fused into the GEMM)
             buf[st.mesh.shard.rank].copy_(local)
             self._ag_pending = {h.name for h in self.params}
+            self._pf_cursor = 0
             self._gathered = buf
             return
         self._gather_work = coll.all_gather_into(buf, local, st.mesh.shard, async_op=True)
@@ -212,7 +216,7 @@ class FSDPUnit:
 
     def gathered(self) -> torch.Tensor:
         if self._gathered is None:
-            self.start_gather()
+            self.start_gather(force=True)
         if self._gather_work is not None:
             self._gather_work.wait()
             self._gather_work = None
@@ -226,6 +230,9 @@ class FSDPUnit:
             self.store._give_buffer("gather", self._gathered)
         self._gathered = None
         self._ag_pending = set()
+        self._pf_cursor = 0
+        if self.store._pf_unit is self:
+            self.store._pf_unit = None
         self._full_cache.clear()
 
     # ---- gradients ---------------------------------------------------------------------------------------------
@@ -287,6 +294,10 @@ class ParamStore:
         self.stats: Dict[str, int] = {"all_gather_bytes": 0, "reduce_scatter_bytes": 0, "all_reduce_bytes": 0}
         self._finalized = False
         self.symm = None  # symmetric-memory context when the fused backend is active
+        self._pf_unit: Optional[FSDPUnit] = None
+        self._in_backward = False
+        self.symm_ag = None  # ... used for the all-gather side (weights fetched inside the GEMMs)
+        self.symm_rs = None  # ... used for the reduce-scatter side (gradients added into the owners' shards)
 
     # ------------------------------------------------------------------ registration
     def register(
@@ -346,6 +357,7 @@ class ParamStore:
                 h.meta.offset = off + uoff
                 uoff += (h.meta.numel_local + align - 1) // align * align
             u.numel_local = uoff
+            u.numel_full_2d = max(1, sum(int(math.prod(h.meta.tp_shape)) for h in u.params if len(h.meta.shape) == 2))
             off += uoff
         self.numel_local = off
         dev = self.device
@@ -361,6 +373,9 @@ class ParamStore:
             self.symm = SymmContext(self, off)
             self.grad = self.symm.grad
             self.shadow = self.symm.shadow
+            # experiment knobs: fall back to the NCCL collective for one direction while keeping the other fused
+            self.symm_ag = self.symm if os.environ.get("OLMAX_B200_FUSED_AG", "1") == "1" else None
+            self.symm_rs = self.symm if os.environ.get("OLMAX_B200_FUSED_RS", "1") == "1" else None
         else:
             self.grad = torch.zeros(off, dtype=torch.float32, device=dev)
             if self.compute_dtype == self.param_dtype:
@@ -445,8 +460,41 @@ class ParamStore:
         return self._unit_by_name[name]
 
     def prefetch(self, unit_index: int) -> None:
-        if 0 <= unit_index < len(self.units):
-            self.units[unit_index].start_gather()
+        """Start bringing in the weights of a unit that will be needed soon.  NCCL backend: launch its all-gather.
+        Peer-memory backend: allocate its staging buffer and make it the target that subsequent GEMM launches stream
+        remote shards into (see :meth:`prefetch_slice`)."""
+        if not (0 <= unit_index < len(self.units)):
+            return
+        u = self.units[unit_index]
+        u.start_gather()
+        if self.symm_ag is not None and self.mesh.shard.size > 1:
+            self._pf_unit = u if u._pf_cursor < u.numel_local * self.shadow.element_size() else None
+
+    def prefetch_slice(self, weight_numel: int):
+        """Arguments that let one GEMM launch carry part of the prefetch target's all-gather: the launch copies a byte
+        range of every remote shard's slice of that unit, sized in proportion to the GEMM's own weight so that the copy
+        takes about as long as the math.  Parameters whose bytes are covered stop being pending."""
+        u = self._pf_unit
+        if u is None or u._gathered is None or self.symm_ag is None:
+            return None
+        es = self.shadow.element_size()
+        total = u.numel_local * es
+        if u._pf_cursor >= total:
+            self._pf_unit = None
+            return None
+        passes = 2.0 if self._in_backward else 1.0
+        frac = 1.25 * weight_numel / max(1.0, u.numel_full_2d * passes)
+        nbytes = min(total - u._pf_cursor, (int(total * frac) + 15) // 16 * 16)
+        if nbytes <= 0:
+            return None
+        off = u._pf_cursor
+        u._pf_cursor += nbytes
+        for h in u.params:
+            if (h.meta.unit_offset + h.meta.numel_local) * es <= u._pf_cursor:
+                u._ag_pending.discard(h.name)
+        buf = u._gathered
+        return (self.symm_ag.unit_pointer_table(u), buf.data_ptr(), buf.stride(0) * es, off, nbytes,
+                self.mesh.shard.size, self.mesh.shard.rank)
 
     def invalidate_gathered(self) -> None:
         for u in self.units:
@@ -455,6 +503,7 @@ class ParamStore:
     def finish_backward(self) -> None:
         """Reduce any unit whose gradient is still un-reduced (embedding: its backward runs last), wait for the
         in-flight reduce-scatters, fold them into the fp32 accumulators and drop gathered weights."""
+        self._in_backward = False
         for u in self.units:
             if u._full_grad is not None:
                 u.reduce_grads()

@@ -84,6 +84,16 @@ class SymmContext:
     def shadow_pointer_table(self, handle) -> torch.Tensor:
         return self._table("shadow", handle, self.shadow_ptrs, self.shadow.element_size())
 
+    def unit_pointer_table(self, unit) -> torch.Tensor:
+        """Device array of the R addresses of ``unit``'s slice of the bf16 weights (one per GPU)."""
+        key = ("unit", unit.name)
+        t = self._tables.get(key)
+        if t is None:
+            off = unit.offset * self.shadow.element_size()
+            t = K.pointer_table([p + off for p in self.shadow_ptrs], self.store.device)
+            self._tables[key] = t
+        return t
+
     def sync_peers(self) -> None:
         """Stream-ordered barrier over the shard group (a one-element NCCL all-reduce)."""
         dist.all_reduce(self._token, group=self.group.pg)
