@@ -33,7 +33,8 @@ constexpr int TMEM_COLS = 512;
 constexpr int GEMM_THREADS = 256;  // warp 0 TMA, 1 MMA, 2-5 epilogue, 6-7 peer-copy (fused all-gather)
 constexpr int COPY_WARPS = 2;
 constexpr int AG_BLOCK_ROWS = 256;  // granularity of the all-gather ready flags
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int EPI_STAGE_BYTES = 128 * 128;  // one 128-row x 128-byte output chunk
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * EPI_STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 
 struct KernelParams {
   int M, N, Kc;
@@ -50,6 +51,9 @@ struct KernelParams {
   long long c_shard_stride;
   long long ldc;
   int* status;
+  int group_m;                 // tile rasterisation group (M tiles)
+  int a_single, b_single;      // MN-major operand fetched with one 4-D TMA box per stage instead of 64-wide boxes
+  int tma_epi;                 // 1: outputs leave through shared memory + TMA store / reduce-add (tmC valid)
   // FSDP all-gather fused into the GEMM: the B operand's remote shards are pulled from peer GPUs (plain loads over
   // NVLink) into the local staging buffer by the copy warps while the tensor cores work on tiles already present.
   int ag_shards;               // 0: off
@@ -87,6 +91,18 @@ __device__ __forceinline__ void warp_copy16(const uint4* __restrict__ src, uint4
   for (; i < n16; i += step) dst[i] = __ldcg(src + i);
 }
 
+// Tile rasterisation: tiles are visited in groups of `group_m` consecutive M tiles, all N tiles of a group before the
+// next group, M fastest inside.  A wave of ~148 concurrent CTAs then touches group_m A slabs and 148 / group_m B slabs
+// instead of every A slab, which keeps the operands of a wave resident in L2.
+__device__ __forceinline__ void decode_tile(int tile, int m_tiles, int n_tiles, int group_m, int n_rot, int& mt, int& nt) {
+  const int per_group = group_m * n_tiles;
+  const int g = tile / per_group;
+  const int within = tile - g * per_group;
+  const int gm = min(group_m, m_tiles - g * group_m);
+  nt = (within / gm + n_rot) % n_tiles;
+  mt = g * group_m + within % gm;
+}
+
 // Bounded wait for an all-gather block; returns false (and records the error) when it does not arrive.
 __device__ __forceinline__ bool ag_wait(const KernelParams& p, int shard, int block, volatile int* abort_flag) {
   if (p.ag_shards == 0 || shard == p.ag_rank) return true;
@@ -116,10 +132,12 @@ __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x));
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                     const __grid_constant__ CUtensorMap tmB2, const KernelParams p) {
+                     const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmC,
+                     const KernelParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* epi_smem = smem + STAGES * STAGE_BYTES;   // 2 x 16 KiB output staging, 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + 2 * EPI_STAGE_BYTES);
   uint64_t* full_bar = bars;                       // [STAGES]
   uint64_t* empty_bar = bars + STAGES;             // [STAGES]
   uint64_t* tfull_bar = bars + 2 * STAGES;         // [2]
@@ -172,7 +190,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int mt = tile % m_tiles, nt = (tile / m_tiles + n_rot) % n_tiles;
+        int mt, nt;
+        decode_tile(tile, m_tiles, n_tiles, p.group_m, n_rot, mt, nt);
         const int m0 = (mt / p.m_tiles_per_shard) * p.M_s + (mt % p.m_tiles_per_shard) * BM;
         const int n_shard = nt / p.n_tiles_per_shard;
         const int n_local0 = (nt % p.n_tiles_per_shard) * p.bn_out;
@@ -192,17 +211,26 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           uint8_t* sb = sa + A_STAGE_BYTES;
           mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
           if (A_MN) {
-            tma_load_3d(sa, &tmA, &full_bar[stage], m0, k_glob, 0);
-            tma_load_3d(sa + MN_BLOCK_BYTES, &tmA, &full_bar[stage], m0 + 64, k_glob, 0);
+            if (p.a_single) {
+              // one 4-D box: (64 elements, 64 k-rows, 2 column blocks): lands as [block][k][128 B]
+              tma_load_4d(sa, &tmA, &full_bar[stage], 0, k_glob, m0 >> 6, 0);
+            } else {
+              tma_load_3d(sa, &tmA, &full_bar[stage], m0, k_glob, 0);
+              tma_load_3d(sa + MN_BLOCK_BYTES, &tmA, &full_bar[stage], m0 + 64, k_glob, 0);
+            }
           } else {
             tma_load_3d(sa, &tmA, &full_bar[stage], k_glob, m0, 0);
           }
           if (B_MN) {
             // dims (N, Kc_s, k_shards): four 64-wide blocks along N
             const int n0 = n_local0;  // MN-major B is never N-sharded
+            if (p.b_single) {
+              tma_load_4d(sb, &tmB, &full_bar[stage], 0, k_local, n0 >> 6, k_shard);
+            } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              tma_load_3d(sb + j * MN_BLOCK_BYTES, &tmB, &full_bar[stage], n0 + j * 64, k_local, k_shard);
+              for (int j = 0; j < 4; ++j)
+                tma_load_3d(sb + j * MN_BLOCK_BYTES, &tmB, &full_bar[stage], n0 + j * 64, k_local, k_shard);
+            }
           } else if (glu) {
             tma_load_3d(sb, &tmB, &full_bar[stage], k_glob, n_local0, n_shard);
             tma_load_3d(sb + B_STAGE_BYTES / 2, &tmB2, &full_bar[stage], k_glob, n_local0, n_shard);
@@ -300,7 +328,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
       const int buf = it & 1;
       const uint32_t tphase = (uint32_t)(it >> 1) & 1u;
-      const int mt = tile % m_tiles, nt = (tile / m_tiles + n_rot) % n_tiles;
+      int mt, nt;
+        decode_tile(tile, m_tiles, n_tiles, p.group_m, n_rot, mt, nt);
       const int m_shard = mt / p.m_tiles_per_shard;
       const int m_local0 = (mt % p.m_tiles_per_shard) * BM;
       const int n_shard = nt / p.n_tiles_per_shard;
@@ -326,7 +355,55 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         cbase = reinterpret_cast<uint8_t*>(p.c);
         row_off = (long long)(m_shard * p.M_s + m_local0 + row_in_tile) * p.ldc + n_glob0;
       }
-      if (!glu) {
+      if (p.tma_epi) {
+        // Output through shared memory + TMA: each thread writes its row's 128 bytes of the chunk into a swizzled
+        // staging tile, one thread issues a bulk tensor store (or reduce-add for the accumulating epilogue).  The
+        // TMA clips at the tensor / shard boundary, so partial tiles need no per-element guards.
+        const bool f32 = (p.epi != EPI_BF16);
+        const int cols = f32 ? 32 : 64;                      // columns per 128-byte chunk row
+        const int out_row = (p.c_shard_stride > 0) ? m_local0 : m_shard * p.M_s + m_local0;
+        const int out_z = (p.c_shard_stride > 0) ? m_shard : 0;
+        const bool store_thread = (threadIdx.x == 64);
+        int chunk = 0;
+        for (int c0 = 0; c0 < BN; c0 += cols, ++chunk) {
+          if (c0 >= n_valid) break;
+          uint8_t* stage_buf = epi_smem + (chunk & 1) * EPI_STAGE_BYTES;
+          if (store_thread) tma_store_wait_read<1>();        // the store that last read this buffer is done with it
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          uint32_t r[32], r2[32];
+          tmem_ld32(t_row + (uint32_t)c0, r);
+          if (!f32) tmem_ld32(t_row + (uint32_t)(c0 + 32), r2);
+          tmem_ld_wait();
+          uint8_t* srow = stage_buf + row_in_tile * 128;
+          const int sw = row_in_tile & 7;
+          if (f32) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 v = make_float4(__uint_as_float(r[j * 4 + 0]) * p.alpha, __uint_as_float(r[j * 4 + 1]) * p.alpha,
+                                     __uint_as_float(r[j * 4 + 2]) * p.alpha, __uint_as_float(r[j * 4 + 3]) * p.alpha);
+              *reinterpret_cast<float4*>(srow + ((j ^ sw) << 4)) = v;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t* src = (j < 4) ? &r[j * 8] : &r2[(j - 4) * 8];
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(src[0]) * p.alpha, __uint_as_float(src[1]) * p.alpha);
+              v.y = pack_bf16x2(__uint_as_float(src[2]) * p.alpha, __uint_as_float(src[3]) * p.alpha);
+              v.z = pack_bf16x2(__uint_as_float(src[4]) * p.alpha, __uint_as_float(src[5]) * p.alpha);
+              v.w = pack_bf16x2(__uint_as_float(src[6]) * p.alpha, __uint_as_float(src[7]) * p.alpha);
+              *reinterpret_cast<uint4*>(srow + ((j ^ sw) << 4)) = v;
+            }
+          }
+          fence_proxy_async();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (store_thread) {
+            if (p.epi == EPI_F32_ACC) tma_reduce_add_3d(&tmC, stage_buf, n_glob0 + c0, out_row, out_z);
+            else tma_store_3d(&tmC, stage_buf, n_glob0 + c0, out_row, out_z);
+            tma_store_commit();
+          }
+        }
+      } else if (!glu) {
         for (int c0 = 0; c0 < BN; c0 += 32) {
           if (c0 >= n_valid) break;  // warp-uniform
           uint32_t r[32];
@@ -472,6 +549,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   }
 
   // teardown: everyone meets here (also after an aborted wait), then the allocating warp frees TMEM
+  if (threadIdx.x == 64) tma_store_wait<0>();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -479,15 +557,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 }
 
 template <bool A_MN, bool B_MN>
-static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const KernelParams& kp,
-                  int grid, cudaStream_t stream) {
+static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const CUtensorMap& tC,
+                  const KernelParams& kp, int grid, cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
     OB_CUDA_OK(cudaFuncSetAttribute(gemm_bf16_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     SMEM_BYTES));
     attr_set = true;
   }
-  gemm_bf16_kernel<A_MN, B_MN><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(tA, tB, tB2, kp);
+  gemm_bf16_kernel<A_MN, B_MN><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(tA, tB, tB2, tC, kp);
   OB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -521,6 +599,8 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
   kp.n_tiles_per_shard = (N_s + kp.bn_out - 1) / kp.bn_out;
   kp.k_iters_per_shard = (Kc_s + BK - 1) / BK;
   kp.epi = a->epi;
+  kp.group_m = a->group_m > 0 ? a->group_m : 16;
+  if (kp.group_m > kp.m_shards * kp.m_tiles_per_shard) kp.group_m = kp.m_shards * kp.m_tiles_per_shard;
   kp.alpha = a->alpha;
   kp.c = a->c; kp.c2 = a->c2; kp.c3 = a->c3;
   kp.c_shards = a->c_shards;
@@ -545,7 +625,16 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
   CUtensorMap tA, tB, tB2;
   memset(&tB2, 0, sizeof(tB2));
   int rc;
-  if (a->a_mn) {  // stored [Kc, M], M contiguous
+  kp.a_single = kp.b_single = 0;
+  if (a->a_mn && a->M % 64 == 0 && !a->multi_box_mn) {
+    // view [Kc, M] as (64, Kc, M/64): a tile is ONE box of 64 x 64 x 2, which lands in shared memory as two
+    // [64 k][128 B] blocks, the MN-major layout the MMA descriptor expects
+    uint64_t dims[4] = {64, (uint64_t)a->Kc, (uint64_t)a->M / 64, 1};
+    uint64_t str[3] = {(uint64_t)a->lda * 2, 128, (uint64_t)a->lda * 2 * (uint64_t)a->Kc};
+    uint32_t box[4] = {64, (uint32_t)BK, 2, 1};
+    rc = encode_tmap(&tA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, a->a, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    kp.a_single = 1;
+  } else if (a->a_mn) {  // stored [Kc, M], M contiguous
     uint64_t dims[3] = {(uint64_t)a->M, (uint64_t)a->Kc, 1};
     uint64_t str[2] = {(uint64_t)a->lda * 2, (uint64_t)a->lda * 2 * (uint64_t)a->Kc};
     uint32_t box[3] = {64, (uint32_t)BK, 1};
@@ -558,7 +647,15 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
   }
   if (rc) return rc;
   const long long bss = a->b_shard_stride > 0 ? a->b_shard_stride : 0;
-  if (a->b_mn) {  // stored [Kc, N] per k-shard, N contiguous
+  if (a->b_mn && a->N % 64 == 0 && !a->multi_box_mn) {
+    uint64_t sstride = kp.k_shards > 1 ? (uint64_t)bss * 2 : (uint64_t)a->ldb * 2 * (uint64_t)Kc_s;
+    uint64_t dims[4] = {64, (uint64_t)Kc_s, (uint64_t)a->N / 64, (uint64_t)kp.k_shards};
+    uint64_t str[3] = {(uint64_t)a->ldb * 2, 128, sstride};
+    uint32_t box[4] = {64, (uint32_t)BK, 4, 1};
+    rc = encode_tmap(&tB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, a->b, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    kp.b_single = 1;
+  } else if (a->b_mn) {  // stored [Kc, N] per k-shard, N contiguous
     uint64_t dims[3] = {(uint64_t)a->N, (uint64_t)Kc_s, (uint64_t)kp.k_shards};
     uint64_t sstride = kp.k_shards > 1 ? (uint64_t)bss * 2 : (uint64_t)a->ldb * 2 * (uint64_t)Kc_s;
     uint64_t str[2] = {(uint64_t)a->ldb * 2, sstride};
@@ -602,10 +699,30 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
     kp.ag_target = (unsigned)(grid * COPY_WARPS);
     OB_CUDA_OK(cudaMemsetAsync(a->ag_flags, 0, sizeof(unsigned) * (size_t)shards * kp.ag_blocks, stream));
   }
-  if (a->a_mn) {
-    return a->b_mn ? launch<true, true>(tA, tB, tB2, kp, grid, stream) : launch<true, false>(tA, tB, tB2, kp, grid, stream);
+  // Output map for the TMA epilogue (local destinations only; peer destinations keep the direct red.add path).
+  CUtensorMap tC;
+  memset(&tC, 0, sizeof(tC));
+  kp.tma_epi = 0;
+  const bool tma_ok = (a->epi == EPI_BF16 || a->epi == EPI_F32 || a->epi == EPI_F32_ACC) && a->c_shards == nullptr &&
+                      !a->no_tma_epilogue && (kp.m_shards == 1 || a->c_shard_stride > 0);
+  if (tma_ok) {
+    const bool f32 = a->epi != EPI_BF16;
+    const uint64_t es = f32 ? 4 : 2;
+    const bool sharded = a->c_shard_stride > 0;
+    uint64_t dims[3] = {(uint64_t)a->N, (uint64_t)(sharded ? M_s : a->M), (uint64_t)(sharded ? kp.m_shards : 1)};
+    uint64_t str[2] = {(uint64_t)a->ldc * es, sharded ? (uint64_t)a->c_shard_stride * es : (uint64_t)a->ldc * es * (uint64_t)a->M};
+    uint32_t box[3] = {(uint32_t)(f32 ? 32 : 64), (uint32_t)BM, 1};
+    if ((reinterpret_cast<uintptr_t>(a->c) & 15) == 0 && str[0] % 16 == 0 && str[1] % 16 == 0) {
+      rc = encode_tmap(&tC, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a->c, dims, str, box,
+                       CU_TENSOR_MAP_SWIZZLE_128B);
+      if (rc) return rc;
+      kp.tma_epi = 1;
+    }
   }
-  return a->b_mn ? launch<false, true>(tA, tB, tB2, kp, grid, stream) : launch<false, false>(tA, tB, tB2, kp, grid, stream);
+  if (a->a_mn) {
+    return a->b_mn ? launch<true, true>(tA, tB, tB2, tC, kp, grid, stream) : launch<true, false>(tA, tB, tB2, tC, kp, grid, stream);
+  }
+  return a->b_mn ? launch<false, true>(tA, tB, tB2, tC, kp, grid, stream) : launch<false, false>(tA, tB, tB2, tC, kp, grid, stream);
 }
 
 extern "C" const char* ob_last_error() { return ob::last_error_buf(); }

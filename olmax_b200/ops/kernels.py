@@ -111,6 +111,9 @@ def gemm(
     ag_flags: Optional[torch.Tensor] = None,
     ag_rank: int = 0,
     prefetch: Optional[tuple] = None,
+    no_tma_epilogue: bool = False,
+    group_m: int = 0,
+    multi_box_mn: bool = False,
 ) -> None:
     """``C[M, N] (+)= alpha * A[M, K] . B[K, N]``; see ``csrc/gemm.h`` for operand layouts and sharding."""
     _req_bf16(a, b, b2)
@@ -136,6 +139,9 @@ def gemm(
     args.ag_src2 = _ptr(ag_src2)
     args.ag_flags = _ptr(ag_flags)
     args.ag_rank = ag_rank
+    args.no_tma_epilogue = int(no_tma_epilogue)
+    args.group_m = group_m
+    args.multi_box_mn = int(multi_box_mn)
     if prefetch is not None:
         table, dst_ptr, dst_stride, off, nbytes, shards, rank = prefetch
         args.pf_src, args.pf_dst, args.pf_dst_stride = table.data_ptr(), dst_ptr, dst_stride
