@@ -6,7 +6,7 @@
 // with S / dP / dK / dV in the four 128-column quarters of TMEM.  dK and dV stay in TMEM for the whole CTA lifetime
 // (no atomics, GQA heads accumulate in place); the dQ partial is produced in the S columns once S has been consumed
 // and is added to an fp32 scratch tensor with red.global.add, which a small kernel converts to bf16 at the end.
-// P and dS are formed by 128 threads that each own one query row, written as bf16 to one shared 32 KiB buffer in
+// P and dS are formed by 256 threads (two per query row, 64 columns each), written as bf16 to one shared 32 KiB buffer in
 // the 128-byte-swizzled layout the MMAs read (P^T / dS^T as an MN-major A operand, dS as a K-major A operand).
 // Q and dO tiles stream through a 2-stage TMA ring; K and V stay resident in shared memory.
 //
@@ -38,7 +38,7 @@ constexpr int OFF_DO = OFF_Q + STAGES * TILE;      // STAGES tiles
 constexpr int OFF_P = OFF_DO + STAGES * TILE;      // P, later dS
 constexpr int OFF_BAR = OFF_P + TILE;
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;   // TMA warp, MMA warp, 8 compute warps
 constexpr int TMEM_COLS = 512;
 constexpr int C_S = 0, C_DP = 128, C_DK = 256, C_DV = 384;
 
@@ -109,11 +109,11 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(p_ready, 128);
+    mbar_init(p_ready, 256);
     mbar_init(pv_done, 1);
-    mbar_init(ds_ready, 128);
+    mbar_init(ds_ready, 256);
     mbar_init(dq_full, 1);
-    mbar_init(dq_read, 128);
+    mbar_init(dq_read, 256);
     mbar_init(all_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -239,11 +239,18 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
     __syncwarp();
   } else {
+    // ---------------- P / dS / dQ / dK / dV: 8 warps, thread <-> (row, 64-column half) ----------------
+    // Two warps share each TMEM lane quarter and split the 128 columns, so that every scheduler has two compute warps
+    // to hide TMEM-load, MUFU and shared-memory latencies behind each other.
     const int qd = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = qd * 32 + lane;
+    const int col0 = half * 64;
     const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16);
-    uint8_t* sP = smem + OFF_P;
+    uint8_t* sP = smem + OFF_P + half * BLK + row * 128;   // this thread's 128-byte row of key block `half`
+    const int sw = row & 7;
     const float LOG2E = 1.4426950408889634f;
+    const bool capped = p.softcap > 0.f;
     bool ok = true;
     for (int it = 0; it < n_iters && ok; ++it) {
       const uint32_t ph1 = (uint32_t)it & 1u;
@@ -262,94 +269,92 @@ __global__ void __launch_bounds__(THREADS, 1)
       ok = mbar_wait(s_full, ph1, abort_flag, p.status, 900);
       if (!ok) break;
       tc_fence_after_sync();
-      uint32_t pp[64];  // P of this row, bf16x2
-#pragma unroll
-      for (int c = 0; c < T; c += 32) {
-        uint32_t r[32];
-        tmem_ld32(t_lane + C_S + (uint32_t)c, r);
+      uint32_t pp[32];  // P of this half row, bf16x2
+      {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(t_lane + C_S + (uint32_t)col0, r0);
+        tmem_ld32(t_lane + C_S + (uint32_t)(col0 + 32), r1);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float s0 = __uint_as_float(r[i]), s1 = __uint_as_float(r[i + 1]);
-          if (p.softcap > 0.f) {
-            s0 = p.cap_log2 * fast_tanh(s0 * p.scale_over_cap);
-            s1 = p.cap_log2 * fast_tanh(s1 * p.scale_over_cap);
+        for (int i = 0; i < 64; i += 2) {
+          float s0 = __uint_as_float(i < 32 ? r0[i] : r1[i - 32]);
+          float s1 = __uint_as_float(i < 32 ? r0[i + 1] : r1[i - 31]);
+          float e0, e1;
+          if (capped) {
+            e0 = fast_exp2(p.cap_log2 * fast_tanh(s0 * p.scale_over_cap) - lse2);
+            e1 = fast_exp2(p.cap_log2 * fast_tanh(s1 * p.scale_over_cap) - lse2);
           } else {
-            s0 *= p.scale_log2;
-            s1 *= p.scale_log2;
+            e0 = fast_exp2(fmaf(s0, p.scale_log2, -lse2));
+            e1 = fast_exp2(fmaf(s1, p.scale_log2, -lse2));
           }
-          float e0 = fast_exp2(s0 - lse2), e1 = fast_exp2(s1 - lse2);
           if (need_mask) {
-            const int kv = kv0 + c + i;
+            const int kv = kv0 + col0 + i;
             if (kv > kv_hi || kv < kv_lo) e0 = 0.f;
             if (kv + 1 > kv_hi || kv + 1 < kv_lo) e1 = 0.f;
           }
-          pp[(c + i) >> 1] = pack_bf16x2(e0, e1);
-        }
-        // 32 keys = four 16-byte chunks of this row; chunk index within the 128-byte row is XOR-swizzled by row % 8
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int kvc = c + g * 8;  // first key of the chunk
-          const int blk = kvc >> 6, ch = (kvc & 63) >> 3;
-          uint4 v = make_uint4(pp[(kvc >> 1) + 0], pp[(kvc >> 1) + 1], pp[(kvc >> 1) + 2], pp[(kvc >> 1) + 3]);
-          *reinterpret_cast<uint4*>(sP + blk * BLK + row * 128 + ((ch ^ (row & 7)) << 4)) = v;
+          pp[i >> 1] = pack_bf16x2(e0, e1);
         }
       }
+      // eight 16-byte chunks of this row; the chunk index is XOR-swizzled by row % 8 (128-byte swizzle)
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch)
+        *reinterpret_cast<uint4*>(sP + ((ch ^ sw) << 4)) = make_uint4(pp[ch * 4], pp[ch * 4 + 1], pp[ch * 4 + 2], pp[ch * 4 + 3]);
       fence_proxy_async();
       mbar_arrive(p_ready);
 
       ok = mbar_wait(dp_full, ph1, abort_flag, p.status, 901);
       if (!ok) break;
-      ok = mbar_wait(pv_done, ph1, abort_flag, p.status, 902);
-      if (!ok) break;
       tc_fence_after_sync();
-#pragma unroll
-      for (int c = 0; c < T; c += 32) {
-        uint32_t r[32];
-        tmem_ld32(t_lane + C_DP + (uint32_t)c, r);
-        uint32_t sr[32];
-        if (p.softcap > 0.f) tmem_ld32(t_lane + C_S + (uint32_t)c, sr);
+      uint32_t ds[32];
+      {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(t_lane + C_DP + (uint32_t)col0, r0);
+        tmem_ld32(t_lane + C_DP + (uint32_t)(col0 + 32), r1);
         tmem_ld_wait();
-        uint32_t ds[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float2 pv = unpack_bf16x2(pp[(c + i) >> 1]);
-          float d0 = pv.x * (__uint_as_float(r[i]) - dl) * p.scale;
-          float d1 = pv.y * (__uint_as_float(r[i + 1]) - dl) * p.scale;
-          if (p.softcap > 0.f) {
-            const float t0 = fast_tanh(__uint_as_float(sr[i]) * p.scale_over_cap);
-            const float t1 = fast_tanh(__uint_as_float(sr[i + 1]) * p.scale_over_cap);
-            d0 *= (1.f - t0 * t0);
-            d1 *= (1.f - t1 * t1);
-          }
-          ds[i >> 1] = pack_bf16x2(d0, d1);
-        }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int kvc = c + g * 8;
-          const int blk = kvc >> 6, ch = (kvc & 63) >> 3;
-          uint4 v = make_uint4(ds[g * 4 + 0], ds[g * 4 + 1], ds[g * 4 + 2], ds[g * 4 + 3]);
-          *reinterpret_cast<uint4*>(sP + blk * BLK + row * 128 + ((ch ^ (row & 7)) << 4)) = v;
+        for (int i = 0; i < 64; i += 2) {
+          const float2 pv = unpack_bf16x2(pp[i >> 1]);
+          const float g0 = __uint_as_float(i < 32 ? r0[i] : r1[i - 32]);
+          const float g1 = __uint_as_float(i < 32 ? r0[i + 1] : r1[i - 31]);
+          ds[i >> 1] = pack_bf16x2(pv.x * (g0 - dl) * p.scale, pv.y * (g1 - dl) * p.scale);
         }
       }
+      if (capped) {  // dS *= 1 - tanh^2 (S is still intact: dQ overwrites it only after ds_ready)
+        uint32_t r0[32], r1[32];
+        tmem_ld32(t_lane + C_S + (uint32_t)col0, r0);
+        tmem_ld32(t_lane + C_S + (uint32_t)(col0 + 32), r1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 64; i += 2) {
+          const float t0 = fast_tanh(__uint_as_float(i < 32 ? r0[i] : r1[i - 32]) * p.scale_over_cap);
+          const float t1 = fast_tanh(__uint_as_float(i < 32 ? r0[i + 1] : r1[i - 31]) * p.scale_over_cap);
+          const float2 d = unpack_bf16x2(ds[i >> 1]);
+          ds[i >> 1] = pack_bf16x2(d.x * (1.f - t0 * t0), d.y * (1.f - t1 * t1));
+        }
+      }
+      ok = mbar_wait(pv_done, ph1, abort_flag, p.status, 902);   // dV MMA has consumed P: the buffer may hold dS now
+      if (!ok) break;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch)
+        *reinterpret_cast<uint4*>(sP + ((ch ^ sw) << 4)) = make_uint4(ds[ch * 4], ds[ch * 4 + 1], ds[ch * 4 + 2], ds[ch * 4 + 3]);
       fence_proxy_async();
       mbar_arrive(ds_ready);
 
       ok = mbar_wait(dq_full, ph1, abort_flag, p.status, 903);
       if (!ok) break;
       tc_fence_after_sync();
-      float* dq_row = p.dq_accum + (((long long)b * p.S + q_idx) * p.H + h) * HD;
-#pragma unroll 1
-      for (int c = 0; c < HD; c += 32) {
-        uint32_t r[32];
-        tmem_ld32(t_lane + C_S + (uint32_t)c, r);
+      float* dq_row = p.dq_accum + (((long long)b * p.S + q_idx) * p.H + h) * HD + col0;
+      {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(t_lane + C_S + (uint32_t)col0, r0);
+        tmem_ld32(t_lane + C_S + (uint32_t)(col0 + 32), r1);
         tmem_ld_wait();
         if (q_ok) {
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + c + g * 4),
-                         "f"(__uint_as_float(r[g * 4 + 0])), "f"(__uint_as_float(r[g * 4 + 1])),
-                         "f"(__uint_as_float(r[g * 4 + 2])), "f"(__uint_as_float(r[g * 4 + 3]))
+          for (int g = 0; g < 16; ++g) {
+            const uint32_t* r = g < 8 ? &r0[g * 4] : &r1[(g - 8) * 4];
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + g * 4), "f"(__uint_as_float(r[0])),
+                         "f"(__uint_as_float(r[1])), "f"(__uint_as_float(r[2])), "f"(__uint_as_float(r[3]))
                          : "memory");
           }
         }
@@ -357,14 +362,14 @@ __global__ void __launch_bounds__(THREADS, 1)
       tc_fence_before_sync();
       mbar_arrive(dq_read);
     }
-    // dK, dV out (thread <-> key row)
+    // dK, dV out (thread <-> key row, 64-column half)
     const int kv_idx = kv0 + row;
     const bool kv_ok = kv_idx < p.S;
-    bf16* dk_row = p.dk + (long long)b * p.dk_sb + (long long)kv_idx * p.dk_ss + (long long)hkv * p.dk_sh;
-    bf16* dv_row = p.dv + (long long)b * p.dv_sb + (long long)kv_idx * p.dv_ss + (long long)hkv * p.dv_sh;
+    bf16* dk_row = p.dk + (long long)b * p.dk_sb + (long long)kv_idx * p.dk_ss + (long long)hkv * p.dk_sh + col0;
+    bf16* dv_row = p.dv + (long long)b * p.dv_sb + (long long)kv_idx * p.dv_ss + (long long)hkv * p.dv_sh + col0;
     if (n_iters == 0) {
       if (kv_ok) {
-        for (int c = 0; c < HD; c += 8) {
+        for (int c = 0; c < 64; c += 8) {
           *reinterpret_cast<uint4*>(dk_row + c) = make_uint4(0, 0, 0, 0);
           *reinterpret_cast<uint4*>(dv_row + c) = make_uint4(0, 0, 0, 0);
         }
@@ -374,10 +379,10 @@ __global__ void __launch_bounds__(THREADS, 1)
       if (ok) {
         tc_fence_after_sync();
 #pragma unroll 1
-        for (int c = 0; c < HD; c += 32) {
+        for (int c = 0; c < 64; c += 32) {
           uint32_t r[32], r2[32];
-          tmem_ld32(t_lane + C_DK + (uint32_t)c, r);
-          tmem_ld32(t_lane + C_DV + (uint32_t)c, r2);
+          tmem_ld32(t_lane + C_DK + (uint32_t)(col0 + c), r);
+          tmem_ld32(t_lane + C_DV + (uint32_t)(col0 + c), r2);
           tmem_ld_wait();
           if (kv_ok) {
 #pragma unroll

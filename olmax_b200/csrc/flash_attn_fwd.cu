@@ -3,8 +3,8 @@
 // One CTA handles one 128-row query tile of one (batch, head).  S = Q K^T and O += P V run on tcgen05 tensor
 // cores with accumulators in TMEM: S occupies 128 fp32 columns, O another 128; P (bf16) is written back over the
 // S columns and is consumed from TMEM as the A operand of the second MMA, so P never touches shared memory.
-// The softmax is done by 128 threads that each own one query row (TMEM lane == row, so row reductions need no
-// shuffles).  The running maximum is only raised when it grows by more than 2^8 ("lazy rescale"), which keeps the
+// The softmax is done by 256 threads, two per query row (TMEM lane == row; the two column halves exchange their row
+// maximum through shared memory, no shuffles).  The running maximum is only raised when it grows by more than 2^8 ("lazy rescale"), which keeps the
 // O correction (a TMEM read-modify-write) off most iterations.  A CTA uses 256 TMEM columns and ~97 KiB of shared
 // memory so that two CTAs share an SM: while one is in its softmax the other one's MMAs keep the tensor cores busy.
 //
@@ -27,8 +27,8 @@ constexpr int TK = 128;   // keys per iteration
 constexpr int HD = 128;   // head dim
 constexpr int BLK = 128 * 64 * 2;            // one [128 rows][64 elems] swizzled block: 16 KiB
 constexpr int TILE_BYTES = 2 * BLK;          // [128][128] bf16 as two blocks
-constexpr int SMEM_BYTES = 3 * TILE_BYTES + 1024 + 128;
-constexpr int THREADS = 192;
+constexpr int SMEM_BYTES = 3 * TILE_BYTES + 1024 + 128 + 1024;  // + row-statistics exchange [2][128] floats
+constexpr int THREADS = 320;   // TMA warp, MMA warp, 8 softmax warps
 constexpr int TMEM_COLS = 256;
 constexpr int S_COL = 0;      // S (fp32, 128 cols); P (bf16x2, 64 cols) is written over its first 64 columns
 constexpr int O_COL = 128;    // O (fp32, 128 cols)
@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(THREADS, 2)
   uint64_t* o_done = bars + 7;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* xch = reinterpret_cast<float*>(bars + 16);   // [2][128] exchange between the two column halves of a row
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -100,7 +101,7 @@ __global__ void __launch_bounds__(THREADS, 2)
     mbar_init(v_full, 1);
     mbar_init(v_empty, 1);
     mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 256);
     mbar_init(o_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -178,13 +179,19 @@ __global__ void __launch_bounds__(THREADS, 2)
     }
     __syncwarp();
   } else {
-    // ---------------- softmax + output: thread <-> query row ----------------
+    // ---------------- softmax + output: 8 warps, thread <-> (query row, 64-column half) ----------------
+    // Two warps share each TMEM lane quarter and split the 128 score columns; the halves exchange their row maxima
+    // through shared memory once per tile.  With two CTAs per SM every scheduler then has four softmax warps to hide
+    // TMEM and MUFU latency.
     const int qd = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = qd * 32 + lane;
+    const int col0 = half * 64;
     const int q_idx = q0 + row;
     const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16);
-    float m_run = -INFINITY;  // running max, log2 domain
-    float l_run = 0.f;
+    const bool capped = p.softcap > 0.f;
+    float m_run = -INFINITY;  // running max, log2 domain (identical in both halves of a row)
+    float l_run = 0.f;        // this half's share of the running sum
     bool ok = true;
     for (int j = 0; j < n_iters && ok; ++j) {
       const uint32_t ph = (uint32_t)j & 1u;
@@ -196,94 +203,88 @@ __global__ void __launch_bounds__(THREADS, 2)
                              (p.window >= 0 && kv0 < q0 + TQ - 1 - p.window);
       const int kv_hi = p.causal ? min(q_idx, p.S - 1) : p.S - 1;  // last visible key
       const int kv_lo = p.window >= 0 ? q_idx - p.window : 0;      // first visible key
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < TK; c += 32) {
-        uint32_t r[32];
-        tmem_ld32(t_lane + S_COL + (uint32_t)c, r);
-        tmem_ld_wait();
+      // this thread's 64 scores, kept in registers for both the max and the exponentials
+      uint32_t r0[32], r1[32];
+      tmem_ld32(t_lane + S_COL + (uint32_t)col0, r0);
+      tmem_ld32(t_lane + S_COL + (uint32_t)(col0 + 32), r1);
+      tmem_ld_wait();
+      if (capped) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(r[i]);
-          s = (p.softcap > 0.f) ? p.cap_log2 * fast_tanh(s * p.scale_over_cap) : s * p.scale_log2;
-          if (need_mask) {
-            const int kv = kv0 + c + i;
-            if (kv > kv_hi || kv < kv_lo) s = -INFINITY;
-          }
-          mx = fmaxf(mx, s);
+          r0[i] = __float_as_uint(p.cap_log2 * fast_tanh(__uint_as_float(r0[i]) * p.scale_over_cap));
+          r1[i] = __float_as_uint(p.cap_log2 * fast_tanh(__uint_as_float(r1[i]) * p.scale_over_cap));
         }
       }
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kv = kv0 + col0 + i;
+          if (kv > kv_hi || kv < kv_lo) r0[i] = __float_as_uint(-INFINITY);
+          if (kv + 32 > kv_hi || kv + 32 < kv_lo) r1[i] = __float_as_uint(-INFINITY);
+        }
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(r0[i]), __uint_as_float(r1[i])));
+      const float sc = capped ? 1.0f : p.scale_log2;   // soft-capped scores are already in the log2 domain
+      mx *= sc;                                        // sc > 0: max commutes with the scaling
+      xch[half * 128 + row] = mx;
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      const float m_new = fmaxf(m_run, fmaxf(mx, xch[(half ^ 1) * 128 + row]));
       // lazy rescale: raise the running max only when it grows by more than 8 (factor 256); warp-uniform decision
-      const float m_new = fmaxf(m_run, mx);
       const bool want = (m_new > m_run + 8.0f) || (m_run == -INFINITY && m_new > -INFINITY);
       if (__any_sync(0xffffffffu, want)) {
         const float m_next = want ? m_new : m_run;
         const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_next);
         if (j > 0) {
 #pragma unroll 1
-          for (int c = 0; c < HD; c += 32) {
-            uint32_t r[32];
-            tmem_ld32(t_lane + O_COL + (uint32_t)c, r);
+          for (int c = 0; c < 64; c += 16) {
+            uint32_t o[16];
+            tmem_ld16(t_lane + O_COL + (uint32_t)(col0 + c), o);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(t_lane + O_COL + (uint32_t)c, r);
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st16(t_lane + O_COL + (uint32_t)(col0 + c), o);
           }
           tmem_st_wait();
         }
         l_run *= alpha;
         m_run = m_next;
       }
-      const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-      // pass 2: P = exp2(s - m), row sum, bf16 pack, store over the S columns already consumed
+      const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
+      // P = exp2(s - m) as bf16 pairs, written over the S columns (both halves hold their scores in registers by now)
       float lsum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < TK; c += 32) {
-        uint32_t r[32];
-        tmem_ld32(t_lane + S_COL + (uint32_t)c, r);
-        tmem_ld_wait();
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float s0 = __uint_as_float(r[i]), s1 = __uint_as_float(r[i + 1]);
-          if (p.softcap > 0.f) {
-            s0 = p.cap_log2 * fast_tanh(s0 * p.scale_over_cap);
-            s1 = p.cap_log2 * fast_tanh(s1 * p.scale_over_cap);
-          } else {
-            s0 *= p.scale_log2;
-            s1 *= p.scale_log2;
-          }
-          float e0 = fast_exp2(s0 - m_use), e1 = fast_exp2(s1 - m_use);
-          if (need_mask) {
-            const int kv = kv0 + c + i;
-            if (kv > kv_hi || kv < kv_lo) e0 = 0.f;
-            if (kv + 1 > kv_hi || kv + 1 < kv_lo) e1 = 0.f;
-          }
-          // accumulate the sum from the bf16-rounded values the MMA will actually use
-          const uint32_t packed = pack_bf16x2(e0, e1);
-          const float2 back = unpack_bf16x2(packed);
-          lsum += back.x + back.y;
-          pk[i >> 1] = packed;
+          const float s0 = __uint_as_float(hh ? r1[i] : r0[i]), s1 = __uint_as_float(hh ? r1[i + 1] : r0[i + 1]);
+          const float e0 = fast_exp2(fmaf(s0, sc, neg_m)), e1 = fast_exp2(fmaf(s1, sc, neg_m));
+          lsum += e0 + e1;
+          pk[i >> 1] = pack_bf16x2(e0, e1);
         }
-        tmem_st16(t_lane + S_COL + (uint32_t)(c >> 1), pk);
+        tmem_st16(t_lane + S_COL + (uint32_t)(half * 32 + hh * 16), pk);
       }
       l_run += lsum;
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(p_full);
     }
-    // epilogue: wait for the last P V, normalise, store
+    // epilogue: wait for the last P V, combine the halves' sums, normalise, store
     if (ok) ok = mbar_wait(o_done, (uint32_t)(n_iters - 1) & 1u, abort_flag, p.status, 601);
+    xch[half * 128 + row] = l_run;
+    asm volatile("bar.sync 2, 256;" ::: "memory");
     if (ok) {
       tc_fence_after_sync();
-      const float inv_l = l_run > 0.f ? 1.0f / l_run : 0.f;
+      const float l_tot = l_run + xch[(half ^ 1) * 128 + row];
+      const float inv_l = l_tot > 0.f ? 1.0f / l_tot : 0.f;
       const bool row_ok = q_idx < p.S;
-      bf16* orow = p.o + (long long)b * p.o_sb + (long long)q_idx * p.o_ss + (long long)h * p.o_sh;
+      bf16* orow = p.o + (long long)b * p.o_sb + (long long)q_idx * p.o_ss + (long long)h * p.o_sh + col0;
 #pragma unroll 1
-      for (int c = 0; c < HD; c += 32) {
+      for (int c = 0; c < 64; c += 32) {
         uint32_t r[32];
-        tmem_ld32(t_lane + O_COL + (uint32_t)c, r);
+        tmem_ld32(t_lane + O_COL + (uint32_t)(col0 + c), r);
         tmem_ld_wait();
         if (row_ok) {
 #pragma unroll
@@ -297,8 +298,8 @@ __global__ void __launch_bounds__(THREADS, 2)
           }
         }
       }
-      if (row_ok) {
-        const float lse = l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+      if (row_ok && half == 0) {
+        const float lse = l_tot > 0.f ? (m_run + log2f(l_tot)) * 0.6931471805599453f : -INFINITY;
         p.lse[((long long)b * p.H + h) * p.S + q_idx] = lse;
       }
     }
