@@ -388,19 +388,19 @@ class Trainer:
                 gc.collect()
             for cb in self._iter_callbacks():
                 cb.post_step()
-            # next batch (counts as data-loading time)
+            now = time.perf_counter()
+            self._record_throughput(now - last_time, batch)
+            last_time = now
+            # checkpoint BEFORE the next batch is drawn, so that the saved data-loader state points at it
+            if self.checkpoint_interval is not None and self._step % self.checkpoint_interval == 0:
+                self._save_checkpoint(block=not self.async_checkpointing)
             t_load = time.perf_counter()
             with _nvtx("load_batch"):
                 try:
                     nxt = next(batches)
                 except StopIteration:
                     nxt = None
-            self.record_metric("throughput/data loading time (s)", time.perf_counter() - t_load)
-            now = time.perf_counter()
-            self._record_throughput(now - last_time, batch)
-            last_time = now
-            if self.checkpoint_interval is not None and self._step % self.checkpoint_interval == 0:
-                self._save_checkpoint(block=not self.async_checkpointing)
+            self.record_metric("throughput/data loading time (s)", time.perf_counter() - t_load, step=self._step)
             batch = nxt
         for cb in self._iter_callbacks():
             cb.post_epoch()
