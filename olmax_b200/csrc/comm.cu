@@ -1,0 +1,90 @@
+// All-reduce kernels over NVLink peer memory for the once-per-step gradient all-reduce of HSDP / DDP
+// (the reference issues an NCCL all-reduce after EVERY micro-batch, `README.md:30` of the reference).
+//
+// Both kernels are two-shot and contain no waits: rank i reduces slice i of the buffer over all members and writes
+// the result back to every member.  The caller brackets the launch with stream-ordered barriers (all members have
+// finished producing their buffers / all slices have been written), so a missing peer can never hang a kernel.
+//   * ob_allreduce_p2p_f32:      plain vector loads from / stores to the members' buffers (any group of GPUs);
+//   * ob_allreduce_multimem_f32: NVSwitch in-network reduction, multimem.ld_reduce + multimem.st on a multicast address
+//                                that maps the same buffer on every member.
+#include "comm.h"
+#include "host_common.h"
+
+namespace ob {
+
+constexpr int AR_THREADS = 512;
+
+__global__ void __launch_bounds__(AR_THREADS)
+    allreduce_p2p_kernel(float* const* __restrict__ bufs, long long n, int me, int world, float scale) {
+  // slice of this rank, in float4 units
+  const long long n4 = n / 4;
+  const long long per = (n4 + world - 1) / world;
+  const long long lo = per * me, hi = min(n4, lo + per);
+  for (long long i = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < hi; i += (long long)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < world; ++r) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(bufs[(me + r) % world]) + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+    for (int r = 0; r < world; ++r) reinterpret_cast<float4*>(bufs[(me + r) % world])[i] = acc;
+  }
+  // tail elements (n not a multiple of 4) are handled by rank 0
+  if (me == 0 && blockIdx.x == 0) {
+    for (long long i = n4 * 4 + threadIdx.x; i < n; i += blockDim.x) {
+      float acc = 0.f;
+      for (int r = 0; r < world; ++r) acc += bufs[r][i];
+      acc *= scale;
+      for (int r = 0; r < world; ++r) bufs[r][i] = acc;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(AR_THREADS)
+    allreduce_multimem_kernel(float* mc, long long n, int me, int world) {
+  const long long n4 = n / 4;   // the caller pads n to a multiple of 4
+  const long long per = (n4 + world - 1) / world;
+  const long long lo = per * me, hi = min(n4, lo + per);
+  for (long long i = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < hi; i += (long long)gridDim.x * blockDim.x) {
+    float* addr = mc + i * 4;
+    float x, y, z, w;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(x), "=f"(y), "=f"(z), "=f"(w)
+                 : "l"(addr)
+                 : "memory");
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(x), "f"(y), "f"(z), "f"(w)
+                 : "memory");
+  }
+}
+
+}  // namespace ob
+
+using namespace ob;
+
+extern "C" int ob_allreduce_p2p_f32(float* const* bufs, long long n, int me, int world, float scale, int max_blocks,
+                                    cudaStream_t stream) {
+  if (n <= 0 || world <= 1) return 0;
+  if (me < 0 || me >= world) OB_FAIL(-1, "allreduce: rank %d outside [0, %d)", me, world);
+  const long long per = ((n / 4) + world - 1) / world;
+  long long blocks = (per + AR_THREADS - 1) / AR_THREADS;
+  const long long cap = max_blocks > 0 ? max_blocks : 2LL * sm_count();
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  allreduce_p2p_kernel<<<(unsigned)blocks, AR_THREADS, 0, stream>>>(bufs, n, me, world, scale);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_allreduce_multimem_f32(float* mc, long long n, int me, int world, int max_blocks, cudaStream_t stream) {
+  if (n <= 0 || world <= 1) return 0;
+  if (mc == nullptr) OB_FAIL(-2, "allreduce: no multicast address");
+  if (n % 4 != 0 || (reinterpret_cast<uintptr_t>(mc) & 15)) OB_FAIL(-3, "allreduce: need n %% 4 == 0 and 16-byte alignment");
+  const long long per = ((n / 4) + world - 1) / world;
+  long long blocks = (per + AR_THREADS - 1) / AR_THREADS;
+  const long long cap = max_blocks > 0 ? max_blocks : 2LL * sm_count();
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  allreduce_multimem_kernel<<<(unsigned)blocks, AR_THREADS, 0, stream>>>(mc, n, me, world);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}

@@ -1,0 +1,19 @@
+// C interface of the peer-memory all-reduce kernels (comm.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// In-place sum (times `scale`) of an fp32 buffer over `world` GPUs.  bufs: DEVICE array of the members' buffer
+// addresses (peer-mapped), me: this GPU's index in that array.  The caller must barrier the members before (buffers
+// complete) and after (results visible) the launch; the kernel itself never waits.
+int ob_allreduce_p2p_f32(float* const* bufs, long long n, int me, int world, float scale, int max_blocks,
+                         cudaStream_t stream);
+// Same through an NVLS multicast address `mc` (multimem.ld_reduce / multimem.st); n must be a multiple of 4.
+int ob_allreduce_multimem_f32(float* mc, long long n, int me, int world, int max_blocks, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

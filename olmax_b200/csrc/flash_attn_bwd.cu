@@ -5,7 +5,8 @@
 //     S  = Q K^T          dP = dO V^T          dV += P^T dO          dK += dS^T Q          dQ_part = dS K
 // with S / dP / dK / dV in the four 128-column quarters of TMEM.  dK and dV stay in TMEM for the whole CTA lifetime
 // (no atomics, GQA heads accumulate in place); the dQ partial is produced in the S columns once S has been consumed
-// and is added to an fp32 scratch tensor with red.global.add, which a small kernel converts to bf16 at the end.
+// and is added to an fp32 scratch tensor with a TMA reduce-add from shared memory (staged in the Q / dO buffers of the
+// iteration, which are idle by then), which a small kernel converts to bf16 at the end.
 // P and dS are formed by 256 threads (two per query row, 64 columns each), written as bf16 to one shared 32 KiB buffer in
 // the 128-byte-swizzled layout the MMAs read (P^T / dS^T as an MN-major A operand, dS as a K-major A operand).
 // Q and dO tiles stream through a 2-stage TMA ring; K and V stay resident in shared memory.
@@ -38,7 +39,7 @@ constexpr int OFF_DO = OFF_Q + STAGES * TILE;      // STAGES tiles
 constexpr int OFF_P = OFF_DO + STAGES * TILE;      // P, later dS
 constexpr int OFF_BAR = OFF_P + TILE;
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
-constexpr int THREADS = 320;   // TMA warp, MMA warp, 8 compute warps
+constexpr int THREADS = 352;   // TMA warp, MMA warp, 8 compute warps, dQ store warp
 constexpr int TMEM_COLS = 512;
 constexpr int C_S = 0, C_DP = 128, C_DK = 256, C_DV = 384;
 
@@ -68,7 +69,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 __global__ void __launch_bounds__(THREADS, 1)
     flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
-                     const Params p) {
+                     const __grid_constant__ CUtensorMap tmDQ, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
@@ -83,7 +84,8 @@ __global__ void __launch_bounds__(THREADS, 1)
   uint64_t* dq_full = bars + 10;
   uint64_t* dq_read = bars + 11;   // 128 arrivals
   uint64_t* all_done = bars + 12;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* dq_staged = bars + 13; // 256 arrivals: the fp32 dQ partial tile is in shared memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -115,6 +117,7 @@ __global__ void __launch_bounds__(THREADS, 1)
     mbar_init(dq_full, 1);
     mbar_init(dq_read, 256);
     mbar_init(all_done, 1);
+    mbar_init(dq_staged, 256);
     *abort_flag = 0;
     mbar_fence_init();
     fence_proxy_async();
@@ -218,8 +221,7 @@ __global__ void __launch_bounds__(THREADS, 1)
           umma_ss(tmem_base + C_S, make_smem_desc(aP + off, 0, 1024),
                   make_smem_desc(aK + (uint32_t)kk * 2048, BLK, 1024), id_km, kk != 0 ? 1u : 0u);
         }
-        umma_commit(dq_full);
-        umma_commit(&empty[s]);
+        umma_commit(dq_full);   // also tells the compute warps that every MMA reading stage s has finished
         if (it + 1 < n_iters) {
           const int s2 = (it + 1) % STAGES;
           const uint32_t ph2 = (uint32_t)((it + 1) / STAGES) & 1u;
@@ -236,6 +238,29 @@ __global__ void __launch_bounds__(THREADS, 1)
         }
       }
       if (ok) umma_commit(all_done);
+    }
+    __syncwarp();
+  } else if (warp == 10) {
+    // ---------------- dQ store warp: fp32 partial tile (in the Q / dO stage) += into global memory ----------------
+    if (lane == 0 && n_iters > 0) {
+      bool ok = true;
+      for (int it = 0; it < n_iters && ok; ++it) {
+        const int s = it % STAGES;
+        const int h = hkv * G + it / n_q;
+        const int q0 = (i_lo + it % n_q) * T;
+        ok = mbar_wait(dq_staged, (uint32_t)it & 1u, abort_flag, p.status, 950);
+        if (!ok) break;
+        // columns [0, 64) sit in the Q stage, [64, 128) in the dO stage, 32 columns (128 bytes) per chunk
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          const uint8_t* src = smem + (cc < 2 ? OFF_Q : OFF_DO) + s * TILE + (cc & 1) * 16384;
+          tma_reduce_add_4d(&tmDQ, src, cc * 32, h, q0, b);
+        }
+        tma_store_commit();
+        tma_store_wait_read<0>();      // the stage has been read: hand it back to the TMA producer
+        mbar_arrive(&empty[s]);
+      }
+      tma_store_wait<0>();
     }
     __syncwarp();
   } else {
@@ -343,24 +368,28 @@ __global__ void __launch_bounds__(THREADS, 1)
       ok = mbar_wait(dq_full, ph1, abort_flag, p.status, 903);
       if (!ok) break;
       tc_fence_after_sync();
-      float* dq_row = p.dq_accum + (((long long)b * p.S + q_idx) * p.H + h) * HD + col0;
+      // dQ partial: TMEM -> registers -> the (now idle) Q/dO stage as an fp32 [128 x 128] tile made of four
+      // [128 rows][128 B] swizzled chunks; the store warp adds it to global memory with TMA reduce-add.
       {
         uint32_t r0[32], r1[32];
         tmem_ld32(t_lane + C_S + (uint32_t)col0, r0);
         tmem_ld32(t_lane + C_S + (uint32_t)(col0 + 32), r1);
         tmem_ld_wait();
-        if (q_ok) {
+        tc_fence_before_sync();
+        mbar_arrive(dq_read);   // the S / dQ columns may be overwritten by the next S = Q K^T
+        // columns [0, 64) go to this iteration's Q stage, [64, 128) to its dO stage (both idle since dq_full)
+        uint8_t* c0p = (half == 0 ? smem + OFF_Q : smem + OFF_DO) + (it % STAGES) * TILE;
 #pragma unroll
-          for (int g = 0; g < 16; ++g) {
-            const uint32_t* r = g < 8 ? &r0[g * 4] : &r1[(g - 8) * 4];
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + g * 4), "f"(__uint_as_float(r[0])),
-                         "f"(__uint_as_float(r[1])), "f"(__uint_as_float(r[2])), "f"(__uint_as_float(r[3]))
-                         : "memory");
-          }
+        for (int cc = 0; cc < 2; ++cc) {
+          uint8_t* crow = c0p + cc * 16384 + row * 128;
+          const uint32_t* r = cc ? r1 : r0;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(crow + ((j ^ sw) << 4)) = make_uint4(r[j * 4], r[j * 4 + 1], r[j * 4 + 2], r[j * 4 + 3]);
         }
+        fence_proxy_async();
+        mbar_arrive(dq_staged);
       }
-      tc_fence_before_sync();
-      mbar_arrive(dq_read);
     }
     // dK, dV out (thread <-> key row, 64-column half)
     const int kv_idx = kv0 + row;
@@ -448,6 +477,14 @@ __global__ void attn_dq_convert_kernel(const float* __restrict__ acc, bf16* __re
   *reinterpret_cast<uint2*>(dq + b * sb + s * ss + h * sh + lane * 4) = o;
 }
 
+// fp32 dQ accumulator [B, S, H, 128] contiguous -> 4-D map (d, h, s, b), box 32 x 1 x 128 x 1 (128-byte rows)
+static int encode_dq_map(CUtensorMap* m, float* acc, int B, int S, int H) {
+  uint64_t dims[4] = {128, (uint64_t)H, (uint64_t)S, (uint64_t)B};
+  uint64_t str[3] = {128 * 4, (uint64_t)H * 128 * 4, (uint64_t)S * H * 128 * 4};
+  uint32_t box[4] = {32, 1, 128, 1};
+  return encode_tmap(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, acc, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
 }  // namespace fa_bwd
 }  // namespace ob
 
@@ -496,7 +533,9 @@ extern "C" int ob_flash_attn_bwd(const ObAttnArgs* a, cudaStream_t stream) {
     attr_set = true;
   }
   dim3 grid((a->S + 127) / 128, a->Hkv, a->B);
-  fa_bwd::flash_bwd_kernel<<<grid, fa_bwd::THREADS, fa_bwd::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+  CUtensorMap tdq;
+  if ((rc = fa_bwd::encode_dq_map(&tdq, a->dq_accum, a->B, a->S, a->H))) return rc;
+  fa_bwd::flash_bwd_kernel<<<grid, fa_bwd::THREADS, fa_bwd::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdq, p);
   OB_CUDA_OK(cudaGetLastError());
   fa_bwd::attn_dq_convert_kernel<<<nblk, wpb * 32, 0, stream>>>(a->dq_accum, reinterpret_cast<bf16*>(a->dq), a->dq_sb,
                                                                a->dq_ss, a->dq_sh, a->B, a->S, a->H);
@@ -593,7 +632,9 @@ extern "C" int ob_flash_attn_bwd_static(const ObAttnArgs* a, cudaStream_t stream
     attr_set = true;
   }
   dim3 grid((a->S + 127) / 128, a->Hkv, a->B);
-  fa_bwd::flash_bwd_kernel<<<grid, fa_bwd::THREADS, fa_bwd::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+  CUtensorMap tdq;
+  if ((rc = fa_bwd::encode_dq_map(&tdq, dq_accum, a->B, a->S, a->H))) return rc;
+  fa_bwd::flash_bwd_kernel<<<grid, fa_bwd::THREADS, fa_bwd::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdq, p);
   OB_CUDA_OK(cudaGetLastError());
   fa_bwd::attn_dq_convert_kernel<<<nblk, wpb * 32, 0, stream>>>(dq_accum, reinterpret_cast<bf16*>(a->dq), a->dq_sb,
                                                                a->dq_ss, a->dq_sh, a->B, a->S, a->H);

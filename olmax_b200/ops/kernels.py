@@ -64,6 +64,8 @@ register_signature("ob_clip_coef", [_vp, _f, _f, _vp, _vp])
 register_signature("ob_cast_f32_bf16", [_vp, _vp, _ll, _vp])
 register_signature("ob_gather_shards", [_vp, _vp, _ll, _ll, _i, _i, _vp])
 register_signature("ob_scatter_add_shards", [_vp, _vp, _ll, _i, _f, _vp])
+register_signature("ob_allreduce_p2p_f32", [_vp, _ll, _i, _i, _f, _i, _vp])
+register_signature("ob_allreduce_multimem_f32", [_vp, _ll, _i, _i, _i, _vp])
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -314,4 +316,17 @@ def scatter_add_shards(src, table, n_per_shard, n_shards, scale=1.0) -> None:
     """shard_r[i] += scale * src[r * n_per_shard + i] (fp32 red.add; shards may live on peer GPUs)."""
     check(lib().ob_scatter_add_shards(src.data_ptr(), table.data_ptr(), n_per_shard, n_shards, scale,
                                       stream_ptr(src.device)), "scatter_add_shards")
+    _count()
+
+
+def allreduce_p2p(table, n, me, world, scale=1.0, max_blocks=0) -> None:
+    """In-place sum of an fp32 buffer over the GPUs whose buffer addresses are in ``table`` (device pointer array)."""
+    check(lib().ob_allreduce_p2p_f32(table.data_ptr(), n, me, world, scale, max_blocks, stream_ptr(table.device)),
+          "allreduce_p2p")
+    _count()
+
+
+def allreduce_multimem(mc_ptr: int, n, me, world, max_blocks=0, device=None) -> None:
+    """In-place sum through an NVLS multicast address (multimem.ld_reduce / multimem.st)."""
+    check(lib().ob_allreduce_multimem_f32(mc_ptr, n, me, world, max_blocks, stream_ptr(device)), "allreduce_multimem")
     _count()

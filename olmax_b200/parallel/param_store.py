@@ -363,7 +363,8 @@ class ParamStore:
         dev = self.device
         self.master = torch.zeros(off, dtype=self.param_dtype, device=dev)
         use_symm = False
-        if self.comm_backend in ("auto", "fused") and self.mesh.shard.size > 1 and self.compute_dtype != self.param_dtype:
+        if (self.comm_backend in ("auto", "fused") and self.compute_dtype != self.param_dtype
+                and (self.mesh.shard.size > 1 or self.mesh.replicate.size > 1) and self.mesh.tp.size == 1):
             from .symm import SymmContext, symm_available
 
             use_symm = symm_available(dev)
@@ -374,8 +375,9 @@ class ParamStore:
             self.grad = self.symm.grad
             self.shadow = self.symm.shadow
             # experiment knobs: fall back to the NCCL collective for one direction while keeping the other fused
-            self.symm_ag = self.symm if os.environ.get("OLMAX_B200_FUSED_AG", "1") == "1" else None
-            self.symm_rs = self.symm if os.environ.get("OLMAX_B200_FUSED_RS", "1") == "1" else None
+            sharded = self.mesh.shard.size > 1
+            self.symm_ag = self.symm if (sharded and os.environ.get("OLMAX_B200_FUSED_AG", "1") == "1") else None
+            self.symm_rs = self.symm if (sharded and os.environ.get("OLMAX_B200_FUSED_RS", "1") == "1") else None
         else:
             self.grad = torch.zeros(off, dtype=torch.float32, device=dev)
             if self.compute_dtype == self.param_dtype:
@@ -527,7 +529,10 @@ class ParamStore:
         """
         self.sync_peers()
         rep = self.mesh.replicate
-        if rep.size > 1:
+        if rep.size > 1 and self.symm is not None and os.environ.get("OLMAX_B200_FUSED_AR", "1") == "1":
+            self.stats["all_reduce_bytes"] += self.symm.all_reduce_replicas()
+            self.sync_peers()
+        elif rep.size > 1:
             coll.all_reduce(self.grad, rep)
             self.stats["all_reduce_bytes"] += 2 * (rep.size - 1) * self.grad.numel() * 4 // rep.size
         tp = self.mesh.tp

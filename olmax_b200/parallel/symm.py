@@ -1,27 +1,31 @@
 """
-Peer-memory ("fused") communication backend for the FSDP shard group.
+Peer-memory ("fused") communication backend.
 
 The bf16 compute copy of the parameters and the fp32 gradient accumulator are allocated in symmetric memory
-(``torch.distributed._symmetric_memory``: every rank of the group maps every other rank's buffer over NVLink), which
-lets our kernels fuse the FSDP collectives into the GEMMs instead of calling NCCL:
+(``torch.distributed._symmetric_memory``: every rank of the job maps every other rank's buffer over NVLink), which
+lets our kernels fuse the collectives into the compute instead of calling NCCL:
 
-* **all-gather -> GEMM**: a weight is never gathered by a separate collective.  The first GEMM that needs it gets a
-  table of the peers' shard addresses; its copy warps stream the remote shards into the local staging buffer while
-  its tensor-core warps already work on the local shard, and tiles of a remote shard wait on per-block arrival
-  counters (``csrc/gemm.cu``).  The embedding gather reads rows straight from the owner GPU.
+* **all-gather -> GEMM**: a weight is never gathered by a separate collective.  Every GEMM launch carries, in its copy
+  warps, a slice of the NEXT FSDP unit's remote shards (so the transfer of layer i+1 runs under the math of layer i);
+  whatever a weight still misses when its own GEMM starts is fetched by that GEMM itself, whose tiles then wait on
+  per-block arrival counters (``csrc/gemm.cu``).  The embedding gather reads rows straight from the owner GPU.
 * **GEMM -> reduce-scatter**: the weight-gradient GEMM's epilogue adds each row block into the owner GPU's fp32
   accumulator with ``red.global.add`` (scaled by 1 / (ranks x micro-batches)), so there is no reduce-scatter at all.
+* **HSDP / DDP all-reduce**: once per optimizer step a two-shot kernel sums the fp32 accumulator over the replicas
+  (plain peer loads / stores, or ``multimem.ld_reduce`` + ``multimem.st`` through NVSwitch when the group is the whole
+  job and a multicast mapping exists).
 
-Only plain loads / stores / reductions touch peer memory; TMA descriptors always point at local memory.  Two
-stream-ordered barriers per optimizer step (before it: every peer's reductions have landed and nobody still reads
-our weights; after it: every peer's new weights are visible and its accumulator is cleared) are the only
-synchronisation between ranks.
+Only plain loads / stores / reductions and multimem instructions touch peer memory; TMA descriptors always point at
+local memory.  Stream-ordered barriers separate the phases (before the optimizer step: every peer's reductions have
+landed and nobody still reads our weights; after it: every peer's new weights are visible and its accumulator is
+cleared); the kernels themselves never wait on a peer except for the bounded arrival-counter wait inside one GEMM.
 """
 
 from __future__ import annotations
 
 import logging
-from typing import Dict, List, Optional
+import os
+from typing import Dict, List
 
 import torch
 import torch.distributed as dist
@@ -48,25 +52,34 @@ class SymmContext:
         import torch.distributed._symmetric_memory as symm_mem
 
         self.store = store
-        group = store.mesh.shard
-        self.group = group
-        self.R = group.size
-        self.rank = group.rank
+        mesh = store.mesh
         dev = store.device
         self.shadow = symm_mem.empty(numel, dtype=store.compute_dtype, device=dev)
         self.grad = symm_mem.empty(numel, dtype=torch.float32, device=dev)
         self.shadow.zero_()
         self.grad.zero_()
-        self._h_shadow = symm_mem.rendezvous(self.shadow, group.pg)
-        self._h_grad = symm_mem.rendezvous(self.grad, group.pg)
-        self.shadow_ptrs: List[int] = [int(p) for p in self._h_shadow.buffer_ptrs]
-        self.grad_ptrs: List[int] = [int(p) for p in self._h_grad.buffer_ptrs]
-        self.flags = torch.zeros(self.R * 4096, dtype=torch.int32, device=dev)
+        world = dist.group.WORLD
+        self._h_shadow = symm_mem.rendezvous(self.shadow, world)
+        self._h_grad = symm_mem.rendezvous(self.grad, world)
+        all_shadow = [int(p) for p in self._h_shadow.buffer_ptrs]
+        all_grad = [int(p) for p in self._h_grad.buffer_ptrs]
+        # the shard group's view (index = rank inside the shard group)
+        self.R = mesh.shard.size
+        self.rank = mesh.shard.rank
+        self.shadow_ptrs: List[int] = [all_shadow[r] for r in mesh.shard.ranks]
+        self.grad_ptrs: List[int] = [all_grad[r] for r in mesh.shard.ranks]
+        # the replicate group's view, for the once-per-step gradient all-reduce
+        self.replica_grad_table = K.pointer_table([all_grad[r] for r in mesh.replicate.ranks], dev)
+        mc = int(getattr(self._h_grad, "multicast_ptr", 0) or 0)
+        use_mc = os.environ.get("OLMAX_B200_MULTIMEM", "1") == "1"
+        self.multicast_ptr = mc if (use_mc and mesh.replicate.size == mesh.world_size) else 0
+        self.flags = torch.zeros(max(1, self.R) * 4096, dtype=torch.int32, device=dev)
         self._tables: Dict[tuple, torch.Tensor] = {}
         self._token = torch.zeros(1, dtype=torch.float32, device=dev)
-        self.multicast_ptr = int(getattr(self._h_grad, "multicast_ptr", 0) or 0)
-        log.info("Peer-memory backend on: %d ranks, %.1f MiB bf16 weights + %.1f MiB fp32 gradients mapped per rank",
-                 self.R, numel * 2 / 2**20, numel * 4 / 2**20)
+        self._sync_group = world if mesh.replicate.size > 1 else mesh.shard.pg
+        log.info("Peer-memory backend on: shard group %d, replicate group %d, %.1f MiB bf16 weights + %.1f MiB fp32 "
+                 "gradients mapped per rank%s", self.R, mesh.replicate.size, numel * 2 / 2**20, numel * 4 / 2**20,
+                 ", NVLS multicast" if self.multicast_ptr else "")
 
     def _table(self, kind: str, handle, base_ptrs: List[int], elem_size: int) -> torch.Tensor:
         key = (kind, handle.name)
@@ -95,5 +108,16 @@ class SymmContext:
         return t
 
     def sync_peers(self) -> None:
-        """Stream-ordered barrier over the shard group (a one-element NCCL all-reduce)."""
-        dist.all_reduce(self._token, group=self.group.pg)
+        """Stream-ordered barrier (a one-element NCCL all-reduce) over every rank that shares memory with this one."""
+        dist.all_reduce(self._token, group=self._sync_group)
+
+    def all_reduce_replicas(self) -> int:
+        """Sum the fp32 gradient accumulator over the replicate group with our peer-memory kernel; returns the bytes
+        this rank moved over NVLink.  Barriers before and after are the caller's (``sync_peers``)."""
+        rep = self.store.mesh.replicate
+        n = self.grad.numel()
+        if self.multicast_ptr and n % 4 == 0:
+            K.allreduce_multimem(self.multicast_ptr, n, rep.rank, rep.size)
+        else:
+            K.allreduce_p2p(self.replica_grad_table, n, rep.rank, rep.size)
+        return 2 * (rep.size - 1) * n * 4 // rep.size

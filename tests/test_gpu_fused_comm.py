@@ -98,7 +98,7 @@ def test_small_shard_helpers():
     _check()
 
 
-def _train_worker(backend):
+def _train_worker(backend, mesh_kind="fsdp"):
     import torch.distributed as dist
 
     from olmax_b200.models import DefaultTransformerConfig, ReorderedNormTransformerLayerConfig
@@ -112,7 +112,9 @@ def _train_worker(backend):
     attn = MultiheadSelfAttentionConfig(n_heads=4, head_dim=128, qk_norm=RMSNormConfig(), use_head_qk_norm=False)
     cfg = DefaultTransformerConfig(vocab_size=4096, d_model=512, hidden_size=1408, num_layers=2,
                                    layer=ReorderedNormTransformerLayerConfig(attention=attn), ce_chunk_rows=256)
-    model = cfg.build(seed=5, mesh_resource=MeshResource.FSDP(world), device=dev, comm_backend=backend)
+    res = {"fsdp": lambda: MeshResource.FSDP(world), "ddp": lambda: MeshResource.DDP(world),
+           "hsdp": lambda: MeshResource.HSDP(2, world, 2)}[mesh_kind]()
+    model = cfg.build(seed=5, mesh_resource=res, device=dev, comm_backend=backend)
     assert (model.store.symm is not None) == (backend == "fused")
     optim = AdamWConfig(lr=ConstantSchedule(1e-3), max_grad_norm=1.0).build(model, 2)
     g = torch.Generator().manual_seed(100 + rank)
@@ -135,12 +137,13 @@ def _train_worker(backend):
     return losses, first_grads.cpu(), full
 
 
-def test_peer_memory_backend_matches_nccl_on_two_gpus():
-    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    fused = run_distributed_test(_train_worker, world_size=2, backend="nccl", func_args=("fused",), timeout=300)
-    nccl = run_distributed_test(_train_worker, world_size=2, backend="nccl", func_args=("nccl",), timeout=300)
-    for r in range(2):
+@pytest.mark.parametrize("mesh_kind,world", [("fsdp", 2), ("ddp", 2), ("hsdp", 4)])
+def test_peer_memory_backend_matches_nccl(mesh_kind, world):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    fused = run_distributed_test(_train_worker, world_size=world, backend="nccl", func_args=("fused", mesh_kind), timeout=300)
+    nccl = run_distributed_test(_train_worker, world_size=world, backend="nccl", func_args=("nccl", mesh_kind), timeout=300)
+    for r in range(world):
         lf, gf, pf = fused[r]
         ln, gn, pn = nccl[r]
         assert all(abs(a - b) < 2e-2 * abs(b) for a, b in zip(lf, ln)), (lf, ln)
