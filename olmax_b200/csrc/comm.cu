@@ -57,6 +57,29 @@ __global__ void __launch_bounds__(AR_THREADS)
   }
 }
 
+// acc[i] += scale * sum_r stage[r * slot_stride + i]: folds the R per-source slots that peers' weight-gradient GEMMs
+// stored into this GPU's staging buffer into the fp32 gradient accumulator (all local memory).
+__global__ void __launch_bounds__(AR_THREADS)
+    reduce_slots_kernel(const float* __restrict__ stage, float* __restrict__ acc, long long n, int R,
+                        long long slot_stride, float scale) {
+  const long long n4 = n / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 a = reinterpret_cast<float4*>(acc)[i];
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < R; ++r) {
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(stage + r * slot_stride) + i);
+      sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+    }
+    a.x += scale * sum.x; a.y += scale * sum.y; a.z += scale * sum.z; a.w += scale * sum.w;
+    reinterpret_cast<float4*>(acc)[i] = a;
+  }
+  for (long long i = n4 * 4 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float sum = 0.f;
+    for (int r = 0; r < R; ++r) sum += stage[r * slot_stride + i];
+    acc[i] += scale * sum;
+  }
+}
+
 }  // namespace ob
 
 using namespace ob;
@@ -85,6 +108,17 @@ extern "C" int ob_allreduce_multimem_f32(float* mc, long long n, int me, int wor
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   allreduce_multimem_kernel<<<(unsigned)blocks, AR_THREADS, 0, stream>>>(mc, n, me, world);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_reduce_slots_f32(const float* stage, float* acc, long long n, int R, long long slot_stride, float scale,
+                                   cudaStream_t stream) {
+  if (n <= 0 || R <= 0) return 0;
+  long long blocks = ((n + 3) / 4 + AR_THREADS - 1) / AR_THREADS;
+  const long long cap = 8LL * sm_count();
+  if (blocks > cap) blocks = cap;
+  reduce_slots_kernel<<<(unsigned)blocks, AR_THREADS, 0, stream>>>(stage, acc, n, R, slot_stride, scale);
   OB_CUDA_OK(cudaGetLastError());
   return 0;
 }

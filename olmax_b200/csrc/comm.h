@@ -14,6 +14,10 @@ int ob_allreduce_p2p_f32(float* const* bufs, long long n, int me, int world, flo
 // Same through an NVLS multicast address `mc` (multimem.ld_reduce / multimem.st); n must be a multiple of 4.
 int ob_allreduce_multimem_f32(float* mc, long long n, int me, int world, int max_blocks, cudaStream_t stream);
 
+// acc[i] += scale * sum over r < R of stage[r * slot_stride + i]   (fp32, local memory)
+int ob_reduce_slots_f32(const float* stage, float* acc, long long n, int R, long long slot_stride, float scale,
+                        cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -52,6 +52,7 @@ struct KernelParams {
   long long ldc;
   int* status;
   int group_m;                 // tile rasterisation group (M tiles)
+  int m_rot;                   // rotation of the M tile order (tiles), see decode_tile
   int a_single, b_single;      // MN-major operand fetched with one 4-D TMA box per stage instead of 64-wide boxes
   int tma_epi;                 // 1: outputs leave through shared memory + TMA store / reduce-add (tmC valid)
   // FSDP all-gather fused into the GEMM: the B operand's remote shards are pulled from peer GPUs (plain loads over
@@ -83,10 +84,13 @@ __device__ __forceinline__ void warp_copy16(const uint4* __restrict__ src, uint4
                                             int n_cw, int lane) {
   long long i = (long long)cw * 32 + lane;
   const long long step = (long long)n_cw * 32;
-  for (; i + 3 * step < n16; i += 4 * step) {
-    const uint4 v0 = __ldcg(src + i), v1 = __ldcg(src + i + step), v2 = __ldcg(src + i + 2 * step),
-                v3 = __ldcg(src + i + 3 * step);
-    dst[i] = v0; dst[i + step] = v1; dst[i + 2 * step] = v2; dst[i + 3 * step] = v3;
+  // 8 x 16 bytes per lane in flight: NVLink latency is a few microseconds, so the copy rate is set by the bytes in flight
+  for (; i + 7 * step < n16; i += 8 * step) {
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = __ldcg(src + i + u * step);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) dst[i + u * step] = v[u];
   }
   for (; i < n16; i += step) dst[i] = __ldcg(src + i);
 }
@@ -94,13 +98,16 @@ __device__ __forceinline__ void warp_copy16(const uint4* __restrict__ src, uint4
 // Tile rasterisation: tiles are visited in groups of `group_m` consecutive M tiles, all N tiles of a group before the
 // next group, M fastest inside.  A wave of ~148 concurrent CTAs then touches group_m A slabs and 148 / group_m B slabs
 // instead of every A slab, which keeps the operands of a wave resident in L2.
-__device__ __forceinline__ void decode_tile(int tile, int m_tiles, int n_tiles, int group_m, int n_rot, int& mt, int& nt) {
+__device__ __forceinline__ void decode_tile(int tile, int m_tiles, int n_tiles, int group_m, int n_rot, int m_rot,
+                                            int& mt, int& nt) {
   const int per_group = group_m * n_tiles;
   const int g = tile / per_group;
   const int within = tile - g * per_group;
   const int gm = min(group_m, m_tiles - g * group_m);
   nt = (within / gm + n_rot) % n_tiles;
-  mt = g * group_m + within % gm;
+  // m_rot staggers the output row shards by rank, so that GPUs adding into each other's shards do not all target the
+  // same owner (and the same addresses) at the same time
+  mt = (g * group_m + within % gm + m_rot) % m_tiles;
 }
 
 // Bounded wait for an all-gather block; returns false (and records the error) when it does not arrive.
@@ -191,7 +198,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int mt, nt;
-        decode_tile(tile, m_tiles, n_tiles, p.group_m, n_rot, mt, nt);
+        decode_tile(tile, m_tiles, n_tiles, p.group_m, n_rot, p.m_rot, mt, nt);
         const int m0 = (mt / p.m_tiles_per_shard) * p.M_s + (mt % p.m_tiles_per_shard) * BM;
         const int n_shard = nt / p.n_tiles_per_shard;
         const int n_local0 = (nt % p.n_tiles_per_shard) * p.bn_out;
@@ -329,7 +336,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       const int buf = it & 1;
       const uint32_t tphase = (uint32_t)(it >> 1) & 1u;
       int mt, nt;
-        decode_tile(tile, m_tiles, n_tiles, p.group_m, n_rot, mt, nt);
+        decode_tile(tile, m_tiles, n_tiles, p.group_m, n_rot, p.m_rot, mt, nt);
       const int m_shard = mt / p.m_tiles_per_shard;
       const int m_local0 = (mt % p.m_tiles_per_shard) * BM;
       const int n_shard = nt / p.n_tiles_per_shard;
@@ -368,7 +375,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         for (int c0 = 0; c0 < BN; c0 += cols, ++chunk) {
           if (c0 >= n_valid) break;
           uint8_t* stage_buf = epi_smem + (chunk & 1) * EPI_STAGE_BYTES;
-          if (store_thread) tma_store_wait_read<1>();        // the store that last read this buffer is done with it
+          if (store_thread && p.tma_epi == 1) tma_store_wait_read<1>();   // the store that last read this buffer is done
           asm volatile("bar.sync 1, 128;" ::: "memory");
           uint32_t r[32], r2[32];
           tmem_ld32(t_row + (uint32_t)c0, r);
@@ -395,12 +402,38 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
               *reinterpret_cast<uint4*>(srow + ((j ^ sw) << 4)) = v;
             }
           }
-          fence_proxy_async();
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (store_thread) {
-            if (p.epi == EPI_F32_ACC) tma_reduce_add_3d(&tmC, stage_buf, n_glob0 + c0, out_row, out_z);
-            else tma_store_3d(&tmC, stage_buf, n_glob0 + c0, out_row, out_z);
-            tma_store_commit();
+          if (p.tma_epi == 1) {
+            fence_proxy_async();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (store_thread) {
+              if (p.epi == EPI_F32_ACC) tma_reduce_add_3d(&tmC, stage_buf, n_glob0 + c0, out_row, out_z);
+              else tma_store_3d(&tmC, stage_buf, n_glob0 + c0, out_row, out_z);
+              tma_store_commit();
+            }
+          } else {
+            // Destination may be another GPU's memory (no TMA there): the four epilogue warps write the staged chunk
+            // out cooperatively, 8 lanes per 128-byte row segment, so that every store instruction covers whole
+            // 128-byte lines (NVLink moves full lines far better than scattered 16-byte pieces).
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int et = (int)threadIdx.x - 64;          // 0..127
+            const int piece = et & 7;
+            uint8_t* dbase = reinterpret_cast<uint8_t*>(p.c_shards[m_shard]);
+            const int nv_bytes = min(cols, n_valid - c0) * (f32 ? 4 : 2);
+#pragma unroll
+            for (int pass = 0; pass < 8; ++pass) {
+              const int rr = pass * 16 + (et >> 3);
+              if (rr < m_valid && piece * 16 < nv_bytes) {
+                const uint4 v = *reinterpret_cast<const uint4*>(stage_buf + rr * 128 + ((piece ^ (rr & 7)) << 4));
+                uint8_t* dst = dbase + ((long long)(m_local0 + rr) * p.ldc + n_glob0 + c0) * (f32 ? 4 : 2) + piece * 16;
+                if (p.epi == EPI_F32_RED) {
+                  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(__uint_as_float(v.x)),
+                               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                               : "memory");
+                } else {
+                  *reinterpret_cast<uint4*>(dst) = v;
+                }
+              }
+            }
           }
         }
       } else if (!glu) {
@@ -600,6 +633,7 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
   kp.k_iters_per_shard = (Kc_s + BK - 1) / BK;
   kp.epi = a->epi;
   kp.group_m = a->group_m > 0 ? a->group_m : 16;
+  kp.m_rot = (a->m_shard_rot > 0 ? a->m_shard_rot : 0) * ((M_s + BM - 1) / BM);
   if (kp.group_m > kp.m_shards * kp.m_tiles_per_shard) kp.group_m = kp.m_shards * kp.m_tiles_per_shard;
   kp.alpha = a->alpha;
   kp.c = a->c; kp.c2 = a->c2; kp.c3 = a->c3;
@@ -719,6 +753,10 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
       kp.tma_epi = 1;
     }
   }
+  // peer destinations: staged, line-coalesced stores / reductions (needs 16-byte aligned rows)
+  if (kp.tma_epi == 0 && a->c_shards != nullptr && !a->no_tma_epilogue &&
+      (a->epi == EPI_F32 || a->epi == EPI_F32_RED || a->epi == EPI_BF16) && (a->ldc * (a->epi == EPI_BF16 ? 2 : 4)) % 16 == 0)
+    kp.tma_epi = 2;
   if (a->a_mn) {
     return a->b_mn ? launch<true, true>(tA, tB, tB2, tC, kp, grid, stream) : launch<true, false>(tA, tB, tB2, tC, kp, grid, stream);
   }

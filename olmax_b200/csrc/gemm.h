@@ -60,6 +60,7 @@ typedef struct ObGemmArgs {
   void* pf_dst;
   long long pf_dst_stride, pf_off, pf_bytes;  // bytes, multiples of 16
   int pf_shards, pf_rank;
+  int m_shard_rot;      // start the M tile order at output row shard m_shard_rot (stagger ranks that add into peers)
   int group_m;          // tile rasterisation group in M tiles (0 = default 16)
   int multi_box_mn;     // 1: fetch MN-major operands as 64-wide boxes even when one 4-D box per stage would do
   int no_tma_epilogue;  // 1: write outputs with per-thread stores instead of shared memory + TMA (for comparison)

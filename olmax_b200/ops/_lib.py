@@ -64,6 +64,7 @@ class ObGemmArgs(ctypes.Structure):
         ("pf_bytes", ctypes.c_longlong),
         ("pf_shards", ctypes.c_int),
         ("pf_rank", ctypes.c_int),
+        ("m_shard_rot", ctypes.c_int),
         ("group_m", ctypes.c_int),
         ("multi_box_mn", ctypes.c_int),
         ("no_tma_epilogue", ctypes.c_int),

@@ -91,11 +91,14 @@ def _gemm_wgrad(dy2: torch.Tensor, x2: torch.Tensor, handle) -> None:
     Kd = x2.shape[1]
     R = handle.shard_count
     symm = getattr(handle.store, "symm_rs", None)
-    peer = symm.grad_pointer_table(handle) if (symm is not None and R > 1) else None
+    peer = symm.stage_pointer_table(handle) if (symm is not None and R > 1) else None
     pf = handle.store.prefetch_slice(N * Kd)
     if peer is not None:
-        K.gemm(dy2, x2, handle.local_grad, N, Kd, M, a_mn=True, b_mn=True, epi=K.EPI_F32_RED, alpha=handle.store.grad_scale,
-               ldc=Kd, M_s=handle.rows_local, c_shards=peer, prefetch=pf)
+        # reduce-scatter fused into the epilogue: row block r is STORED into this rank's slot of GPU r's staging buffer
+        # (plain stores over NVLink, rank-staggered tile order); the owner folds the slots after the unit's barrier
+        K.gemm(dy2, x2, handle.local_grad, N, Kd, M, a_mn=True, b_mn=True, epi=K.EPI_F32, alpha=1.0, ldc=Kd,
+               M_s=handle.rows_local, c_shards=peer, prefetch=pf, m_shard_rot=handle.store.mesh.shard.rank)
+        handle.unit._staged.add(handle.name)
     else:
         dst, gstride, scale = handle.grad_pieces()
         kw = {} if R == 1 else {"M_s": handle.rows_local, "c_shard_stride": gstride}
@@ -487,17 +490,26 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
             dx = torch.empty_like(x2) if need_grad else None
             rc = min(chunk_rows, M)
             logits = torch.empty((rc, V), dtype=torch.float32, device=dev)
-            dlogits = torch.empty((rc, V), dtype=torch.bfloat16, device=dev) if need_grad else None
+            # The store-based reduce-scatter of the peer-memory backend cannot accumulate several partial weight
+            # gradients into a staging slot, so there d(logits) is kept for all rows and ONE weight-gradient GEMM runs at
+            # the end; otherwise each chunk's weight gradient is accumulated right away and its d(logits) dropped.
+            single_wgrad = need_grad and getattr(handle.store, "symm_rs", None) is not None and handle.shard_count > 1
+            drows = M if single_wgrad else rc
+            dlogits = torch.empty((drows, V), dtype=torch.bfloat16, device=dev) if need_grad else None
             for r0 in range(0, M, rc):
                 r1 = min(M, r0 + rc)
                 n = r1 - r0
                 xc = x2[r0:r1]
+                dl = (dlogits[r0:r1] if single_wgrad else dlogits[:n]) if need_grad else None
                 _gemm_fwd(xc, handle, out=logits[:n], epi=K.EPI_F32)
-                K.ce_fwd_bwd(logits[:n], lab[r0:r1], dlogits[:n] if need_grad else None, stats, inv, V=V,
-                             ignore_index=ignore_index, softcap=softcap, z_loss=z_loss)
+                K.ce_fwd_bwd(logits[:n], lab[r0:r1], dl, stats, inv, V=V, ignore_index=ignore_index, softcap=softcap,
+                             z_loss=z_loss)
                 if need_grad:
-                    _gemm_dgrad(dlogits[:n], handle, out=dx[r0:r1])
-                    _gemm_wgrad(dlogits[:n], xc, handle)
+                    _gemm_dgrad(dl, handle, out=dx[r0:r1])
+                    if not single_wgrad:
+                        _gemm_wgrad(dl, xc, handle)
+            if single_wgrad:
+                _gemm_wgrad(dlogits, x2, handle)
             loss = stats[0] * inv[0]
             zl = stats[1] * inv[0] * z_loss
             ctx.save_for_backward(dx if need_grad else torch.empty(0))

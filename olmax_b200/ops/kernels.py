@@ -66,6 +66,7 @@ register_signature("ob_gather_shards", [_vp, _vp, _ll, _ll, _i, _i, _vp])
 register_signature("ob_scatter_add_shards", [_vp, _vp, _ll, _i, _f, _vp])
 register_signature("ob_allreduce_p2p_f32", [_vp, _ll, _i, _i, _f, _i, _vp])
 register_signature("ob_allreduce_multimem_f32", [_vp, _ll, _i, _i, _i, _vp])
+register_signature("ob_reduce_slots_f32", [_vp, _vp, _ll, _i, _ll, _f, _vp])
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -116,6 +117,7 @@ def gemm(
     no_tma_epilogue: bool = False,
     group_m: int = 0,
     multi_box_mn: bool = False,
+    m_shard_rot: int = 0,
 ) -> None:
     """``C[M, N] (+)= alpha * A[M, K] . B[K, N]``; see ``csrc/gemm.h`` for operand layouts and sharding."""
     _req_bf16(a, b, b2)
@@ -143,6 +145,7 @@ def gemm(
     args.ag_rank = ag_rank
     args.no_tma_epilogue = int(no_tma_epilogue)
     args.group_m = group_m
+    args.m_shard_rot = m_shard_rot
     args.multi_box_mn = int(multi_box_mn)
     if prefetch is not None:
         table, dst_ptr, dst_stride, off, nbytes, shards, rank = prefetch
@@ -329,4 +332,11 @@ def allreduce_p2p(table, n, me, world, scale=1.0, max_blocks=0) -> None:
 def allreduce_multimem(mc_ptr: int, n, me, world, max_blocks=0, device=None) -> None:
     """In-place sum through an NVLS multicast address (multimem.ld_reduce / multimem.st)."""
     check(lib().ob_allreduce_multimem_f32(mc_ptr, n, me, world, max_blocks, stream_ptr(device)), "allreduce_multimem")
+    _count()
+
+
+def reduce_slots(stage, acc, n, R, slot_stride, scale=1.0) -> None:
+    """acc[:n] += scale * sum_r stage[r * slot_stride : r * slot_stride + n] (fp32, local)."""
+    check(lib().ob_reduce_slots_f32(stage.data_ptr(), acc.data_ptr(), n, R, slot_stride, scale, stream_ptr(acc.device)),
+          "reduce_slots")
     _count()

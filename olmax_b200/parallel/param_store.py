@@ -187,6 +187,7 @@ class FSDPUnit:
         self._full_grad: Optional[torch.Tensor] = None
         self._full_cache: Dict[str, torch.Tensor] = {}
         self._ag_pending: set = set()
+        self._staged: set = set()   # parameters whose weight gradient sits in the peers' staging slots
         self._pf_cursor = 0
         self.numel_full_2d = 1
         self.lazy = False  # True: only gather when a consumer actually asks for the gathered buffer
@@ -248,6 +249,13 @@ class FSDPUnit:
     def reduce_grads(self) -> None:
         """Reduce-scatter this unit's full gradient into the local accumulator (asynchronously on the GPU)."""
         st = self.store
+        if self._staged:
+            # peer-memory backend: every rank's weight-gradient GEMMs have stored their contributions into the owners'
+            # staging slots; after a barrier each owner folds its slots into its accumulator
+            names, self._staged = self._staged, set()
+            st.sync_peers()
+            st.symm.fold_stage(self, names)
+            st.stats["reduce_scatter_bytes"] += (st.mesh.shard.size - 1) * self.numel_local * 4
         if self._full_grad is None:
             return
         R = st.mesh.shard.size
@@ -507,7 +515,7 @@ class ParamStore:
         in-flight reduce-scatters, fold them into the fp32 accumulators and drop gathered weights."""
         self._in_backward = False
         for u in self.units:
-            if u._full_grad is not None:
+            if u._full_grad is not None or u._staged:
                 u.reduce_grads()
         if self.reshard_after_forward and self.mesh.shard.size > 1:
             for u in self.units:

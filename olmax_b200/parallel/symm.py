@@ -73,6 +73,17 @@ class SymmContext:
         mc = int(getattr(self._h_grad, "multicast_ptr", 0) or 0)
         use_mc = os.environ.get("OLMAX_B200_MULTIMEM", "1") == "1"
         self.multicast_ptr = mc if (use_mc and mesh.replicate.size == mesh.world_size) else 0
+        # Reduce-scatter staging: every weight-gradient GEMM STORES (plain stores, no atomics) the row block owned by
+        # GPU r into slot `me` of r's staging buffer; after a barrier r folds its R slots into its accumulator.  Two
+        # buffers alternate between consecutive FSDP units.
+        self.stage_slot = max((u.numel_local for u in store.units), default=0)
+        self.rs_stage = None
+        self.stage_ptrs: List[int] = []
+        if self.R > 1 and os.environ.get("OLMAX_B200_FUSED_RS", "1") == "1":
+            self.rs_stage = symm_mem.empty(2 * self.R * self.stage_slot, dtype=torch.float32, device=dev)
+            self._h_stage = symm_mem.rendezvous(self.rs_stage, world)
+            all_stage = [int(p) for p in self._h_stage.buffer_ptrs]
+            self.stage_ptrs = [all_stage[r] for r in mesh.shard.ranks]
         self.flags = torch.zeros(max(1, self.R) * 4096, dtype=torch.int32, device=dev)
         self._tables: Dict[tuple, torch.Tensor] = {}
         self._token = torch.zeros(1, dtype=torch.float32, device=dev)
@@ -93,6 +104,31 @@ class SymmContext:
     def grad_pointer_table(self, handle) -> torch.Tensor:
         """Device array of the R addresses where the row shards of ``handle``'s gradient live (one per GPU)."""
         return self._table("grad", handle, self.grad_ptrs, 4)
+
+    def stage_pointer_table(self, handle) -> torch.Tensor:
+        """Device array: for every owner GPU r, the address inside r's staging buffer where THIS rank's contribution
+        to the row shard r of ``handle``'s gradient goes (buffer chosen by the parity of the unit index)."""
+        buf = handle.unit.index & 1
+        key = ("stage", handle.name, buf)
+        t = self._tables.get(key)
+        if t is None:
+            off = ((buf * self.R + self.rank) * self.stage_slot + handle.meta.unit_offset) * 4
+            t = K.pointer_table([p + off for p in self.stage_ptrs], self.store.device)
+            self._tables[key] = t
+        return t
+
+    def fold_stage(self, unit, names) -> None:
+        """accumulator += grad_scale * sum over the R slots of the unit's staging buffer, for the parameters in
+        ``names`` (those whose weight gradient was stored this pass; other regions of the slots hold stale data)."""
+        buf = unit.index & 1
+        base = buf * self.R * self.stage_slot
+        for h in unit.params:
+            if h.name not in names:
+                continue
+            m = h.meta
+            stage = self.rs_stage[base + m.unit_offset:]
+            acc = self.grad[m.offset : m.offset + m.numel_local]
+            K.reduce_slots(stage, acc, m.numel_local, self.R, self.stage_slot, self.store.grad_scale)
 
     def shadow_pointer_table(self, handle) -> torch.Tensor:
         return self._table("shadow", handle, self.shadow_ptrs, self.shadow.element_size())
