@@ -122,6 +122,8 @@ def main() -> int:
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl"],
                     help="fused: collectives inside our kernels over peer memory; nccl: the NCCL baseline path")
+    ap.add_argument("--ac", default="recipe", choices=["recipe", "none", "mlp", "full"],
+                    help="activation checkpointing: the recipe's policy, none, recompute the MLP blocks, or whole layers")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -154,6 +156,11 @@ def main() -> int:
     if args.layers is not None:
         import dataclasses
         model_cfg = dataclasses.replace(model_cfg, num_layers=args.layers)
+    if args.ac != "recipe":
+        import dataclasses
+        from olmax_b200.activation_checkpointing import NothingSaveable, SaveAnythingExceptTheseNames
+        policy = {"none": None, "mlp": SaveAnythingExceptTheseNames(names=["layers.*.mlp"]), "full": NothingSaveable()}[args.ac]
+        model_cfg = dataclasses.replace(model_cfg, layer_ac_policy=policy)
     mesh_res = build_mesh(args.mesh, world, world, args.shard_degree, None, args.tp_degree)
     mesh = mesh_res.build(device=dev)
     set_mesh(mesh)
@@ -257,7 +264,7 @@ def main() -> int:
                 "model": args.recipe, "global_batch": global_batch, "seq_len": seq, "microbatches": k,
                 "parallelism": f"{args.mesh.lower()}{world}", "optimizer": "AdamW fp32 master/moments",
                 "comm": "fused peer-memory kernels" if model.store.symm is not None else ("nccl" if world > 1 else "none"),
-                "layers": model_cfg.num_layers, "params": model.num_params(),
+                "layers": model_cfg.num_layers, "params": model.num_params(), "activation_checkpointing": args.ac,
                 "l2": "working set (>14 GB of weights per step) exceeds L2, no explicit flush",
             },
             "mfu_of_measured_sustained": round(per_gpu * flops_tok / (sustained * 1e12), 4),

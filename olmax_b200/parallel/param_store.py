@@ -269,6 +269,10 @@ class FSDPUnit:
             work = None
         st.stats["reduce_scatter_bytes"] += (R - 1) * self.numel_local * buf.element_size()
         st._pending_reduce.append((self, work, buf, out))
+        # keep one reduce-scatter in flight: fold the older ones now so that their full-size buffers return to the pool
+        # (otherwise a whole model's worth of un-reduced fp32 gradients is alive at the end of the backward pass)
+        while len(st._pending_reduce) > 1:
+            st._fold_pending(st._pending_reduce.pop(0))
 
 
 class ParamStore:
@@ -520,13 +524,16 @@ class ParamStore:
         if self.reshard_after_forward and self.mesh.shard.size > 1:
             for u in self.units:
                 u.release()
-        for unit, work, buf, out in self._pending_reduce:
-            if work is not None:
-                work.wait()
-            self.grad[unit.offset : unit.offset + unit.numel_local].add_(out, alpha=self.grad_scale)
-            self._give_buffer("grad", buf)
-            self._give_buffer("rs_out", out)
-        self._pending_reduce.clear()
+        while self._pending_reduce:
+            self._fold_pending(self._pending_reduce.pop(0))
+
+    def _fold_pending(self, item) -> None:
+        unit, work, buf, out = item
+        if work is not None:
+            work.wait()   # stream-ordered: the compute stream waits for the collective, the host does not
+        self.grad[unit.offset : unit.offset + unit.numel_local].add_(out, alpha=self.grad_scale)
+        self._give_buffer("grad", buf)
+        self._give_buffer("rs_out", out)
 
     def reduce_replicated_grads(self) -> None:
         """
@@ -619,6 +626,23 @@ class ParamStore:
         """Sum of squares of the full gradient (fp32 scalar tensor, identical on all ranks).  TP-replicated
         parameters are counted once."""
         tp = self.mesh.tp
+        if self.grad.is_cuda:
+            # no temporaries: the reduction kernel accumulates straight into two fp64 scalars
+            acc = torch.zeros(2, dtype=torch.float64, device=self.device)
+            if tp.size > 1:
+                for s, e in self._runs(lambda m: m.tp_dim is not None):
+                    K.sumsq(self.grad[s:e], acc[0:1])
+                for s, e in self._runs(lambda m: m.tp_dim is None):
+                    K.sumsq(self.grad[s:e], acc[1:2])
+                t = (acc[0] + acc[1] / tp.size).view(1)
+            else:
+                K.sumsq(self.grad, acc[0:1])
+                t = acc[0:1]
+            if self.mesh.shard.size > 1:
+                dist.all_reduce(t, group=self.mesh.shard.pg)
+            if tp.size > 1:
+                dist.all_reduce(t, group=tp.pg)
+            return t[0].float()
         total = torch.zeros((), dtype=torch.float64, device=self.device)
         if tp.size > 1:
             sharded = torch.zeros((), dtype=torch.float64, device=self.device)

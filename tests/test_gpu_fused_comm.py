@@ -150,3 +150,53 @@ def test_peer_memory_backend_matches_nccl(mesh_kind, world):
         assert rel_err(gf, gn) < 2e-2
         for name in pn:
             assert rel_err(pf[name], pn[name]) < 1e-2, name
+
+
+def _tp_worker(mesh_kind):
+    from olmax_b200.models import DefaultTransformerConfig, GemmaTransformerLayerConfig
+    from olmax_b200.nn import LMHeadConfig, MultiheadSelfAttentionConfig
+    from olmax_b200.ops import _lib
+    from olmax_b200.optim import AdamWConfig, ConstantSchedule
+    from olmax_b200.parallel import MeshResource, dist_utils
+
+    world, rank = dist_utils.get_world_size(), dist_utils.get_rank()
+    dev = torch.device("cuda", rank)
+    res = MeshResource.FSDP_with_TP(2, world) if mesh_kind == "tp" else MeshResource.FSDP(world)
+    attn = MultiheadSelfAttentionConfig(n_heads=4, n_kv_heads=2, head_dim=128, logit_softcap=50.0)
+    cfg = DefaultTransformerConfig(vocab_size=4096, d_model=512, hidden_size=1024, num_layers=2,
+                                   layer=GemmaTransformerLayerConfig(attention=attn), lm_head=LMHeadConfig(logit_softcap=30.0),
+                                   tie_embeddings=True, scale_embeddings=True, sliding_window=128, sliding_window_pattern=2,
+                                   ce_chunk_rows=256)
+    model = cfg.build(seed=5, mesh_resource=res, device=dev, comm_backend="nccl")
+    mesh = model.mesh
+    optim = AdamWConfig(lr=ConstantSchedule(1e-3)).build(model, 1)
+    gen = torch.Generator().manual_seed(7)
+    cache = model.get_buffer_cache(256, dev)
+    losses = []
+    for step in range(3):
+        ids = torch.randint(0, 4096, (4, 256), generator=gen)      # the same global batch on every rank
+        per = 4 // mesh.data_parallel_size
+        mine = ids[mesh.data_parallel_rank * per : (mesh.data_parallel_rank + 1) * per].to(dev)
+        loss, _ = model(mine, torch.roll(mine, -1, 1), cache)
+        loss.backward()
+        optim.accumulate()
+        optim.step()
+        t = loss.detach().clone()
+        torch.distributed.all_reduce(t)
+        losses.append(t.item() / world)
+    torch.cuda.synchronize()
+    _lib.check_status(dev)
+    return losses, {n: model.store.full_parameter(n).cpu() for n, _ in model.store.named_parameters()}
+
+
+def test_tensor_parallel_matches_fsdp_on_two_gpus():
+    """FSDP x TP (heads and MLP hidden split over 2 GPUs, sequence-parallel norms) trains like plain FSDP."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    tp = run_distributed_test(_tp_worker, world_size=2, backend="nccl", func_args=("tp",), timeout=300)
+    fsdp = run_distributed_test(_tp_worker, world_size=2, backend="nccl", func_args=("fsdp",), timeout=300)
+    lt, pt = tp[0]
+    lf, pf = fsdp[0]
+    assert all(abs(a - b) < 2e-2 * abs(b) for a, b in zip(lt, lf)), (lt, lf)
+    for name in pf:
+        assert rel_err(pt[name], pf[name]) < 1e-2, name
