@@ -114,9 +114,11 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--recipe", default="olmo2_7B_bench")
-    ap.add_argument("--mesh", default="FSDP", choices=["FSDP", "HSDP", "DDP", "FSDP_with_TP"])
+    ap.add_argument("--mesh", default="FSDP", choices=["FSDP", "HSDP", "DDP", "FSDP_with_TP", "FSDP_with_CP", "HSDP_with_CP"])
     ap.add_argument("--shard-degree", type=int, default=None)
     ap.add_argument("--tp-degree", type=int, default=2)
+    ap.add_argument("--cp-degree", type=int, default=None, help="context-parallel degree of the *_with_CP meshes")
+    ap.add_argument("--cp-strategy", default=None, choices=["all_gather", "ring"])
     ap.add_argument("--microbatches", type=int, default=2)
     ap.add_argument("--layers", type=int, default=None, help="debug only: truncate the model (makes the run INVALID as a benchmark)")
     ap.add_argument("--skip-e2e", action="store_true")
@@ -156,19 +158,24 @@ def main() -> int:
     if args.layers is not None:
         import dataclasses
         model_cfg = dataclasses.replace(model_cfg, num_layers=args.layers)
+    if args.cp_strategy is not None:
+        import dataclasses
+        layer = model_cfg.layer
+        model_cfg = dataclasses.replace(model_cfg, layer=dataclasses.replace(
+            layer, attention=dataclasses.replace(layer.attention, cp_strategy=args.cp_strategy)))
     if args.ac != "recipe":
         import dataclasses
         from olmax_b200.activation_checkpointing import NothingSaveable, SaveAnythingExceptTheseNames
         policy = {"none": None, "mlp": SaveAnythingExceptTheseNames(names=["layers.*.mlp"]), "full": NothingSaveable()}[args.ac]
         model_cfg = dataclasses.replace(model_cfg, layer_ac_policy=policy)
-    mesh_res = build_mesh(args.mesh, world, world, args.shard_degree, None, args.tp_degree)
+    mesh_res = build_mesh(args.mesh, world, world, args.shard_degree, args.cp_degree, args.tp_degree)
     mesh = mesh_res.build(device=dev)
     set_mesh(mesh)
     seq = recipe.sequence_length
     inst_local = recipe.local_microbatch_size // seq
     k = args.microbatches
     dp = mesh.data_parallel_size
-    inst_per_dp = inst_local * mesh.tp.size
+    inst_per_dp = inst_local * mesh.tp.size * mesh.cp.size
     global_batch = inst_per_dp * dp * k
     tokens_per_step = global_batch * seq
 
@@ -183,7 +190,8 @@ def main() -> int:
     total_steps = args.warmup + args.steps * (1 if args.skip_e2e else 2) + 1
     batches = list(generate_batches_of_uniform_tokens(
         7, vocab_size=model_cfg.vocab_size, sequence_length=seq, global_microbatch_instances=inst_per_dp * dp,
-        num_microbatches=k, dp_rank=mesh.data_parallel_rank, dp_size=dp, num_batches=min(total_steps, 8), pin_memory=True))
+        num_microbatches=k, dp_rank=mesh.data_parallel_rank, dp_size=dp, cp_rank=mesh.cp.rank, cp_size=mesh.cp.size,
+        num_batches=min(total_steps, 8), pin_memory=True))
     dev_batches = [[(i.to(dev), l.to(dev)) for i, l in b] for b in batches]
 
     def sync_all():

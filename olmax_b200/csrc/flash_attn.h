@@ -28,11 +28,28 @@ typedef struct ObAttnArgs {
   float scale;      // softmax scale (usually 1/sqrt(D))
   float softcap;    // 0: off; else logits = softcap * tanh(scale * q.k / softcap)
   int* status;      // device int[4] error words (may be null)
+  // Rectangular problems (context parallelism, blockwise / ring attention): K and V have Sk rows (0: Sk = S) and
+  // query row i sits at position q_off + i of the key axis, so with `causal` key j is visible when j <= q_off + i.
+  // The launchers accept only geometries in which every query row sees at least one key and every 128-row key tile
+  // is seen by at least one query row: q_off >= 0; causal: Sk <= q_off + S; window >= 0: q_off <= window + 127 and
+  // q_off + S - 1 - window <= Sk - 1.  lse / delta / dq are indexed by the S query rows, dk / dv by the Sk key rows.
+  int Sk, q_off;
 } ObAttnArgs;
 
 int ob_flash_attn_fwd(const ObAttnArgs* args, cudaStream_t stream);
 int ob_flash_attn_bwd(const ObAttnArgs* args, cudaStream_t stream);
 
 #ifdef __cplusplus
+}
+// 0 when the geometry is one the kernels handle; otherwise the number of the violated rule (see ObAttnArgs)
+static inline int ob_attn_check_geometry(const ObAttnArgs* a, int* Sk_out) {
+  const int Sk = a->Sk > 0 ? a->Sk : a->S;
+  *Sk_out = Sk;
+  if (a->q_off < 0) return 1;
+  if (a->causal && Sk > a->q_off + a->S) return 2;
+  if (!a->causal && a->window >= 0) return 3;   // a window is only defined together with the causal mask
+  if (a->window >= 0 && a->q_off > a->window + 127) return 4;
+  if (a->window >= 0 && a->q_off + a->S - 1 - a->window > Sk - 1) return 5;
+  return 0;
 }
 #endif

@@ -45,6 +45,7 @@ constexpr int C_S = 0, C_DP = 128, C_DK = 256, C_DV = 384;
 
 struct Params {
   int B, S, H, Hkv;
+  int Sk, q_off;   // key length; key-axis position of query row 0
   int causal, window;
   float scale, scale_log2, softcap, scale_over_cap, cap_log2;
   const float* lse;
@@ -97,9 +98,13 @@ __global__ void __launch_bounds__(THREADS, 1)
   const int G = p.H / p.Hkv;
   const int kv0 = kv_tile * T;
 
+  // query tiles that see this key tile: rows i with kv0 <= q_off + i (causal) and q_off + i <= kv0 + T - 1 + window
   int i_lo = 0, i_hi = n_tiles - 1;
-  if (p.causal) i_lo = kv0 / T;
-  if (p.window >= 0) i_hi = min(i_hi, (kv0 + T - 1 + p.window) / T);
+  if (p.causal) i_lo = max(0, kv0 - p.q_off) / T;
+  if (p.window >= 0) {
+    const int last = kv0 + T - 1 + p.window - p.q_off;
+    i_hi = last < 0 ? -1 : min(i_hi, last / T);
+  }
   const int n_q = max(0, i_hi - i_lo + 1);
   const int n_iters = n_q * G;
 
@@ -286,10 +291,11 @@ __global__ void __launch_bounds__(THREADS, 1)
       const long long stat_idx = ((long long)b * p.H + h) * p.S + q_idx;
       const float lse2 = q_ok ? p.lse[stat_idx] * LOG2E : INFINITY;
       const float dl = q_ok ? p.delta[stat_idx] : 0.f;
-      const bool need_mask = (kv0 + T > p.S) || (p.causal && kv0 + T - 1 > q0) ||
-                             (p.window >= 0 && kv0 < q0 + T - 1 - p.window);
-      const int kv_hi = p.causal ? min(q_idx, p.S - 1) : p.S - 1;
-      const int kv_lo = p.window >= 0 ? q_idx - p.window : 0;
+      const int qp0 = p.q_off + q0, q_pos = p.q_off + q_idx;   // positions on the key axis
+      const bool need_mask = (kv0 + T > p.Sk) || (p.causal && kv0 + T - 1 > qp0) ||
+                             (p.window >= 0 && kv0 < qp0 + T - 1 - p.window);
+      const int kv_hi = p.causal ? min(q_pos, p.Sk - 1) : p.Sk - 1;
+      const int kv_lo = p.window >= 0 ? q_pos - p.window : 0;
 
       ok = mbar_wait(s_full, ph1, abort_flag, p.status, 900);
       if (!ok) break;
@@ -393,7 +399,7 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
     // dK, dV out (thread <-> key row, 64-column half)
     const int kv_idx = kv0 + row;
-    const bool kv_ok = kv_idx < p.S;
+    const bool kv_ok = kv_idx < p.Sk;
     bf16* dk_row = p.dk + (long long)b * p.dk_sb + (long long)kv_idx * p.dk_ss + (long long)hkv * p.dk_sh + col0;
     bf16* dv_row = p.dv + (long long)b * p.dv_sb + (long long)kv_idx * p.dv_ss + (long long)hkv * p.dv_sh + col0;
     if (n_iters == 0) {
@@ -495,11 +501,15 @@ extern "C" int ob_flash_attn_bwd(const ObAttnArgs* a, cudaStream_t stream) {
   if (a->D != 128) OB_FAIL(-2, "flash attention kernels are built for head_dim 128 (got %d)", a->D);
   if (a->H % a->Hkv != 0) OB_FAIL(-3, "H (%d) must be a multiple of Hkv (%d)", a->H, a->Hkv);
   if (a->delta == nullptr || a->dq_accum == nullptr) OB_FAIL(-4, "backward needs the delta and dq_accum scratch buffers");
+  int Sk = 0;
+  if (int g = ob_attn_check_geometry(a, &Sk))
+    OB_FAIL(-5, "unsupported attention geometry (rule %d): S %d Sk %d q_off %d causal %d window %d", g, a->S, Sk,
+            a->q_off, a->causal, a->window);
   CUtensorMap tq, tk, tv, tdo;
   int rc;
   if ((rc = encode_bshd_map(&tq, a->q, a->B, a->S, a->H, a->q_sb, a->q_ss, a->q_sh, 128))) return rc;
-  if ((rc = encode_bshd_map(&tk, a->k, a->B, a->S, a->Hkv, a->k_sb, a->k_ss, a->k_sh, 128))) return rc;
-  if ((rc = encode_bshd_map(&tv, a->v, a->B, a->S, a->Hkv, a->v_sb, a->v_ss, a->v_sh, 128))) return rc;
+  if ((rc = encode_bshd_map(&tk, a->k, a->B, Sk, a->Hkv, a->k_sb, a->k_ss, a->k_sh, 128))) return rc;
+  if ((rc = encode_bshd_map(&tv, a->v, a->B, Sk, a->Hkv, a->v_sb, a->v_ss, a->v_sh, 128))) return rc;
   if ((rc = encode_bshd_map(&tdo, a->d_o, a->B, a->S, a->H, a->do_sb, a->do_ss, a->do_sh, 128))) return rc;
 
   const long long rows = (long long)a->B * a->S * a->H;
@@ -513,6 +523,7 @@ extern "C" int ob_flash_attn_bwd(const ObAttnArgs* a, cudaStream_t stream) {
 
   fa_bwd::Params p;
   p.B = a->B; p.S = a->S; p.H = a->H; p.Hkv = a->Hkv;
+  p.Sk = Sk; p.q_off = a->q_off;
   p.causal = a->causal; p.window = a->window;
   const float LOG2E = 1.4426950408889634f;
   p.scale = a->scale;
@@ -532,7 +543,7 @@ extern "C" int ob_flash_attn_bwd(const ObAttnArgs* a, cudaStream_t stream) {
                                     fa_bwd::SMEM_BYTES));
     attr_set = true;
   }
-  dim3 grid((a->S + 127) / 128, a->Hkv, a->B);
+  dim3 grid((Sk + 127) / 128, a->Hkv, a->B);
   CUtensorMap tdq;
   if ((rc = fa_bwd::encode_dq_map(&tdq, a->dq_accum, a->B, a->S, a->H))) return rc;
   fa_bwd::flash_bwd_kernel<<<grid, fa_bwd::THREADS, fa_bwd::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdq, p);
@@ -594,11 +605,15 @@ extern "C" int ob_flash_attn_bwd_static(const ObAttnArgs* a, cudaStream_t stream
   if (rc) return rc;
   float* dq_accum = scratch;                     // [rows, 128]
   float* delta = scratch + MAX_ROWS * 128;       // [rows]
+  int Sk = 0;
+  if (int g = ob_attn_check_geometry(a, &Sk))
+    OB_FAIL(-5, "unsupported attention geometry (rule %d): S %d Sk %d q_off %d causal %d window %d", g, a->S, Sk,
+            a->q_off, a->causal, a->window);
 
   CUtensorMap tq, tk, tv, tdo;
   if ((rc = encode_bshd_map(&tq, a->q, a->B, a->S, a->H, a->q_sb, a->q_ss, a->q_sh, 128))) return rc;
-  if ((rc = encode_bshd_map(&tk, a->k, a->B, a->S, a->Hkv, a->k_sb, a->k_ss, a->k_sh, 128))) return rc;
-  if ((rc = encode_bshd_map(&tv, a->v, a->B, a->S, a->Hkv, a->v_sb, a->v_ss, a->v_sh, 128))) return rc;
+  if ((rc = encode_bshd_map(&tk, a->k, a->B, Sk, a->Hkv, a->k_sb, a->k_ss, a->k_sh, 128))) return rc;
+  if ((rc = encode_bshd_map(&tv, a->v, a->B, Sk, a->Hkv, a->v_sb, a->v_ss, a->v_sh, 128))) return rc;
   if ((rc = encode_bshd_map(&tdo, a->d_o, a->B, a->S, a->H, a->do_sb, a->do_ss, a->do_sh, 128))) return rc;
 
   const int wpb = 8;
@@ -612,6 +627,7 @@ extern "C" int ob_flash_attn_bwd_static(const ObAttnArgs* a, cudaStream_t stream
 
   fa_bwd::Params p;
   p.B = a->B; p.S = a->S; p.H = a->H; p.Hkv = a->Hkv;
+  p.Sk = Sk; p.q_off = a->q_off;
   p.causal = a->causal; p.window = a->window;
   const float LOG2E = 1.4426950408889634f;
   p.scale = a->scale;
@@ -631,7 +647,7 @@ extern "C" int ob_flash_attn_bwd_static(const ObAttnArgs* a, cudaStream_t stream
                                     fa_bwd::SMEM_BYTES));
     attr_set = true;
   }
-  dim3 grid((a->S + 127) / 128, a->Hkv, a->B);
+  dim3 grid((Sk + 127) / 128, a->Hkv, a->B);
   CUtensorMap tdq;
   if ((rc = fa_bwd::encode_dq_map(&tdq, dq_accum, a->B, a->S, a->H))) return rc;
   fa_bwd::flash_bwd_kernel<<<grid, fa_bwd::THREADS, fa_bwd::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdq, p);

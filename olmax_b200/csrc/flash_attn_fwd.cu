@@ -35,6 +35,7 @@ constexpr int O_COL = 128;    // O (fp32, 128 cols)
 
 struct Params {
   int B, S, H, Hkv;
+  int Sk, q_off;               // key length; position of query row 0 on the key axis (query i sits at q_off + i)
   int causal, window;          // window < 0: none; else keys with kv >= q - window
   float scale_log2;            // softmax scale * log2(e)            (no soft-cap)
   float softcap;               // 0: none
@@ -89,9 +90,10 @@ __global__ void __launch_bounds__(THREADS, 2)
 
   // key-tile range for this query tile
   int kv_tile_lo = 0;
-  int kv_tile_hi = (p.S + TK - 1) / TK - 1;
-  if (p.causal) kv_tile_hi = min(kv_tile_hi, (q0 + TQ - 1) / TK);
-  if (p.window >= 0) kv_tile_lo = max(0, (q0 - p.window) / TK);
+  const int qp0 = p.q_off + q0;   // key-axis position of this tile's first query row
+  int kv_tile_hi = (p.Sk + TK - 1) / TK - 1;
+  if (p.causal) kv_tile_hi = min(kv_tile_hi, (qp0 + TQ - 1) / TK);
+  if (p.window >= 0) kv_tile_lo = max(0, (qp0 - p.window) / TK);
   const int n_iters = kv_tile_hi - kv_tile_lo + 1;
 
   if (threadIdx.x == 0) {
@@ -188,6 +190,7 @@ __global__ void __launch_bounds__(THREADS, 2)
     const int row = qd * 32 + lane;
     const int col0 = half * 64;
     const int q_idx = q0 + row;
+    const int q_pos = p.q_off + q_idx;
     const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16);
     const bool capped = p.softcap > 0.f;
     float m_run = -INFINITY;  // running max, log2 domain (identical in both halves of a row)
@@ -199,10 +202,10 @@ __global__ void __launch_bounds__(THREADS, 2)
       ok = mbar_wait(s_full, ph, abort_flag, p.status, 600);
       if (!ok) break;
       tc_fence_after_sync();
-      const bool need_mask = (kv0 + TK > p.S) || (p.causal && kv0 + TK - 1 > q0) ||
-                             (p.window >= 0 && kv0 < q0 + TQ - 1 - p.window);
-      const int kv_hi = p.causal ? min(q_idx, p.S - 1) : p.S - 1;  // last visible key
-      const int kv_lo = p.window >= 0 ? q_idx - p.window : 0;      // first visible key
+      const bool need_mask = (kv0 + TK > p.Sk) || (p.causal && kv0 + TK - 1 > qp0) ||
+                             (p.window >= 0 && kv0 < qp0 + TQ - 1 - p.window);
+      const int kv_hi = p.causal ? min(q_pos, p.Sk - 1) : p.Sk - 1;  // last visible key
+      const int kv_lo = p.window >= 0 ? q_pos - p.window : 0;        // first visible key
       // this thread's 64 scores, kept in registers for both the max and the exponentials
       uint32_t r0[32], r1[32];
       tmem_ld32(t_lane + S_COL + (uint32_t)col0, r0);
@@ -331,13 +334,18 @@ extern "C" int ob_flash_attn_fwd(const ObAttnArgs* a, cudaStream_t stream) {
   if (a->D != 128) OB_FAIL(-2, "flash attention kernels are built for head_dim 128 (got %d)", a->D);
   if (a->H % a->Hkv != 0) OB_FAIL(-3, "H (%d) must be a multiple of Hkv (%d)", a->H, a->Hkv);
   if (a->B <= 0 || a->S <= 0) OB_FAIL(-4, "empty problem");
+  int Sk = 0;
+  if (int g = ob_attn_check_geometry(a, &Sk))
+    OB_FAIL(-5, "unsupported attention geometry (rule %d): S %d Sk %d q_off %d causal %d window %d", g, a->S, Sk,
+            a->q_off, a->causal, a->window);
   CUtensorMap tq, tk, tv;
   int rc;
   if ((rc = encode_bshd_map(&tq, a->q, a->B, a->S, a->H, a->q_sb, a->q_ss, a->q_sh, 128))) return rc;
-  if ((rc = encode_bshd_map(&tk, a->k, a->B, a->S, a->Hkv, a->k_sb, a->k_ss, a->k_sh, 128))) return rc;
-  if ((rc = encode_bshd_map(&tv, a->v, a->B, a->S, a->Hkv, a->v_sb, a->v_ss, a->v_sh, 128))) return rc;
+  if ((rc = encode_bshd_map(&tk, a->k, a->B, Sk, a->Hkv, a->k_sb, a->k_ss, a->k_sh, 128))) return rc;
+  if ((rc = encode_bshd_map(&tv, a->v, a->B, Sk, a->Hkv, a->v_sb, a->v_ss, a->v_sh, 128))) return rc;
   fa_fwd::Params p;
   p.B = a->B; p.S = a->S; p.H = a->H; p.Hkv = a->Hkv;
+  p.Sk = Sk; p.q_off = a->q_off;
   p.causal = a->causal; p.window = a->window;
   const float LOG2E = 1.4426950408889634f;
   p.scale_log2 = a->scale * LOG2E;

@@ -6,7 +6,9 @@ Synthetic token batches (``olmax/data/utils.py:12-66``).
 contributes zero loss but still counts in the mean).  ``generate_batches_of_uniform_tokens`` draws ids uniformly and
 uses the ids shifted by one as labels (the last label of a row is ``ignore_index``).  Both derive per-batch and
 per-micro-batch streams by folding indices into the seed, produce only this rank's data shard, and return pinned CPU
-tensors so that the host-to-device copy can be asynchronous.
+tensors so that the host-to-device copy can be asynchronous.  With context parallelism (``cp_size > 1``) a rank
+receives, of every instance of its data shard, the two chunks it holds in dual-chunk-swap order
+(``olmax/data/utils.py:25-31``).
 """
 
 from __future__ import annotations
@@ -28,10 +30,15 @@ def _maybe_pin(t: torch.Tensor, pin: bool) -> torch.Tensor:
     return t
 
 
-def _shard(t: torch.Tensor, dp_rank: int, dp_size: int) -> torch.Tensor:
+def _shard(t: torch.Tensor, dp_rank: int, dp_size: int, cp_rank: int = 0, cp_size: int = 1) -> torch.Tensor:
     assert t.shape[0] % dp_size == 0, "global micro-batch must be divisible by the data-parallel size"
     per = t.shape[0] // dp_size
-    return t[dp_rank * per : (dp_rank + 1) * per].contiguous()
+    t = t[dp_rank * per : (dp_rank + 1) * per]
+    if cp_size > 1:
+        from ..parallel.context import shard_sequence_for_cp
+
+        return shard_sequence_for_cp(t, cp_size, cp_rank, seq_dim=1)
+    return t.contiguous()
 
 
 def generate_batches_of_sequential_tokens(
@@ -43,6 +50,8 @@ def generate_batches_of_sequential_tokens(
     num_microbatches: int = 1,
     dp_rank: int = 0,
     dp_size: int = 1,
+    cp_rank: int = 0,
+    cp_size: int = 1,
     start_batch: int = 0,
     num_batches: Optional[int] = None,
     pin_memory: bool = True,
@@ -55,8 +64,8 @@ def generate_batches_of_sequential_tokens(
             offs = torch.randint(0, max(1, vocab_size - 1), (global_microbatch_instances, 1), generator=gen)
             inputs = (torch.arange(sequence_length).view(1, -1) + offs) % vocab_size
             targets = inputs + 1
-            batch.append((_maybe_pin(_shard(inputs, dp_rank, dp_size), pin_memory),
-                          _maybe_pin(_shard(targets, dp_rank, dp_size), pin_memory)))
+            batch.append((_maybe_pin(_shard(inputs, dp_rank, dp_size, cp_rank, cp_size), pin_memory),
+                          _maybe_pin(_shard(targets, dp_rank, dp_size, cp_rank, cp_size), pin_memory)))
         yield batch
         b += 1
 
@@ -70,6 +79,8 @@ def generate_batches_of_uniform_tokens(
     num_microbatches: int = 1,
     dp_rank: int = 0,
     dp_size: int = 1,
+    cp_rank: int = 0,
+    cp_size: int = 1,
     start_batch: int = 0,
     num_batches: Optional[int] = None,
     ignore_index: int = -100,
@@ -83,7 +94,7 @@ def generate_batches_of_uniform_tokens(
             ids = torch.randint(0, vocab_size, (global_microbatch_instances, sequence_length), generator=gen)
             labels = torch.full_like(ids, ignore_index)
             labels[:, :-1] = ids[:, 1:]
-            batch.append((_maybe_pin(_shard(ids, dp_rank, dp_size), pin_memory),
-                          _maybe_pin(_shard(labels, dp_rank, dp_size), pin_memory)))
+            batch.append((_maybe_pin(_shard(ids, dp_rank, dp_size, cp_rank, cp_size), pin_memory),
+                          _maybe_pin(_shard(labels, dp_rank, dp_size, cp_rank, cp_size), pin_memory)))
         yield batch
         b += 1

@@ -67,11 +67,12 @@ class SyntheticDataLoader(DataLoader[Tuple[torch.Tensor, torch.Tensor]]):
     """Endless synthetic token stream with resumable state (``train_transformer.py:50-99`` of the reference)."""
 
     def __init__(self, seed: int, *, kind: str, vocab_size: int, sequence_length: int, global_microbatch_instances: int,
-                 num_microbatches: int, dp_rank: int, dp_size: int, num_batches: Optional[int] = None):
+                 num_microbatches: int, dp_rank: int, dp_size: int, cp_rank: int = 0, cp_size: int = 1,
+                 num_batches: Optional[int] = None):
         self.seed, self.kind = seed, kind
         self.kw = dict(vocab_size=vocab_size, sequence_length=sequence_length,
                        global_microbatch_instances=global_microbatch_instances, num_microbatches=num_microbatches,
-                       dp_rank=dp_rank, dp_size=dp_size)
+                       dp_rank=dp_rank, dp_size=dp_size, cp_rank=cp_rank, cp_size=cp_size)
         self.num_batches = num_batches
         self.batches_processed = 0
         self.epoch = 0
@@ -114,16 +115,14 @@ def build_mesh(mesh_type: str, world: int, local: int, shard_degree: Optional[in
 def train(config: IntegrationTestConfig) -> Trainer:
     mesh = config.mesh.build()
     set_mesh(mesh)
-    if mesh.cp.size > 1:
-        raise NotImplementedError("context-parallel meshes are declared but ring / all-gather attention is not built yet")
     seq = config.sequence_length
     if config.local_microbatch_size % seq != 0:
         raise ValueError("local_microbatch_size (tokens) must be a multiple of sequence_length")
     instances_local = config.local_microbatch_size // seq
     dp = mesh.data_parallel_size
-    # under TP the ranks of a TP group consume the same data; their instances are pooled so the group still
-    # processes local_microbatch_size tokens per device
-    instances_per_dp_rank = instances_local * mesh.tp.size
+    # the ranks of a TP or CP group consume the same instances; their instances are pooled so that every device still
+    # processes local_microbatch_size tokens
+    instances_per_dp_rank = instances_local * mesh.tp.size * mesh.cp.size
     global_tokens = instances_per_dp_rank * dp * seq * config.num_microbatches
     dist_utils.barrier("pre-model-init")
     model = config.model.build(seed=fold_in(config.seed, 1), mesh=mesh, param_dtype=config.param_dtype,
@@ -146,7 +145,7 @@ def train(config: IntegrationTestConfig) -> Trainer:
     loader = SyntheticDataLoader(
         fold_in(config.seed, 2), kind=config.data, vocab_size=config.model.vocab_size, sequence_length=seq,
         global_microbatch_instances=instances_per_dp_rank * dp, num_microbatches=config.num_microbatches,
-        dp_rank=mesh.data_parallel_rank, dp_size=dp,
+        dp_rank=mesh.data_parallel_rank, dp_size=dp, cp_rank=mesh.cp.rank, cp_size=mesh.cp.size,
     )
     trainer.fit(model, loader, load_path=config.load_path, buffer_cache=cache)
     return trainer

@@ -2,7 +2,9 @@
 Multi-head self-attention (``olmax/nn/attention.py:1-376``): separate q/k/v/o projections, optional QK-norm (over the
 full projection or per head), RoPE on q and k, causal flash attention with grouped KV heads, optional sliding window
 and logit soft-cap.  Under tensor parallelism the heads are split over the TP axis (q/k/v colwise, o rowwise) and the
-block runs between a sequence all-gather and a sequence reduce-scatter.
+block runs between a sequence all-gather and a sequence reduce-scatter.  Under context parallelism every rank holds
+two chunks of each sequence (``parallel/context.py``): RoPE uses the chunks' positions and the attention kernel is
+replaced by the all-gather or ring composition of rectangular flash-attention blocks.
 """
 
 from __future__ import annotations
@@ -15,6 +17,7 @@ import torch
 
 from ..ops import functional as F
 from ..parallel import collectives as coll
+from ..parallel.context import CPStrategy, context_parallel_attention
 from ..parallel.mesh import TPStyle
 from ..types import StrEnum
 from .linear import Linear
@@ -39,16 +42,22 @@ class AttentionKernel(torch.nn.Module):
     """Scaled-dot-product attention on ``[B, S, H, D]`` tensors (``olmax/nn/attention.py:23-109``)."""
 
     def __init__(self, head_dim: int, window_size: Optional[int] = None, logit_softcap: Optional[float] = None,
-                 implementation: Optional[AttentionImplementation] = None):
+                 implementation: Optional[AttentionImplementation] = None, cp_strategy: Optional[str] = None,
+                 cp_group=None):
         super().__init__()
         self.head_dim = head_dim
         self.window_size = window_size
         self.logit_softcap = logit_softcap
         self.implementation = AttentionImplementation.flash_sm100
+        self.cp_strategy = CPStrategy(cp_strategy) if cp_strategy is not None else CPStrategy.default
+        self.cp_group = cp_group
         self.scale = 1.0 / math.sqrt(head_dim)
 
     def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
         window = self.window_size if self.window_size is not None else -1
+        if self.cp_group is not None and self.cp_group.size > 1:
+            return context_parallel_attention(q, k, v, self.cp_group, strategy=self.cp_strategy, window=window,
+                                              softcap=self.logit_softcap or 0.0, scale=self.scale)
         return F.attention(q, k, v, causal=True, window=window, softcap=self.logit_softcap or 0.0, scale=self.scale)
 
 
@@ -66,6 +75,7 @@ class MultiheadSelfAttention(Module):
         window_size: Optional[int] = None,
         logit_softcap: Optional[float] = None,
         init_std: float = 0.02,
+        cp_strategy: Optional[str] = None,
     ):
         super().__init__()
         ctx = current_build_context()
@@ -74,6 +84,8 @@ class MultiheadSelfAttention(Module):
         self.n_kv_heads = n_kv_heads or n_heads
         self.head_dim = head_dim or d_model // n_heads
         tp = self.mesh.tp.size
+        if tp > 1 and self.mesh.cp.size > 1:
+            raise ValueError("tensor parallelism and context parallelism cannot be combined")
         if self.n_heads % tp or self.n_kv_heads % tp:
             raise ValueError(f"heads ({self.n_heads}/{self.n_kv_heads}) must be divisible by the TP degree {tp}")
         self.local_heads = self.n_heads // tp
@@ -100,7 +112,8 @@ class MultiheadSelfAttention(Module):
             with ctx.scope("k_norm"):
                 self.k_norm = qk_norm.build(kn)
         self.rope = rope.build(self.head_dim) if rope is not None else None
-        self.sdpa = AttentionKernel(self.head_dim, window_size=window_size, logit_softcap=logit_softcap)
+        self.sdpa = AttentionKernel(self.head_dim, window_size=window_size, logit_softcap=logit_softcap,
+                                    cp_strategy=cp_strategy, cp_group=self.mesh.cp)
 
     def forward(self, x: torch.Tensor, batch_size: int, cache: Optional[BufferCache] = None) -> torch.Tensor:
         """x: [tokens, d_model] (tokens = batch * seq, or that divided by tp under sequence parallelism)."""
@@ -120,8 +133,9 @@ class MultiheadSelfAttention(Module):
         k = k.view(batch_size, S, self.local_kv_heads, self.head_dim)
         v = v.view(batch_size, S, self.local_kv_heads, self.head_dim)
         if self.rope is not None:
-            q = self.rope(q, cache)
-            k = self.rope(k, cache)
+            cp = self.mesh.cp
+            q = self.rope(q, cache, cp.size, cp.rank)
+            k = self.rope(k, cache, cp.size, cp.rank)
         o = self.sdpa(q, k, v).reshape(T, self.local_heads * self.head_dim)
         y = self.o_proj(o)
         return coll.seq_reduce_scatter(y, tp)
@@ -139,10 +153,12 @@ class MultiheadSelfAttentionConfig:
     window_size: Optional[int] = None
     logit_softcap: Optional[float] = None
     implementation: Optional[AttentionImplementation] = None
+    cp_strategy: Optional[str] = None
+    """``default`` / ``all_gather`` / ``ring`` (``olmax/nn/attention.py:29``); only read on a mesh with a CP axis."""
 
     def build(self, d_model: int, window_size: Optional[int] = "inherit", init_std: float = 0.02) -> MultiheadSelfAttention:
         return MultiheadSelfAttention(
             d_model, self.n_heads, self.n_kv_heads, self.head_dim, self.bias, self.rope, self.qk_norm,
             self.use_head_qk_norm, self.window_size if window_size == "inherit" else window_size, self.logit_softcap,
-            init_std=init_std,
+            init_std=init_std, cp_strategy=self.cp_strategy,
         )

@@ -31,9 +31,28 @@ class RotaryPositionalEmbedding(torch.nn.Module):
             cache[key] = (cos, sin)
         return cos, sin
 
-    def forward(self, x: torch.Tensor, cache: Optional[BufferCache] = None) -> torch.Tensor:
-        """x: [B, S, H, D]."""
-        cos, sin = self.get_tables(x.shape[1], x.device, cache)
+    def get_local_tables(self, local_len: int, cp_size: int, cp_rank: int, device,
+                         cache: Optional[BufferCache] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Rows of the full-sequence tables at the positions a context-parallel rank holds
+        (``olmax/nn/rope.py:135-143``)."""
+        from ..parallel.context import cp_local_positions
+
+        key = (self.head_dim, local_len, self.theta, str(device), cp_size, cp_rank)
+        if cache is not None and key in cache:
+            return cache[key]
+        cos, sin = self.get_tables(local_len * cp_size, device, cache)
+        pos = cp_local_positions(local_len * cp_size, cp_size, cp_rank, device=cos.device)
+        out = (cos.index_select(0, pos).contiguous(), sin.index_select(0, pos).contiguous())
+        if cache is not None:
+            cache[key] = out
+        return out
+
+    def forward(self, x: torch.Tensor, cache: Optional[BufferCache] = None, cp_size: int = 1, cp_rank: int = 0) -> torch.Tensor:
+        """x: [B, S, H, D] (S = this rank's tokens under context parallelism)."""
+        if cp_size > 1:
+            cos, sin = self.get_local_tables(x.shape[1], cp_size, cp_rank, x.device, cache)
+        else:
+            cos, sin = self.get_tables(x.shape[1], x.device, cache)
         return F.rope(x, cos, sin)
 
 

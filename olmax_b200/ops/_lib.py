@@ -180,4 +180,5 @@ class ObAttnArgs(ctypes.Structure):
         + [("B", ctypes.c_int), ("S", ctypes.c_int), ("H", ctypes.c_int), ("Hkv", ctypes.c_int), ("D", ctypes.c_int)]
         + [("causal", ctypes.c_int), ("window", ctypes.c_int), ("scale", ctypes.c_float), ("softcap", ctypes.c_float)]
         + [("status", ctypes.c_void_p)]
+        + [("Sk", ctypes.c_int), ("q_off", ctypes.c_int)]
     )

@@ -393,6 +393,26 @@ def attention(q, k, v, causal: bool = True, window: int = -1, softcap: float = 0
     return _AttentionFn.apply(q, k, v, causal, window if window is not None else -1, softcap or 0.0, scale)
 
 
+def attention_block_fwd(q, k, v, *, q_off: int = 0, causal: bool = True, window: int = -1, softcap: float = 0.0,
+                        scale: Optional[float] = None):
+    """One (query block, key block) pair without autograd: q [B,S,H,D], k/v [B,Sk,Hkv,D], query row i at key-axis
+    position ``q_off + i`` -> (o [B,S,H,D], lse [B,H,S] fp32).  Building block of context-parallel attention."""
+    if _on_gpu(q):
+        return K.flash_attn_fwd(q, k, v, causal=causal, window=window, softcap=softcap, scale=scale, q_off=q_off)
+    return ref.attention(q, k, v, causal, window, softcap, scale, q_off=q_off)
+
+
+def attention_block_bwd(q, k, v, o, lse, d_o, *, q_off: int = 0, causal: bool = True, window: int = -1,
+                        softcap: float = 0.0, scale: Optional[float] = None):
+    """Gradients (dq, dk, dv) of one block pair given the row statistics ``lse`` and the output ``o`` of the WHOLE
+    softmax row (so the blocks of a ring add up to the full gradient)."""
+    if _on_gpu(q):
+        d_o = d_o if d_o.stride(-1) == 1 else d_o.contiguous()
+        return K.flash_attn_bwd(q, k, v, o, lse, d_o, causal=causal, window=window, softcap=softcap, scale=scale,
+                                q_off=q_off)
+    return ref.attention_bwd(q, k, v, o, lse, d_o, causal, window, softcap, scale, q_off=q_off)
+
+
 # ----------------------------------------------------------------------------------------------------------------------
 # Embedding
 # ----------------------------------------------------------------------------------------------------------------------

@@ -165,8 +165,9 @@ def _set_bshd(args: ObAttnArgs, field: str, t: torch.Tensor, prefix: Optional[st
     setattr(args, prefix + "_sh", t.stride(2))
 
 
-def flash_attn_fwd(q, k, v, *, causal=True, window=-1, softcap=0.0, scale=None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """q [B,S,H,128], k/v [B,S,Hkv,128] -> (o [B,S,H,128] bf16, lse [B,H,S] fp32)."""
+def flash_attn_fwd(q, k, v, *, causal=True, window=-1, softcap=0.0, scale=None, q_off=0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """q [B,S,H,128], k/v [B,Sk,Hkv,128] -> (o [B,S,H,128] bf16, lse [B,H,S] fp32).  Query row i sits at position
+    ``q_off + i`` of the key axis (rectangular problems of context-parallel / blockwise attention)."""
     _req_bf16(q, k, v)
     B, S, H, D = q.shape
     o = torch.empty((B, S, H, D), dtype=torch.bfloat16, device=q.device)
@@ -179,6 +180,7 @@ def flash_attn_fwd(q, k, v, *, causal=True, window=-1, softcap=0.0, scale=None) 
     a.lse = lse.data_ptr()
     a.B, a.S, a.H, a.Hkv, a.D = B, S, H, k.shape[2], D
     a.causal, a.window = int(causal), int(window)
+    a.Sk, a.q_off = k.shape[1], int(q_off)
     a.scale = scale if scale is not None else 1.0 / math.sqrt(D)
     a.softcap = float(softcap)
     a.status = status_buffer(q.device).data_ptr()
@@ -188,7 +190,7 @@ def flash_attn_fwd(q, k, v, *, causal=True, window=-1, softcap=0.0, scale=None) 
 
 
 def flash_attn_bwd(q, k, v, o, lse, d_o, *, causal=True, window=-1, softcap=0.0, scale=None,
-                   dq=None, dk=None, dv=None):
+                   dq=None, dk=None, dv=None, q_off=0):
     _req_bf16(q, k, v, o, d_o)
     B, S, H, D = q.shape
     dq = torch.empty_like(q) if dq is None else dq
@@ -210,6 +212,7 @@ def flash_attn_bwd(q, k, v, o, lse, d_o, *, causal=True, window=-1, softcap=0.0,
     a.dq_accum = acc.data_ptr()
     a.B, a.S, a.H, a.Hkv, a.D = B, S, H, k.shape[2], D
     a.causal, a.window = int(causal), int(window)
+    a.Sk, a.q_off = k.shape[1], int(q_off)
     a.scale = scale if scale is not None else 1.0 / math.sqrt(D)
     a.softcap = float(softcap)
     a.status = status_buffer(q.device).data_ptr()

@@ -74,8 +74,9 @@ def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
 
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True, window: int = -1,
-              logit_softcap: float = 0.0, scale: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """q [B,S,H,D], k/v [B,S,Hkv,D] -> (o [B,S,H,D], lse [B,H,S]).  window >= 0 keeps keys j >= i - window."""
+              logit_softcap: float = 0.0, scale: Optional[float] = None, q_off: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """q [B,S,H,D], k/v [B,Sk,Hkv,D] -> (o [B,S,H,D], lse [B,H,S]).  Query row i sits at position ``q_off + i`` of the
+    key axis; window >= 0 keeps keys j >= position - window."""
     B, S, H, D = q.shape
     Hkv = k.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
@@ -85,7 +86,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = 
     s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
     s = softcap(s, logit_softcap)
     Sk = k.shape[1]
-    i = torch.arange(S, device=q.device).view(S, 1)
+    i = torch.arange(S, device=q.device).view(S, 1) + q_off
     j = torch.arange(Sk, device=q.device).view(1, Sk)
     mask = torch.ones(S, Sk, dtype=torch.bool, device=q.device)
     if causal:
@@ -97,6 +98,44 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = 
     p = torch.softmax(s, dim=-1)
     o = torch.matmul(p, vf).permute(0, 2, 1, 3)
     return o.to(q.dtype), lse
+
+
+def attention_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, lse: torch.Tensor,
+                  d_o: torch.Tensor, causal: bool = True, window: int = -1, logit_softcap: float = 0.0,
+                  scale: Optional[float] = None, q_off: int = 0) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Gradients of one (query block, key block) pair of a softmax whose row statistics are given: ``lse`` [B,H,S] is
+    the log-sum-exp over ALL keys of the row (not only this block's) and ``o`` the final output, so the pieces of a
+    blockwise / ring attention add up to the gradient of the whole."""
+    B, S, H, D = q.shape
+    Hkv, Sk = k.shape[2], k.shape[1]
+    G = H // Hkv
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(G, dim=1)
+    dof = d_o.float().permute(0, 2, 1, 3)
+    raw = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    s = softcap(raw, logit_softcap)
+    i = torch.arange(S, device=q.device).view(S, 1) + q_off
+    j = torch.arange(Sk, device=q.device).view(1, Sk)
+    mask = torch.ones(S, Sk, dtype=torch.bool, device=q.device)
+    if causal:
+        mask &= j <= i
+    if window is not None and window >= 0:
+        mask &= j >= i - window
+    p = torch.exp(s - lse.float().unsqueeze(-1)).masked_fill(~mask, 0.0)
+    delta = (o.float() * d_o.float()).sum(-1).permute(0, 2, 1).unsqueeze(-1)   # [B,H,S,1]
+    dv = torch.matmul(p.transpose(-1, -2), dof)
+    dp = torch.matmul(dof, vf.transpose(-1, -2))
+    ds = p * (dp - delta)
+    if logit_softcap and logit_softcap > 0:
+        ds = ds * (1.0 - torch.tanh(raw / logit_softcap) ** 2)
+    ds = ds * scale
+    dq = torch.matmul(ds, kf).permute(0, 2, 1, 3)
+    dk = torch.matmul(ds.transpose(-1, -2), qf)
+    dk = dk.view(B, Hkv, G, Sk, D).sum(2).permute(0, 2, 1, 3)
+    dv = dv.view(B, Hkv, G, Sk, D).sum(2).permute(0, 2, 1, 3)
+    return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
 
 
 def activation(name: str, x: torch.Tensor) -> torch.Tensor:

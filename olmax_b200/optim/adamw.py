@@ -47,8 +47,9 @@ class AdamW:
     def update_grad_scale(self) -> None:
         """Every gradient contribution is scaled by 1 / (ranks whose losses are averaged x micro-batches)."""
         mesh = self.store.mesh
-        ranks = mesh.world_size // mesh.cp.size
-        self.store.set_grad_scale(1.0 / (ranks * self.num_microbatches))
+        # every rank (data, tensor and context parallel alike) reports the mean loss of its own tokens and the
+        # gradient contributions of all ranks are summed, so the divisor is the whole job
+        self.store.set_grad_scale(1.0 / (mesh.world_size * self.num_microbatches))
 
     def accumulate(self) -> bool:
         """Call after each micro-batch's backward.  Returns True when the optimizer step is due."""

@@ -10,7 +10,7 @@ import torch
 from olmax_b200.testing import run_distributed_test
 
 
-def _model(mesh_resource, seed=0, layer="default", tie=False, kv=None):
+def _model(mesh_resource, seed=0, layer="default", tie=False, kv=None, cp_strategy=None, window=None, softcap=None):
     from olmax_b200.models import (DefaultTransformerConfig, DefaultTransformerLayerConfig, GemmaTransformerLayerConfig,
                                    ReorderedNormTransformerLayerConfig)
     from olmax_b200.nn import MultiheadSelfAttentionConfig, RMSNormConfig
@@ -18,17 +18,19 @@ def _model(mesh_resource, seed=0, layer="default", tie=False, kv=None):
     layer_cls = {"default": DefaultTransformerLayerConfig, "reordered_norm": ReorderedNormTransformerLayerConfig,
                  "gemma": GemmaTransformerLayerConfig}[layer]
     attn = MultiheadSelfAttentionConfig(n_heads=4, n_kv_heads=kv, head_dim=16,
-                                        qk_norm=RMSNormConfig() if layer != "default" else None, use_head_qk_norm=True)
+                                        qk_norm=RMSNormConfig() if layer != "default" else None, use_head_qk_norm=True,
+                                        cp_strategy=cp_strategy, window_size=window, logit_softcap=softcap)
     cfg = DefaultTransformerConfig(vocab_size=64, d_model=64, hidden_size=96, num_layers=2, layer=layer_cls(attention=attn),
                                    tie_embeddings=tie, scale_embeddings=tie, ce_chunk_rows=16)
     return cfg.build(seed=seed, mesh_resource=mesh_resource)
 
 
-def _global_batch():
+def _global_batch(ignore_last=True):
     g = torch.Generator().manual_seed(123)
     ids = torch.randint(0, 64, (8, 16), generator=g)
     labels = torch.roll(ids, -1, 1)
-    labels[:, -1] = -100
+    if ignore_last:
+        labels[:, -1] = -100
     return ids, labels
 
 
@@ -89,6 +91,81 @@ def test_sharded_model_matches_single_process(mesh_kind, world, layer, tie, kv):
             assert torch.allclose(grads[n], want_grads[n], rtol=1e-3, atol=1e-6), n
     if mesh_kind == "fsdp":
         assert results[0][3]["all_gather_bytes"] > 0 and results[0][3]["reduce_scatter_bytes"] > 0
+
+
+def _cp_reference(layer, kv, window, softcap):
+    from olmax_b200.parallel import MeshResource
+
+    model = _model(MeshResource.FSDP(1), layer=layer, kv=kv, window=window, softcap=softcap)
+    ids, labels = _global_batch(ignore_last=False)
+    model.store.set_grad_scale(1.0)
+    loss, _ = model(ids, labels)
+    loss.backward()
+    model.store.finish_backward()
+    return loss.item(), {n: model.store.full_gradient(n) for n, _ in model.store.named_parameters()}
+
+
+def _cp_worker(mesh_kind, cp, strategy, layer, kv, window, softcap):
+    import torch.distributed as dist
+
+    from olmax_b200.parallel import MeshResource, dist_utils
+    from olmax_b200.parallel.context import shard_sequence_for_cp
+
+    world = dist_utils.get_world_size()
+    res = MeshResource.FSDP_with_CP(world, cp) if mesh_kind == "fsdp_cp" else MeshResource.HSDP_with_CP(2, world, 2)
+    model = _model(res, layer=layer, kv=kv, cp_strategy=strategy, window=window, softcap=softcap)
+    mesh = model.mesh
+    assert mesh.cp.size == cp
+    ids, labels = _global_batch(ignore_last=False)   # equal token counts on every rank: mean of means = global mean
+    dp, r = mesh.data_parallel_size, mesh.data_parallel_rank
+    per = ids.shape[0] // dp
+    local_ids = shard_sequence_for_cp(ids[r * per : (r + 1) * per], cp, mesh.cp.rank)
+    local_labels = shard_sequence_for_cp(labels[r * per : (r + 1) * per], cp, mesh.cp.rank)
+    model.store.set_grad_scale(1.0 / world)
+    loss, _ = model(local_ids, local_labels)
+    loss.backward()
+    model.store.finish_backward()
+    model.store.reduce_replicated_grads()
+    t = loss.detach().clone()
+    dist.all_reduce(t, group=dist_utils.control_group())
+    return (t / world).item(), {n: model.store.full_gradient(n) for n, _ in model.store.named_parameters()}
+
+
+@pytest.mark.parametrize("mesh_kind,world,cp,strategy,layer,kv,window,softcap", [
+    ("fsdp_cp", 2, 2, "all_gather", "default", None, None, None),
+    ("fsdp_cp", 2, 2, "ring", "reordered_norm", 2, None, 20.0),
+    ("fsdp_cp", 4, 2, "ring", "default", None, None, None),          # batch 2 x context 2
+    ("fsdp_cp", 4, 4, "ring", "gemma", 2, None, None),
+    ("fsdp_cp", 4, 4, "all_gather", "default", 2, 5, None),          # sliding window narrower than a chunk pair
+    ("fsdp_cp", 2, 2, "ring", "default", None, 5, None),             # ring with a narrow window falls back to all-gather
+    ("hsdp_cp", 4, 2, "all_gather", "default", None, None, None),    # CP over the shard axis of an HSDP mesh
+])
+def test_context_parallel_matches_single_process(mesh_kind, world, cp, strategy, layer, kv, window, softcap):
+    want_loss, want_grads = _cp_reference(layer, kv, window, softcap)
+    results = run_distributed_test(_cp_worker, world_size=world,
+                                   func_args=(mesh_kind, cp, strategy, layer, kv, window, softcap))
+    for loss, grads in results:
+        assert loss == pytest.approx(want_loss, rel=1e-5)
+        for n in want_grads:
+            assert torch.allclose(grads[n], want_grads[n], rtol=1e-3, atol=1e-6), n
+
+
+def test_dual_chunk_swap_reordering():
+    from olmax_b200.parallel.context import (cp_local_positions, inverse_reorder_causal_load_balancing,
+                                             reorder_causal_load_balancing, shard_sequence_for_cp)
+
+    x = torch.arange(2 * 16).view(2, 16)
+    y = reorder_causal_load_balancing(x, 2, seq_dim=1)
+    assert y[0].tolist() == [0, 1, 2, 3, 12, 13, 14, 15, 4, 5, 6, 7, 8, 9, 10, 11]
+    assert torch.equal(inverse_reorder_causal_load_balancing(y, 2, seq_dim=1), x)
+    for r in range(2):
+        assert torch.equal(shard_sequence_for_cp(x, 2, r), y.chunk(2, dim=1)[r])
+        assert torch.equal(cp_local_positions(16, 2, r), y[0].chunk(2)[r])
+    # every rank gets the same amount of causal work: sum of (position + 1) over its tokens
+    work = [int((cp_local_positions(64, 4, r) + 1).sum()) for r in range(4)]
+    assert len(set(work)) == 1
+    with pytest.raises(ValueError):
+        reorder_causal_load_balancing(torch.zeros(1, 6), 2, seq_dim=1)
 
 
 def _collectives_worker():

@@ -161,8 +161,13 @@ def _tp_worker(mesh_kind):
 
     world, rank = dist_utils.get_world_size(), dist_utils.get_rank()
     dev = torch.device("cuda", rank)
-    res = MeshResource.FSDP_with_TP(2, world) if mesh_kind == "tp" else MeshResource.FSDP(world)
-    attn = MultiheadSelfAttentionConfig(n_heads=4, n_kv_heads=2, head_dim=128, logit_softcap=50.0)
+    from olmax_b200.parallel.context import shard_sequence_for_cp
+
+    res = {"tp": lambda: MeshResource.FSDP_with_TP(2, world), "fsdp": lambda: MeshResource.FSDP(world),
+           "cp_ring": lambda: MeshResource.FSDP_with_CP(world, 2), "cp_all_gather": lambda: MeshResource.FSDP_with_CP(world, 2),
+           }[mesh_kind]()
+    attn = MultiheadSelfAttentionConfig(n_heads=4, n_kv_heads=2, head_dim=128, logit_softcap=50.0,
+                                        cp_strategy=mesh_kind[3:] if mesh_kind.startswith("cp_") else None)
     cfg = DefaultTransformerConfig(vocab_size=4096, d_model=512, hidden_size=1024, num_layers=2,
                                    layer=GemmaTransformerLayerConfig(attention=attn), lm_head=LMHeadConfig(logit_softcap=30.0),
                                    tie_embeddings=True, scale_embeddings=True, sliding_window=128, sliding_window_pattern=2,
@@ -176,8 +181,12 @@ def _tp_worker(mesh_kind):
     for step in range(3):
         ids = torch.randint(0, 4096, (4, 256), generator=gen)      # the same global batch on every rank
         per = 4 // mesh.data_parallel_size
-        mine = ids[mesh.data_parallel_rank * per : (mesh.data_parallel_rank + 1) * per].to(dev)
-        loss, _ = model(mine, torch.roll(mine, -1, 1), cache)
+        mine = ids[mesh.data_parallel_rank * per : (mesh.data_parallel_rank + 1) * per]
+        labels = torch.roll(mine, -1, 1)
+        if mesh.cp.size > 1:   # this rank's two chunks of every sequence
+            mine = shard_sequence_for_cp(mine, mesh.cp.size, mesh.cp.rank)
+            labels = shard_sequence_for_cp(labels, mesh.cp.size, mesh.cp.rank)
+        loss, _ = model(mine.to(dev), labels.to(dev), cache)
         loss.backward()
         optim.accumulate()
         optim.step()
@@ -200,3 +209,18 @@ def test_tensor_parallel_matches_fsdp_on_two_gpus():
     assert all(abs(a - b) < 2e-2 * abs(b) for a, b in zip(lt, lf)), (lt, lf)
     for name in pf:
         assert rel_err(pt[name], pf[name]) < 1e-2, name
+
+
+@pytest.mark.parametrize("strategy", ["all_gather", "ring"])
+def test_context_parallel_matches_fsdp_on_two_gpus(strategy):
+    """Sequences split over 2 GPUs (dual-chunk-swap order; K/V all-gathered or travelling around the ring; the
+    sliding-window layers of the ring run use the all-gather composition) train like plain FSDP."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    cp = run_distributed_test(_tp_worker, world_size=2, backend="nccl", func_args=("cp_" + strategy,), timeout=300)
+    fsdp = run_distributed_test(_tp_worker, world_size=2, backend="nccl", func_args=("fsdp",), timeout=300)
+    lc, pc = cp[0]
+    lf, pf = fsdp[0]
+    assert all(abs(a - b) < 2e-2 * abs(b) for a, b in zip(lc, lf)), (lc, lf)
+    for name in pf:
+        assert rel_err(pc[name], pf[name]) < 1e-2, name

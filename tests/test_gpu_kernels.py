@@ -129,6 +129,86 @@ def test_flash_attention(K, B, S, H, Hkv, causal, window, softcap):
     _check_status()
 
 
+@pytest.mark.parametrize("S,Sk,q_off,window,softcap", [
+    (256, 512, 256, -1, 0.0),      # late query chunk against the causally visible prefix
+    (128, 128, 384, -1, 0.0),      # ring block far below the diagonal: every key visible
+    (256, 640, 384, 300, 0.0),     # sliding window over a left-trimmed prefix
+    (200, 456, 256, -1, 15.0),     # ragged lengths + soft-cap
+])
+def test_flash_attention_rectangular_blocks(K, S, Sk, q_off, window, softcap):
+    """Query rows at key-axis offset ``q_off`` against a key block of another length (context-parallel blocks), read
+    through strided slices of larger tensors as the context-parallel code does."""
+    dev = "cuda"
+    torch.manual_seed(5)
+    B, H, Hkv = 2, 4, 2
+    q_all = torch.randn(B, S + 64, H, 128, device=dev, dtype=torch.bfloat16)
+    k_all = torch.randn(B, Sk + 128, Hkv, 128, device=dev, dtype=torch.bfloat16)
+    v_all = torch.randn(B, Sk + 128, Hkv, 128, device=dev, dtype=torch.bfloat16)
+    q, k, v = q_all[:, 64:], k_all[:, 128:], v_all[:, 128:]
+    qr, kr, vr = (t.float().clone().requires_grad_(True) for t in (q, k, v))
+    o, lse = K.flash_attn_fwd(q, k, v, causal=True, window=window, softcap=softcap, q_off=q_off)
+    o_ref, lse_ref = ref.attention(qr, kr, vr, True, window, softcap, q_off=q_off)
+    assert rel_err(o, o_ref) < 6e-3 and rel_err(lse, lse_ref) < 1e-3
+    d_o = torch.randn_like(o)
+    gq, gk, gv = torch.autograd.grad(o_ref, (qr, kr, vr), d_o.float())
+    dq, dk, dv = K.flash_attn_bwd(q, k, v, o, lse, d_o, causal=True, window=window, softcap=softcap, q_off=q_off)
+    assert rel_err(dq, gq) < 1e-2 and rel_err(dk, gk) < 1e-2 and rel_err(dv, gv) < 1e-2
+    # the explicit block backward of the oracle agrees with autograd (it is the CPU path of context parallelism)
+    rq, rk, rv = ref.attention_bwd(q.float(), k.float(), v.float(), o_ref.detach(), lse_ref.detach(), d_o.float(), True,
+                                   window, softcap, q_off=q_off)
+    assert rel_err(rq, gq) < 1e-4 and rel_err(rk, gk) < 1e-4 and rel_err(rv, gv) < 1e-4
+    _check_status()
+
+
+def test_flash_attention_rejects_unsupported_geometry(K):
+    q = torch.randn(1, 128, 2, 128, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(1, 512, 2, 128, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(Exception):   # keys beyond the last query row's position: no query would see the last tiles
+        K.flash_attn_fwd(q, k, k, causal=True, q_off=0)
+
+
+def test_blockwise_attention_composes_to_full_attention(K):
+    """The two compositions context parallelism uses (prefix blocks; ring blocks merged by log-sum-exp), evaluated
+    for every rank in turn on one GPU, reproduce plain causal attention and its gradients."""
+    from olmax_b200.ops import functional as F
+    from olmax_b200.parallel.context import _merge, _ring_pairs, cp_local_positions
+
+    dev, cp, S, B, H, Hkv = "cuda", 2, 1024, 1, 4, 2
+    c = S // (2 * cp)
+    torch.manual_seed(6)
+    q, k, v = (torch.randn(B, S, h, 128, device=dev, dtype=torch.bfloat16) for h in (H, Hkv, Hkv))
+    d_o = torch.randn_like(q)
+    o_full, lse_full = K.flash_attn_fwd(q, k, v)
+    dq_full, dk_full, dv_full = K.flash_attn_bwd(q, k, v, o_full, lse_full, d_o)
+    local = [cp_local_positions(S, cp, r, device=dev) for r in range(cp)]
+    dq = torch.zeros(q.shape, device=dev)
+    dk, dv = torch.zeros(k.shape, device=dev), torch.zeros(v.shape, device=dev)
+    for r in range(cp):
+        ql = q[:, local[r]]
+        o_acc = torch.zeros(ql.shape, device=dev)
+        lse_acc = torch.full((B, H, 2 * c), float("-inf"), device=dev)
+        for j in range(cp):
+            kl, vl = k[:, local[j]], v[:, local[j]]
+            for qh, kh, dist_c in _ring_pairs(r, j, cp):
+                qs, ks = slice(qh * c, (qh + 1) * c), slice(kh * c, (kh + 1) * c)
+                oo, ll = F.attention_block_fwd(ql[:, qs], kl[:, ks], vl[:, ks], q_off=dist_c * c)
+                o_acc[:, qs], lse_acc[:, :, qs] = _merge(o_acc[:, qs], lse_acc[:, :, qs], oo, ll)
+        assert rel_err(o_acc, o_full[:, local[r]]) < 6e-3
+        assert rel_err(lse_acc, lse_full[:, :, local[r]]) < 1e-3
+        o_l, dol = o_acc.to(torch.bfloat16), d_o[:, local[r]]
+        for j in range(cp):
+            kl, vl = k[:, local[j]], v[:, local[j]]
+            for qh, kh, dist_c in _ring_pairs(r, j, cp):
+                qs, ks = slice(qh * c, (qh + 1) * c), slice(kh * c, (kh + 1) * c)
+                g = F.attention_block_bwd(ql[:, qs], kl[:, ks], vl[:, ks], o_l[:, qs], lse_acc[:, :, qs].contiguous(),
+                                          dol[:, qs], q_off=dist_c * c)
+                dq[:, local[r][qs]] += g[0].float()
+                dk[:, local[j][ks]] += g[1].float()
+                dv[:, local[j][ks]] += g[2].float()
+    assert rel_err(dq, dq_full) < 1e-2 and rel_err(dk, dk_full) < 1e-2 and rel_err(dv, dv_full) < 1e-2
+    _check_status()
+
+
 @pytest.mark.parametrize("rows,d,heads", [(300, 512, 1), (64, 4096, 1), (100, 128, 6)])
 def test_rmsnorm(K, rows, d, heads):
     dev = "cuda"
