@@ -203,6 +203,147 @@ __global__ void __launch_bounds__(NORM_THREADS)
   for (int i = threadIdx.x; i < d; i += NORM_THREADS) atomicAdd(dw + i, dw_part[i] * dw_scale);
 }
 
+// LayerNorm (`olmax/nn/functional.py:30-49`): y = (x - mean) * rstd * w (+ b), statistics over the row in fp32 (the
+// variance is taken around the mean from the registers that hold the row, not as E[x^2] - mean^2).
+template <int TPR>
+__global__ void __launch_bounds__(NORM_THREADS)
+    layernorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ b,
+                         bf16* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                         long long rows, int d, float eps) {
+  __shared__ float red[NORM_THREADS / 32];
+  constexpr int ROWS_PER_BLOCK = NORM_THREADS / TPR;
+  const int sub = threadIdx.x / TPR, tr = threadIdx.x % TPR;
+  const int nvec = d / 8;
+  for (long long row0 = (long long)blockIdx.x * ROWS_PER_BLOCK; row0 < rows; row0 += (long long)gridDim.x * ROWS_PER_BLOCK) {
+    const long long row = row0 + sub;
+    const bool live = row < rows;
+    const long long off = live ? row * (long long)d : 0;
+    float t[MAX_VPT][8];
+    float s1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_VPT; ++i) {
+      const int vi = tr + i * TPR;
+      if (live && vi < nvec) {
+        load8(x + off + vi * 8, t[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s1 += t[i][j];
+      }
+    }
+    const float mean = row_sum<TPR>(s1, red) / (float)d;
+    float s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_VPT; ++i) {
+      const int vi = tr + i * TPR;
+      if (live && vi < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          t[i][j] -= mean;
+          s2 += t[i][j] * t[i][j];
+        }
+      }
+    }
+    const float rstd = rsqrtf(row_sum<TPR>(s2, red) / (float)d + eps);
+    if (live && tr == 0) {
+      mean_out[row] = mean;
+      rstd_out[row] = rstd;
+    }
+#pragma unroll
+    for (int i = 0; i < MAX_VPT; ++i) {
+      const int vi = tr + i * TPR;
+      if (live && vi < nvec) {
+        float wv[8], o[8];
+        if (w != nullptr) load8(w + vi * 8, wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = t[i][j] * rstd * (w != nullptr ? wv[j] : 1.f);
+        if (b != nullptr) {
+          float bv[8];
+          load8(b + vi * 8, bv);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += bv[j];
+        }
+        store8(y + off + vi * 8, o);
+      }
+    }
+  }
+}
+
+// g = w*dy;  dx = rstd * (g - mean(g) - xhat * mean(g*xhat));  dw += scale * sum_rows dy*xhat;  db += scale * sum_rows dy
+template <int TPR>
+__global__ void __launch_bounds__(NORM_THREADS)
+    layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                         const float* __restrict__ mean_in, const float* __restrict__ rstd_in, bf16* __restrict__ dx,
+                         float* __restrict__ dw, float* __restrict__ db, long long rows, int d, float scale) {
+  __shared__ float red[NORM_THREADS / 32];
+  extern __shared__ float part[];  // [2][d] per-block partials of dw and db
+  constexpr int ROWS_PER_BLOCK = NORM_THREADS / TPR;
+  const int sub = threadIdx.x / TPR, tr = threadIdx.x % TPR;
+  const int nvec = d / 8;
+  float dwacc[MAX_VPT][8], dbacc[MAX_VPT][8];
+#pragma unroll
+  for (int i = 0; i < MAX_VPT; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = dbacc[i][j] = 0.f;
+  for (long long row0 = (long long)blockIdx.x * ROWS_PER_BLOCK; row0 < rows; row0 += (long long)gridDim.x * ROWS_PER_BLOCK) {
+    const long long row = row0 + sub;
+    const bool live = row < rows;
+    const long long off = live ? row * (long long)d : 0;
+    const float mean = live ? mean_in[row] : 0.f;
+    const float rstd = live ? rstd_in[row] : 0.f;
+    float g[MAX_VPT][8], xh[MAX_VPT][8];
+    float sg = 0.f, sgx = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_VPT; ++i) {
+      const int vi = tr + i * TPR;
+      if (live && vi < nvec) {
+        float wv[8];
+        load8(dy + off + vi * 8, g[i]);
+        load8(x + off + vi * 8, xh[i]);
+        if (w != nullptr) load8(w + vi * 8, wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = (xh[i][j] - mean) * rstd;
+          dwacc[i][j] += g[i][j] * xh[i][j];
+          dbacc[i][j] += g[i][j];
+          if (w != nullptr) g[i][j] *= wv[j];
+          sg += g[i][j];
+          sgx += g[i][j] * xh[i][j];
+        }
+      }
+    }
+    sg = row_sum<TPR>(sg, red) / (float)d;
+    sgx = row_sum<TPR>(sgx, red) / (float)d;
+#pragma unroll
+    for (int i = 0; i < MAX_VPT; ++i) {
+      const int vi = tr + i * TPR;
+      if (live && vi < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - sg - xh[i][j] * sgx);
+        store8(dx + off + vi * 8, o);
+      }
+    }
+  }
+  if (dw == nullptr && db == nullptr) return;
+  for (int i = threadIdx.x; i < 2 * d; i += NORM_THREADS) part[i] = 0.f;
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < MAX_VPT; ++i) {
+    const int vi = tr + i * TPR;
+    if (vi < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        atomicAdd(&part[vi * 8 + j], dwacc[i][j]);
+        atomicAdd(&part[d + vi * 8 + j], dbacc[i][j]);
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < d; i += NORM_THREADS) {
+    if (dw != nullptr) atomicAdd(dw + i, part[i] * scale);
+    if (db != nullptr) atomicAdd(db + i, part[d + i] * scale);
+  }
+}
+
 // Rotary embedding, rotate-half convention: out = x * cos + rotate_half(x) * sin, cos/sin tables [S, D/2] fp32.
 // sign = +1 forward, -1 backward (the transpose of a rotation).  One thread per 8 elements of the first half.
 __global__ void rope_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, const float* __restrict__ cos_t,
@@ -408,6 +549,51 @@ extern "C" int ob_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
     rmsnorm_bwd_kernel<NORM_THREADS><<<grid, NORM_THREADS, smem, stream>>>(
         (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dsum, (bf16*)dx, dw, rows, d, heads, ld_dy,
         ld_x, ld_dx, dw_scale);
+  }
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                                long long rows, int d, float eps, cudaStream_t stream) {
+  if (d % 8 != 0) OB_FAIL(-1, "layernorm: d (%d) must be a multiple of 8", d);
+  if (mean == nullptr || rstd == nullptr) OB_FAIL(-3, "layernorm: the mean and rstd outputs are required");
+  if (rows <= 0) return 0;
+  if (d <= 512) {
+    constexpr int TPR = 16;
+    const int rpb = NORM_THREADS / TPR;
+    layernorm_fwd_kernel<TPR><<<grid_for((rows + rpb - 1) / rpb, 1), NORM_THREADS, 0, stream>>>(
+        (const bf16*)x, (const bf16*)w, (const bf16*)b, (bf16*)y, mean, rstd, rows, d, eps);
+  } else {
+    if (d > NORM_THREADS * 8 * MAX_VPT) OB_FAIL(-2, "layernorm: d (%d) too large (max %d)", d, NORM_THREADS * 8 * MAX_VPT);
+    layernorm_fwd_kernel<NORM_THREADS><<<grid_for(rows, 1), NORM_THREADS, 0, stream>>>(
+        (const bf16*)x, (const bf16*)w, (const bf16*)b, (bf16*)y, mean, rstd, rows, d, eps);
+  }
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                                void* dx, float* dw, float* db, long long rows, int d, float scale,
+                                cudaStream_t stream) {
+  if (d % 8 != 0) OB_FAIL(-1, "layernorm: d (%d) must be a multiple of 8", d);
+  if (rows <= 0) return 0;
+  const size_t smem = (size_t)2 * d * sizeof(float);
+  if (d <= 512) {
+    constexpr int TPR = 16;
+    const int rpb = NORM_THREADS / TPR;
+    layernorm_bwd_kernel<TPR><<<grid_for((rows + rpb - 1) / rpb, 1, 4), NORM_THREADS, smem, stream>>>(
+        (const bf16*)dy, (const bf16*)x, (const bf16*)w, mean, rstd, (bf16*)dx, dw, db, rows, d, scale);
+  } else {
+    if (d > NORM_THREADS * 8 * MAX_VPT) OB_FAIL(-2, "layernorm: d (%d) too large", d);
+    static bool attr_set = false;   // 2 * d floats of shared memory: up to 64 KB
+    if (!attr_set) {
+      OB_CUDA_OK(cudaFuncSetAttribute(layernorm_bwd_kernel<NORM_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      2 * NORM_THREADS * 8 * MAX_VPT * (int)sizeof(float)));
+      attr_set = true;
+    }
+    layernorm_bwd_kernel<NORM_THREADS><<<grid_for(rows, 1, 4), NORM_THREADS, smem, stream>>>(
+        (const bf16*)dy, (const bf16*)x, (const bf16*)w, mean, rstd, (bf16*)dx, dw, db, rows, d, scale);
   }
   OB_CUDA_OK(cudaGetLastError());
   return 0;

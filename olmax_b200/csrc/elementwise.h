@@ -17,6 +17,12 @@ int ob_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void*
 int ob_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dsum, void* dx,
                    float* dw, long long rows, int d, int heads, long long ld_dy, long long ld_x, long long ld_dx,
                    float dw_scale, cudaStream_t stream);
+// LayerNorm over plain [rows, d] tensors: y = (x - mean) * rstd * w (+ b); w / b may be null.  mean / rstd fp32 [rows].
+int ob_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd, long long rows,
+                     int d, float eps, cudaStream_t stream);
+// dx = rstd * (g - mean(g) - xhat * mean(g * xhat)), g = w * dy; dw / db (fp32, may be null) += scale * column sums
+int ob_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
+                     float* dw, float* db, long long rows, int d, float scale, cudaStream_t stream);
 // rotate-half RoPE on [B, S, H, D] with element strides; cos/sin fp32 [>= S + pos_offset, D/2]; sign -1 = backward
 int ob_rope(const void* x, void* y, const float* cos_t, const float* sin_t, int B, int S, int H, int D, long long sb,
             long long ss, long long sh, long long ysb, long long yss, long long ysh, float sign, int pos_offset,

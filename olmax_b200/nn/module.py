@@ -16,7 +16,7 @@ import torch
 
 from ..parallel.param_store import ParamHandle, ParamStore
 
-__all__ = ["BuildContext", "Module", "current_build_context"]
+__all__ = ["BuildContext", "Module", "current_build_context", "build_module"]
 
 _CTX_STACK: List["BuildContext"] = []
 
@@ -91,3 +91,34 @@ class Module(torch.nn.Module):
 
     def get_checkpoint_names(self) -> List[str]:
         return [m.checkpoint_name for m in self.modules() if isinstance(m, Module) and m.checkpoint_name]
+
+
+def build_module(factory, *, seed: int = 0, mesh=None, mesh_resource=None, param_dtype: torch.dtype = torch.float32,
+                 compute_dtype: Optional[torch.dtype] = None, device: Optional[torch.device] = None,
+                 comm_backend: Optional[str] = None, unit: str = "root"):
+    """
+    Build a single module (or any tree of modules) outside a Transformer: creates a parameter store on ``mesh`` (default:
+    the current mesh, else FSDP over the whole job), runs ``factory()`` inside a build context, initialises the
+    parameters and returns the module.  ``module.store`` gives access to gradients and full parameters, e.g.::
+
+        lin = build_module(lambda: Linear(64, 32))
+        y = lin(x); y.sum().backward(); lin.store.finish_backward()
+        dw = lin.store.full_gradient("weight")
+    """
+    from ..parallel import dist_utils
+    from ..parallel.mesh import MeshResource, get_mesh
+
+    if mesh is None:
+        mesh = get_mesh() if mesh_resource is None else None
+    if mesh is None:
+        resource = mesh_resource or MeshResource.FSDP(dist_utils.get_world_size())
+        mesh = resource.build(device=device)
+    device = torch.device(device) if device is not None else mesh.device
+    if compute_dtype is None:
+        compute_dtype = torch.bfloat16 if device.type == "cuda" else param_dtype
+    store = ParamStore(mesh, param_dtype=param_dtype, compute_dtype=compute_dtype, device=device,
+                       comm_backend=comm_backend)
+    with BuildContext(store, unit=unit):
+        module = factory()
+    store.finalize(seed=seed)
+    return module

@@ -1,6 +1,6 @@
 """
 Normalisation layers and their config (``olmax/nn/normalization.py:1-152``).  RMSNorm runs on the fused kernel with
-optional residual fusion; LayerNorm is provided for completeness through the PyTorch restatement.
+optional residual fusion; LayerNorm has its own forward / backward kernels (residual adds stay ordinary tensor ops).
 """
 
 from __future__ import annotations
@@ -46,8 +46,7 @@ class LayerNorm(Normalizer):
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, mode: Optional[str] = None,
                 heads: int = 1):
-        raise NotImplementedError(
-            "LayerNorm has no fused kernel yet; every recipe uses RMSNorm (use ops.reference.layer_norm for analysis)")
+        return F.layer_norm(x, self.weight, self.bias, self.eps, residual, mode, heads)
 
 
 @dataclass

@@ -21,7 +21,8 @@ from . import kernels as K
 from . import reference as ref
 
 __all__ = [
-    "linear", "gated_mlp", "rms_norm", "rope", "attention", "embedding", "linear_cross_entropy", "glu",
+    "linear", "gated_mlp", "rms_norm", "layer_norm", "rope", "attention", "attention_block_fwd", "attention_block_bwd",
+    "embedding", "linear_cross_entropy", "glu",
 ]
 
 
@@ -326,6 +327,80 @@ def rms_norm(x: torch.Tensor, handle, eps: float = 1e-5, residual: Optional[torc
     if mode is None:
         residual = None
     return _RMSNormFn.apply(x, residual, handle, eps, mode, heads)
+
+
+class _LayerNormFn(torch.autograd.Function):
+    """y = (x - mean) * rstd * w (+ b) over the last dimension (``olmax/nn/functional.py:30-49``)."""
+
+    @staticmethod
+    def forward(ctx, x, w_handle, b_handle, eps):
+        shp = x.shape
+        d = shp[-1]
+        w = w_handle.full() if w_handle is not None else None
+        b = b_handle.full() if b_handle is not None else None
+        ctx.handles, ctx.eps, ctx.shape = (w_handle, b_handle), eps, shp
+        if _on_gpu(x):
+            xc = x.contiguous()
+            rows = xc.numel() // d
+            y = torch.empty_like(xc)
+            mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+            rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+            K.layernorm_fwd(xc, w, b, y, mean, rstd, rows=rows, d=d, eps=eps)
+            ctx.save_for_backward(xc, mean, rstd, *([w] if w is not None else []))
+            return y
+        ctx.save_for_backward(x, *([w] if w is not None else []), *([b] if b is not None else []))
+        return ref.layer_norm(x, w, b, eps)
+
+    @staticmethod
+    def backward(ctx, dy):
+        w_handle, b_handle = ctx.handles
+        d = ctx.shape[-1]
+        if _on_gpu(dy):
+            x, mean, rstd = ctx.saved_tensors[:3]
+            w = ctx.saved_tensors[3] if w_handle is not None else None
+            dyc = dy.contiguous()
+            rows = dyc.numel() // d
+            dx = torch.empty_like(dyc)
+            dw = torch.zeros(d, dtype=torch.float32, device=dy.device) if w_handle is not None else None
+            db = torch.zeros(d, dtype=torch.float32, device=dy.device) if b_handle is not None else None
+            K.layernorm_bwd(dyc, x, w, mean, rstd, dx, rows=rows, d=d, dw=dw, db=db)
+            if dw is not None:
+                w_handle.add_grad(dw)
+            if db is not None:
+                b_handle.add_grad(db)
+            return dx.view(ctx.shape), None, None, None
+        saved = list(ctx.saved_tensors)
+        x = saved.pop(0)
+        with torch.enable_grad():
+            xx = x.detach().requires_grad_(True)
+            ww = saved.pop(0).detach().requires_grad_(True) if w_handle is not None else None
+            bb = saved.pop(0).detach().requires_grad_(True) if b_handle is not None else None
+            y = ref.layer_norm(xx, ww, bb, ctx.eps)
+        leaves = [t for t in (xx, ww, bb) if t is not None]
+        grads = list(torch.autograd.grad(y, leaves, dy))
+        dx = grads.pop(0)
+        if ww is not None:
+            w_handle.add_grad(grads.pop(0))
+        if bb is not None:
+            b_handle.add_grad(grads.pop(0))
+        return dx, None, None, None
+
+
+def layer_norm(x: torch.Tensor, weight, bias, eps: float = 1e-5, residual: Optional[torch.Tensor] = None,
+               mode: Optional[str] = None, heads: int = 1):
+    """LayerNorm with the calling convention of :func:`rms_norm`: ``mode`` None: norm(x); ``post``: residual + norm(x);
+    ``pre``: returns (x + residual, norm(x + residual)).  ``heads > 1`` normalises every head separately.  The residual
+    adds are ordinary tensor ops (no recipe uses LayerNorm on the residual stream)."""
+    if mode == "pre":
+        x = x + residual
+    shp = x.shape
+    xv = x.reshape(-1, shp[-1] // heads) if heads > 1 else x
+    y = _LayerNormFn.apply(xv, weight, bias, eps).reshape(shp)
+    if mode == "pre":
+        return x, y
+    if mode == "post":
+        return residual + y
+    return y
 
 
 # ----------------------------------------------------------------------------------------------------------------------

@@ -51,6 +51,8 @@ _f = ctypes.c_float
 
 register_signature("ob_rmsnorm_fwd", [_vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _ll, _ll, _ll, _i, _f, _vp])
 register_signature("ob_rmsnorm_bwd", [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _ll, _ll, _ll, _f, _vp])
+register_signature("ob_layernorm_fwd", [_vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _f, _vp])
+register_signature("ob_layernorm_bwd", [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _f, _vp])
 register_signature("ob_rope", [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp])
 register_signature("ob_glu_fwd", [_vp, _vp, _vp, _ll, _i, _vp])
 register_signature("ob_glu_bwd", [_vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _vp])
@@ -237,6 +239,21 @@ def rmsnorm_bwd(dy, x, w, rstd, dx, *, rows, d, dw=None, dsum=None, heads=1, ld_
                                _ptr(dw), rows, d, heads, ld_dy if ld_dy is not None else d,
                                ld_x if ld_x is not None else d, ld_dx if ld_dx is not None else d, dw_scale,
                                stream_ptr(x.device)), "rmsnorm_bwd")
+    _count()
+
+
+def layernorm_fwd(x, w, b, y, mean, rstd, *, rows, d, eps) -> None:
+    """y = (x - mean) * rstd * w (+ b) over plain [rows, d] bf16 tensors; w / b may be None; mean / rstd fp32 [rows]."""
+    _req_bf16(x, w, b, y)
+    check(lib().ob_layernorm_fwd(x.data_ptr(), _ptr(w), _ptr(b), y.data_ptr(), mean.data_ptr(), rstd.data_ptr(), rows, d,
+                                 eps, stream_ptr(x.device)), "layernorm_fwd")
+    _count()
+
+
+def layernorm_bwd(dy, x, w, mean, rstd, dx, *, rows, d, dw=None, db=None, scale=1.0) -> None:
+    _req_bf16(dy, x, w, dx)
+    check(lib().ob_layernorm_bwd(dy.data_ptr(), x.data_ptr(), _ptr(w), mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
+                                 _ptr(dw), _ptr(db), rows, d, scale, stream_ptr(x.device)), "layernorm_bwd")
     _count()
 
 

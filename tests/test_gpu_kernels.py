@@ -209,6 +209,36 @@ def test_blockwise_attention_composes_to_full_attention(K):
     _check_status()
 
 
+@pytest.mark.parametrize("rows,d,bias", [(300, 512, True), (70, 4096, True), (33, 8192, False), (257, 128, True)])
+def test_layernorm(K, rows, d, bias):
+    dev = "cuda"
+    torch.manual_seed(8)
+    x = (torch.randn(rows, d, device=dev) * 2 + 0.5).to(torch.bfloat16)
+    w = (torch.randn(d, device=dev) * 0.1 + 1).to(torch.bfloat16)
+    b = (torch.randn(d, device=dev) * 0.1).to(torch.bfloat16) if bias else None
+    y = torch.empty_like(x)
+    mean = torch.empty(rows, device=dev)
+    rstd = torch.empty(rows, device=dev)
+    K.layernorm_fwd(x, w, b, y, mean, rstd, rows=rows, d=d, eps=1e-5)
+    xr, wr = x.float().requires_grad_(True), w.float().requires_grad_(True)
+    br = b.float().requires_grad_(True) if bias else None
+    want = torch.nn.functional.layer_norm(xr, (d,), wr, br, 1e-5)
+    assert rel_err(y, want) < 5e-3
+    assert rel_err(mean, x.float().mean(-1)) < 1e-4
+    dy = torch.randn_like(y)
+    leaves = [xr, wr] + ([br] if bias else [])
+    grads = torch.autograd.grad(want, leaves, dy.float())
+    dx = torch.empty_like(x)
+    dw = torch.zeros(d, device=dev)
+    db = torch.zeros(d, device=dev) if bias else None
+    K.layernorm_bwd(dy, x, w, mean, rstd, dx, rows=rows, d=d, dw=dw, db=db, scale=0.5)
+    assert rel_err(dx, grads[0]) < 1e-2
+    assert rel_err(dw, 0.5 * grads[1]) < 1e-2
+    if bias:
+        assert rel_err(db, 0.5 * grads[2]) < 1e-2
+    _check_status()
+
+
 @pytest.mark.parametrize("rows,d,heads", [(300, 512, 1), (64, 4096, 1), (100, 128, 6)])
 def test_rmsnorm(K, rows, d, heads):
     dev = "cuda"
