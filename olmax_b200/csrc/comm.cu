@@ -9,6 +9,7 @@
 //                                that maps the same buffer on every member.
 #include "comm.h"
 #include "host_common.h"
+#include "sm100.cuh"
 
 namespace ob {
 
@@ -80,9 +81,62 @@ __global__ void __launch_bounds__(AR_THREADS)
   }
 }
 
+// out[i] = (accumulate ? out[i] : 0) + sum over slots r != skip of stage[r * slot_stride + i], bf16 storage, fp32 sums
+__global__ void __launch_bounds__(AR_THREADS)
+    fold_slots_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ stage, long long n8,
+                           int slots, long long slot_stride, int skip, int accumulate) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    if (accumulate) {
+      const uint4 o = *reinterpret_cast<const uint4*>(out + i * 8);
+      const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 t = unpack_bf16x2(w[e]);
+        acc[2 * e] = t.x;
+        acc[2 * e + 1] = t.y;
+      }
+    }
+    for (int r = 0; r < slots; ++r) {
+      if (r == skip) continue;
+      const uint4 o = *reinterpret_cast<const uint4*>(stage + (long long)r * slot_stride + i * 8);
+      const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 t = unpack_bf16x2(w[e]);
+        acc[2 * e] += t.x;
+        acc[2 * e + 1] += t.y;
+      }
+    }
+    uint4 v;
+    v.x = pack_bf16x2(acc[0], acc[1]);
+    v.y = pack_bf16x2(acc[2], acc[3]);
+    v.z = pack_bf16x2(acc[4], acc[5]);
+    v.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + i * 8) = v;
+  }
+}
+
 }  // namespace ob
 
 using namespace ob;
+
+extern "C" int ob_fold_slots_bf16(void* out, const void* stage, long long n, int slots, long long slot_stride, int skip,
+                                  int accumulate, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (n % 8 != 0 || slot_stride % 8 != 0) OB_FAIL(-4, "fold: element counts must be multiples of 8");
+  if ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(stage)) & 15) OB_FAIL(-5, "fold: 16-byte alignment");
+  long long blocks = (n / 8 + AR_THREADS - 1) / AR_THREADS;
+  const long long cap = 8LL * sm_count();
+  if (blocks > cap) blocks = cap;
+  fold_slots_bf16_kernel<<<(unsigned)blocks, AR_THREADS, 0, stream>>>(
+      reinterpret_cast<bf16*>(out), reinterpret_cast<const bf16*>(stage), n / 8, slots, slot_stride,
+      skip, accumulate);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
 
 extern "C" int ob_allreduce_p2p_f32(float* const* bufs, long long n, int me, int world, float scale, int max_blocks,
                                     cudaStream_t stream) {

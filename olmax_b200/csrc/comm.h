@@ -18,6 +18,11 @@ int ob_allreduce_multimem_f32(float* mc, long long n, int me, int world, int max
 int ob_reduce_slots_f32(const float* stage, float* acc, long long n, int R, long long slot_stride, float scale,
                         cudaStream_t stream);
 
+// out[i] = (accumulate ? out[i] : 0) + sum over slots r != skip of stage[r * slot_stride + i]  (bf16 storage, fp32
+// sums, local memory): folds the staging slots of a fused GEMM -> reduce-scatter over a tensor-parallel group
+int ob_fold_slots_bf16(void* out, const void* stage, long long n, int slots, long long slot_stride, int skip,
+                       int accumulate, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

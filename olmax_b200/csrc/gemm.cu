@@ -9,6 +9,10 @@
 //   * dgrad:                          the contraction runs over R weight shards,
 //   * wgrad with reduce-scatter:      output row block s is added into the buffer `c_shards[s]`, which may live in
 //                                     another GPU's memory (plain red.global over NVLink; never TMA).
+// Tensor parallelism with sequence parallelism uses the same two mechanisms on the ACTIVATION side: the all-gather of
+// the A operand's row shards is fused in (`ag_on_a`: the copy warps pull the peers' rows while the tensor cores work
+// on the local rows), and the reduce-scatter of a row-parallel output is fused into the epilogue (row block s of
+// the partial product, plus an optional local partial sum, is stored into GPU s's staging slot).
 // Epilogues: bf16 store, fp32 store / accumulate / red.add, and the gated-MLP epilogue act(gate) * up computed from
 // a tile whose 256 accumulator columns are 128 gate columns followed by 128 up columns.
 //
@@ -58,6 +62,7 @@ struct KernelParams {
   // FSDP all-gather fused into the GEMM: the B operand's remote shards are pulled from peer GPUs (plain loads over
   // NVLink) into the local staging buffer by the copy warps while the tensor cores work on tiles already present.
   int ag_shards;               // 0: off
+  int ag_on_a;                 // 1: the gathered operand is A (row shards of a K-major activation), 0: B (weights)
   int ag_rank;                 // this GPU's shard index (its slot of the staging buffer is filled by the host)
   int ag_rows;                 // rows of one shard piece
   int ag_blocks;               // AG_BLOCK_ROWS-row blocks per shard piece
@@ -184,8 +189,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   const bool glu = (p.epi == EPI_SWIGLU || p.epi == EPI_GEGLU);
   // With a fused all-gather the tile order is rotated so that work on the local shard comes first and the other
   // shards follow in the order the copy warps fetch them (rank+1, rank+2, ...).
-  const int n_rot = (p.ag_shards > 0 && !B_MN) ? p.ag_rank * p.n_tiles_per_shard : 0;
-  const int k_rot = (p.ag_shards > 0 && B_MN) ? p.ag_rank * p.k_iters_per_shard : 0;
+  const int n_rot = (p.ag_shards > 0 && !p.ag_on_a && !B_MN) ? p.ag_rank * p.n_tiles_per_shard : 0;
+  const int k_rot = (p.ag_shards > 0 && !p.ag_on_a && B_MN) ? p.ag_rank * p.k_iters_per_shard : 0;
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
@@ -210,8 +215,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 100);
           if (!ok) break;
           if (p.ag_shards > 0) {
-            ok = B_MN ? ag_wait(p, k_shard, k_local / AG_BLOCK_ROWS, abort_flag)
-                      : ag_wait(p, n_shard, n_local0 / AG_BLOCK_ROWS, abort_flag);
+            if (p.ag_on_a)
+              ok = ag_wait(p, mt / p.m_tiles_per_shard, ((mt % p.m_tiles_per_shard) * BM) / AG_BLOCK_ROWS, abort_flag);
+            else
+              ok = B_MN ? ag_wait(p, k_shard, k_local / AG_BLOCK_ROWS, abort_flag)
+                        : ag_wait(p, n_shard, n_local0 / AG_BLOCK_ROWS, abort_flag);
             if (!ok) break;
           }
           uint8_t* sa = smem + stage * STAGE_BYTES;
@@ -366,8 +374,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         // Output through shared memory + TMA: each thread writes its row's 128 bytes of the chunk into a swizzled
         // staging tile, one thread issues a bulk tensor store (or reduce-add for the accumulating epilogue).  The
         // TMA clips at the tensor / shard boundary, so partial tiles need no per-element guards.
-        const bool f32 = (p.epi != EPI_BF16);
+        const bool f32 = !(p.epi == EPI_BF16 || p.epi == EPI_BF16_ACC);
         const int cols = f32 ? 32 : 64;                      // columns per 128-byte chunk row
+        // EPI_BF16_ACC towards c_shards: the LOCAL partial sum in p.c ([M, N], row stride ldc) is folded in first
+        const bf16* prior_row = (p.epi == EPI_BF16_ACC && p.tma_epi == 2 && row_ok)
+            ? reinterpret_cast<const bf16*>(p.c) + (long long)(m_shard * p.M_s + m_local0 + row_in_tile) * p.ldc + n_glob0
+            : nullptr;
         const int out_row = (p.c_shard_stride > 0) ? m_local0 : m_shard * p.M_s + m_local0;
         const int out_z = (p.c_shard_stride > 0) ? m_shard : 0;
         const bool store_thread = (threadIdx.x == 64);
@@ -394,11 +406,24 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const uint32_t* src = (j < 4) ? &r[j * 8] : &r2[(j - 4) * 8];
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(src[e]) * p.alpha;
+              if (prior_row != nullptr && c0 + j * 8 + 8 <= n_valid) {
+                const uint4 o = *reinterpret_cast<const uint4*>(prior_row + c0 + j * 8);
+                const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 t = unpack_bf16x2(ow[e]);
+                  f[2 * e] += t.x;
+                  f[2 * e + 1] += t.y;
+                }
+              }
               uint4 v;
-              v.x = pack_bf16x2(__uint_as_float(src[0]) * p.alpha, __uint_as_float(src[1]) * p.alpha);
-              v.y = pack_bf16x2(__uint_as_float(src[2]) * p.alpha, __uint_as_float(src[3]) * p.alpha);
-              v.z = pack_bf16x2(__uint_as_float(src[4]) * p.alpha, __uint_as_float(src[5]) * p.alpha);
-              v.w = pack_bf16x2(__uint_as_float(src[6]) * p.alpha, __uint_as_float(src[7]) * p.alpha);
+              v.x = pack_bf16x2(f[0], f[1]);
+              v.y = pack_bf16x2(f[2], f[3]);
+              v.z = pack_bf16x2(f[4], f[5]);
+              v.w = pack_bf16x2(f[6], f[7]);
               *reinterpret_cast<uint4*>(srow + ((j ^ sw) << 4)) = v;
             }
           }
@@ -642,6 +667,7 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
   kp.ldc = a->ldc;
   kp.status = a->status;
   kp.ag_shards = 0;
+  kp.ag_on_a = 0;
   kp.ag_rank = 0; kp.ag_rows = 0; kp.ag_blocks = 0; kp.ag_row_bytes = 0;
   kp.ag_src = nullptr; kp.ag_src2 = nullptr; kp.ag_dst = nullptr; kp.ag_dst2 = nullptr; kp.ag_dst_stride = 0;
   kp.ag_flags = nullptr; kp.ag_target = 0;
@@ -713,7 +739,29 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
   const int total = kp.m_shards * kp.m_tiles_per_shard * kp.n_shards * kp.n_tiles_per_shard;
   int cap = a->max_ctas > 0 ? a->max_ctas : sm_count();
   int grid = total < cap ? total : cap;
-  if (a->ag_src != nullptr) {
+  if (a->ag_src != nullptr && a->ag_on_a) {
+    // all-gather of the A operand's row shards (sequence-parallel activations): shard s = rows [s*M_s, (s+1)*M_s)
+    const int shards = kp.m_shards;
+    if (a->a_mn) OB_FAIL(-16, "fused all-gather of A needs a K-major A operand");
+    if (shards < 2) OB_FAIL(-10, "fused all-gather of A needs M_s < M");
+    if (a->ag_flags == nullptr) OB_FAIL(-11, "fused all-gather needs a flags buffer");
+    if (a->ag_rank < 0 || a->ag_rank >= shards) OB_FAIL(-12, "ag_rank %d outside [0, %d)", a->ag_rank, shards);
+    if (a->ag_src2 != nullptr) OB_FAIL(-17, "fused all-gather of A has a single source table");
+    kp.ag_shards = shards;
+    kp.ag_on_a = 1;
+    kp.ag_rank = a->ag_rank;
+    kp.ag_rows = M_s;
+    kp.ag_blocks = (M_s + AG_BLOCK_ROWS - 1) / AG_BLOCK_ROWS;
+    kp.ag_row_bytes = (long long)a->lda * 2;
+    if (kp.ag_row_bytes % 16 != 0) OB_FAIL(-13, "fused all-gather needs 16-byte aligned rows");
+    kp.ag_src = reinterpret_cast<const uint8_t* const*>(a->ag_src);
+    kp.ag_dst = reinterpret_cast<uint8_t*>(const_cast<void*>(a->a));
+    kp.ag_dst_stride = (long long)M_s * kp.ag_row_bytes;
+    kp.ag_flags = a->ag_flags;
+    kp.ag_target = (unsigned)(grid * COPY_WARPS);
+    if (a->m_shard_rot <= 0) kp.m_rot = a->ag_rank * kp.m_tiles_per_shard;   // local rows first, then rank+1, ...
+    OB_CUDA_OK(cudaMemsetAsync(a->ag_flags, 0, sizeof(unsigned) * (size_t)shards * kp.ag_blocks, stream));
+  } else if (a->ag_src != nullptr) {
     const int shards = a->b_mn ? kp.k_shards : kp.n_shards;
     if (shards < 2 || bss <= 0) OB_FAIL(-10, "fused all-gather needs a sharded B operand");
     if (a->ag_flags == nullptr) OB_FAIL(-11, "fused all-gather needs a flags buffer");
@@ -738,7 +786,7 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
   memset(&tC, 0, sizeof(tC));
   kp.tma_epi = 0;
   const bool tma_ok = (a->epi == EPI_BF16 || a->epi == EPI_F32 || a->epi == EPI_F32_ACC) && a->c_shards == nullptr &&
-                      !a->no_tma_epilogue && (kp.m_shards == 1 || a->c_shard_stride > 0);
+                      !a->no_tma_epilogue && (kp.m_shards == 1 || a->c_shard_stride > 0 || M_s % BM == 0);
   if (tma_ok) {
     const bool f32 = a->epi != EPI_BF16;
     const uint64_t es = f32 ? 4 : 2;
@@ -755,8 +803,11 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
   }
   // peer destinations: staged, line-coalesced stores / reductions (needs 16-byte aligned rows)
   if (kp.tma_epi == 0 && a->c_shards != nullptr && !a->no_tma_epilogue &&
-      (a->epi == EPI_F32 || a->epi == EPI_F32_RED || a->epi == EPI_BF16) && (a->ldc * (a->epi == EPI_BF16 ? 2 : 4)) % 16 == 0)
+      (a->epi == EPI_F32 || a->epi == EPI_F32_RED || a->epi == EPI_BF16 || (a->epi == EPI_BF16_ACC && a->c != nullptr)) &&
+      (a->ldc * ((a->epi == EPI_BF16 || a->epi == EPI_BF16_ACC) ? 2 : 4)) % 16 == 0)
     kp.tma_epi = 2;
+  if (a->c_shards != nullptr && a->epi == EPI_BF16_ACC && kp.tma_epi != 2)
+    OB_FAIL(-18, "EPI_BF16_ACC towards c_shards needs the staged epilogue (16-byte aligned rows, local partial in c)");
   if (a->a_mn) {
     return a->b_mn ? launch<true, true>(tA, tB, tB2, tC, kp, grid, stream) : launch<true, false>(tA, tB, tB2, tC, kp, grid, stream);
   }

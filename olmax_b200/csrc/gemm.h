@@ -13,7 +13,8 @@ enum ObGemmEpilogue {
   EPI_F32_RED = 3,  // C(fp32) += alpha * A.B        (red.global.add; destination may be a peer GPU's memory)
   EPI_SWIGLU = 4,   // C(bf16)  = silu(A.B) * (A.B2); optionally c2 = A.B, c3 = A.B2
   EPI_GEGLU = 5,    // C(bf16)  = gelu_tanh(A.B) * (A.B2)
-  EPI_BF16_ACC = 6, // C(bf16) += alpha * A.B        (read-modify-write, local memory)
+  EPI_BF16_ACC = 6, // C(bf16) += alpha * A.B        (read-modify-write, local memory); with c_shards: row block s of
+                    // c (the local partial sum, [M, N]) + alpha * A.B is STORED to c_shards[s] and c is left unchanged
 };
 
 // C[M, N] = A[M, Kc] . B[Kc, N]  with bf16 operands and fp32 accumulation.
@@ -64,6 +65,10 @@ typedef struct ObGemmArgs {
   int group_m;          // tile rasterisation group in M tiles (0 = default 16)
   int multi_box_mn;     // 1: fetch MN-major operands as 64-wide boxes even when one 4-D box per stage would do
   int no_tma_epilogue;  // 1: write outputs with per-thread stores instead of shared memory + TMA (for comparison)
+  // 1: ag_src / ag_flags / ag_rank describe an all-gather of the A operand instead of B: A (K-major, [M, Kc]) is a
+  // buffer of M / M_s row shards of which only shard ag_rank is filled; the copy warps fetch shard s from ag_src[s]
+  // (a contiguous [M_s, Kc] piece with the same row stride in GPU s's memory) and the tiles of shard s wait for it.
+  int ag_on_a;
 } ObGemmArgs;
 
 int ob_gemm_bf16(const ObGemmArgs* args, cudaStream_t stream);

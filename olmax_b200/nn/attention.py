@@ -118,12 +118,17 @@ class MultiheadSelfAttention(Module):
     def forward(self, x: torch.Tensor, batch_size: int, cache: Optional[BufferCache] = None) -> torch.Tensor:
         """x: [tokens, d_model] (tokens = batch * seq, or that divided by tp under sequence parallelism)."""
         tp = self.mesh.tp
-        x = coll.seq_all_gather(x, tp)
-        T = x.shape[0]
+        tpc = self.store.tp_symm if x.is_cuda else None
+        if tpc is not None:
+            # the all-gather of x over the TP group is fused into the q GEMM (k and v read the gathered rows)
+            q, k, v = F.tp_column_linears(x, tpc, (self.q_proj.weight, self.k_proj.weight, self.v_proj.weight))
+        else:
+            x = coll.seq_all_gather(x, tp)
+            q = self.q_proj(x)
+            k = self.k_proj(x)
+            v = self.v_proj(x)
+        T = q.shape[0]
         S = T // batch_size
-        q = self.q_proj(x)
-        k = self.k_proj(x)
-        v = self.v_proj(x)
         if self.q_norm is not None:
             heads_q = self.local_heads if self.use_head_qk_norm else 1
             heads_k = self.local_kv_heads if self.use_head_qk_norm else 1
@@ -137,6 +142,8 @@ class MultiheadSelfAttention(Module):
             q = self.rope(q, cache, cp.size, cp.rank)
             k = self.rope(k, cache, cp.size, cp.rank)
         o = self.sdpa(q, k, v).reshape(T, self.local_heads * self.head_dim)
+        if tpc is not None:
+            return F.tp_row_linear(o, tpc, self.o_proj.weight)   # reduce-scatter fused into the GEMM epilogue
         y = self.o_proj(o)
         return coll.seq_reduce_scatter(y, tp)
 

@@ -29,6 +29,9 @@ class GatedMLP(Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         tp = self.mesh.tp
+        tpc = self.store.tp_symm if x.is_cuda else None
+        if tpc is not None:   # both tensor-parallel collectives are fused into the GEMMs of the block
+            return F.gated_mlp(x, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight, self.activation, tpc)
         x = coll.seq_all_gather(x, tp)
         y = F.gated_mlp(x, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight, self.activation)
         return coll.seq_reduce_scatter(y, tp)

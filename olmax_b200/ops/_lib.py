@@ -68,6 +68,7 @@ class ObGemmArgs(ctypes.Structure):
         ("group_m", ctypes.c_int),
         ("multi_box_mn", ctypes.c_int),
         ("no_tma_epilogue", ctypes.c_int),
+        ("ag_on_a", ctypes.c_int),
     ]
 
 

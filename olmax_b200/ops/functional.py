@@ -22,7 +22,7 @@ from . import reference as ref
 
 __all__ = [
     "linear", "gated_mlp", "rms_norm", "layer_norm", "rope", "attention", "attention_block_fwd", "attention_block_bwd",
-    "embedding", "linear_cross_entropy", "glu",
+    "embedding", "linear_cross_entropy", "glu", "tp_column_linears", "tp_row_linear",
 ]
 
 
@@ -58,21 +58,29 @@ def _ag_kwargs(handle, second=None) -> dict:
     return out
 
 
-def _gemm_fwd(x2: torch.Tensor, handle, out: Optional[torch.Tensor] = None, epi: int = K.EPI_BF16) -> torch.Tensor:
-    """y[M, N] = x2[M, K] @ W[N, K]^T with W read from the gathered unit buffer."""
+def _gemm_fwd(x2: torch.Tensor, handle, out: Optional[torch.Tensor] = None, epi: int = K.EPI_BF16,
+              extra: Optional[dict] = None) -> torch.Tensor:
+    """y[M, N] = x2[M, K] @ W[N, K]^T with W read from the gathered unit buffer.  ``extra``: more GEMM arguments
+    (tensor-parallel all-gather of x2's rows, or reduce-scatter of the output rows; then ``out`` is only a placeholder)."""
     M, Kd = x2.shape
     N = handle.tp_shape[0]
     first, kw = _b_operand(handle)
     kw.update(_ag_kwargs(handle))
     kw["prefetch"] = handle.store.prefetch_slice(N * Kd)
+    if extra:
+        assert "ag_src" not in kw or "ag_src" not in extra, "one fused all-gather per GEMM"
+        kw.update(extra)
     if out is None:
         out = torch.empty((M, N), dtype=torch.float32 if epi == K.EPI_F32 else torch.bfloat16, device=x2.device)
-    K.gemm(x2, first, out, M, N, Kd, epi=epi, ldb=Kd, **kw)
+    K.gemm(x2, first, out, M, N, Kd, epi=epi, ldb=Kd, ldc=N, **kw)
     return out
 
 
-def _gemm_dgrad(dy2: torch.Tensor, handle, out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
-    """dx[M, K] (+)= dy2[M, N] @ W[N, K], the contraction running over the weight's row shards."""
+def _gemm_dgrad(dy2: torch.Tensor, handle, out: Optional[torch.Tensor] = None, accumulate: bool = False,
+                extra: Optional[dict] = None) -> torch.Tensor:
+    """dx[M, K] (+)= dy2[M, N] @ W[N, K], the contraction running over the weight's row shards.  With a reduce-scatter
+    in ``extra`` (``c_shards``) the result leaves through the peers' staging slots: ``out`` is then the local partial
+    sum that is folded in when ``accumulate`` is set (it is not written), or a placeholder."""
     M, N = dy2.shape
     Kd = handle.tp_shape[1]
     first, stride = handle.pieces()
@@ -80,9 +88,12 @@ def _gemm_dgrad(dy2: torch.Tensor, handle, out: Optional[torch.Tensor] = None, a
     kw = {} if R == 1 else {"Kc_s": handle.rows_local, "b_shard_stride": stride}
     kw.update(_ag_kwargs(handle))
     kw["prefetch"] = handle.store.prefetch_slice(N * Kd)
+    if extra:
+        assert "ag_src" not in kw or "ag_src" not in extra, "one fused all-gather per GEMM"
+        kw.update(extra)
     if out is None:
         out = torch.empty((M, Kd), dtype=torch.bfloat16, device=dy2.device)
-    K.gemm(dy2, first, out, M, Kd, N, b_mn=True, ldb=Kd, epi=K.EPI_BF16_ACC if accumulate else K.EPI_BF16, **kw)
+    K.gemm(dy2, first, out, M, Kd, N, b_mn=True, ldb=Kd, ldc=Kd, epi=K.EPI_BF16_ACC if accumulate else K.EPI_BF16, **kw)
     return out
 
 
@@ -156,13 +167,21 @@ def linear(x: torch.Tensor, handle, bias_handle=None) -> torch.Tensor:
 # Gated MLP: down(act(gate(x)) * up(x)) in one autograd node so that act(g)*u is never kept for backward
 # ----------------------------------------------------------------------------------------------------------------------
 class _GatedMLPFn(torch.autograd.Function):
+    """``tpc`` (a ``TPSymmContext``; GPU only): x holds this rank's rows of the sequence-parallel activation; their
+    all-gather is fused into the gate/up GEMM and the reduce-scatter of the output into the down GEMM's epilogue
+    (forward), and symmetrically in backward (gather of dy into the down dgrad, reduce-scatter of dx out of the
+    up dgrad, which folds in the gate dgrad's partial sum)."""
+
     @staticmethod
-    def forward(ctx, x, gate, up, down, act):
+    def forward(ctx, x, gate, up, down, act, tpc=None):
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
-        ctx.handles, ctx.act, ctx.shape = (gate, up, down), act, shp
+        ctx.handles, ctx.act, ctx.shape, ctx.tpc = (gate, up, down), act, shp, tpc
         if _on_gpu(x):
             x2 = x2.contiguous()
+            ag_kw = {}
+            if tpc is not None:
+                x2, ag_kw = tpc.gather_begin(x2)
             M, d = x2.shape
             h = gate.tp_shape[0]
             a = torch.empty((M, h), dtype=torch.bfloat16, device=x.device)
@@ -172,8 +191,17 @@ class _GatedMLPFn(torch.autograd.Function):
             ufirst, _ = up.pieces()
             kw.update(_ag_kwargs(gate, up))
             kw["prefetch"] = gate.store.prefetch_slice(2 * h * d)
+            kw.update(ag_kw)
             K.gemm(x2, gfirst, a, M, h, d, epi=K.EPI_GEGLU if act != "silu" else K.EPI_SWIGLU, b2=ufirst, c2=g, c3=u,
                    ldb=d, **kw)
+            if tpc is not None:
+                M_s = M // tpc.n
+                stage, rs_kw = tpc.rs_begin(M_s, d)
+                _gemm_fwd(a, down, out=stage, extra=rs_kw)
+                del a
+                y = tpc.rs_finish(stage, M_s, d)
+                ctx.save_for_backward(x2, g, u)
+                return y.view(*shp[:-1], d)
             y = _gemm_fwd(a, down)
             del a
         else:
@@ -189,9 +217,13 @@ class _GatedMLPFn(torch.autograd.Function):
         x2, g, u = ctx.saved_tensors
         gate, up, down = ctx.handles
         dy2 = dy.reshape(-1, dy.shape[-1])
+        tpc = ctx.tpc
         if _on_gpu(dy2):
             dy2 = dy2.contiguous()
-            da = _gemm_dgrad(dy2, down)
+            ag_kw = None
+            if tpc is not None:
+                dy2, ag_kw = tpc.gather_begin(dy2)
+            da = _gemm_dgrad(dy2, down, extra=ag_kw)
             dg = torch.empty_like(g)
             du = torch.empty_like(u)
             a = torch.empty_like(g)
@@ -204,7 +236,13 @@ class _GatedMLPFn(torch.autograd.Function):
             dx = None
             if ctx.needs_input_grad[0]:
                 dx = _gemm_dgrad(dg, gate)
-                _gemm_dgrad(du, up, out=dx, accumulate=True)
+                if tpc is not None:
+                    M_s, d = dx.shape[0] // tpc.n, dx.shape[1]
+                    stage, rs_kw = tpc.rs_begin(M_s, d)
+                    _gemm_dgrad(du, up, out=dx, accumulate=True, extra=rs_kw)   # stores dx + du.Wu to the row owners
+                    dx = tpc.rs_finish(stage, M_s, d)
+                else:
+                    _gemm_dgrad(du, up, out=dx, accumulate=True)
         else:
             with torch.enable_grad():
                 gg = g.detach().requires_grad_(True)
@@ -216,11 +254,91 @@ class _GatedMLPFn(torch.autograd.Function):
             gate.add_grad(dg.t() @ x2)
             up.add_grad(du.t() @ x2)
             dx = dg @ gate.full() + du @ up.full() if ctx.needs_input_grad[0] else None
-        return (dx.view(ctx.shape) if dx is not None else None), None, None, None, None
+        return (dx.view(ctx.shape) if dx is not None else None), None, None, None, None, None
 
 
-def gated_mlp(x: torch.Tensor, gate, up, down, act: str = "silu") -> torch.Tensor:
-    return _GatedMLPFn.apply(x, gate, up, down, act)
+def gated_mlp(x: torch.Tensor, gate, up, down, act: str = "silu", tpc=None) -> torch.Tensor:
+    """``down(act(gate(x)) * up(x))``.  With ``tpc`` x is this rank's row shard of a sequence-parallel activation and
+    so is the result (the tensor-parallel collectives are fused into the GEMMs)."""
+    return _GatedMLPFn.apply(x, gate, up, down, act, tpc if x.is_cuda else None)
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# Tensor parallelism with sequence parallelism, collectives fused into the GEMMs (GPU, peer-memory context)
+# ----------------------------------------------------------------------------------------------------------------------
+class _TPColumnLinearsFn(torch.autograd.Function):
+    """x_local [M/tp, d] -> (x_full @ W_i^T for every column-parallel weight i): the all-gather of x is fused into the
+    first GEMM, the others read the gathered buffer.  Backward: the weight gradients use the gathered x; the input
+    gradient sum_i dy_i W_i is accumulated locally and reduce-scattered out of the LAST dgrad GEMM's epilogue."""
+
+    @staticmethod
+    def forward(ctx, x_local, tpc, *handles):
+        x_full, ag_kw = tpc.gather_begin(x_local.contiguous())
+        ys = []
+        for i, h in enumerate(handles):
+            ys.append(_gemm_fwd(x_full, h, extra=ag_kw if i == 0 else None))
+        ctx.tpc, ctx.handles = tpc, handles
+        ctx.save_for_backward(x_full)
+        return tuple(ys)
+
+    @staticmethod
+    def backward(ctx, *dys):
+        (x_full,) = ctx.saved_tensors
+        tpc, handles = ctx.tpc, ctx.handles
+        dys = [dy.contiguous() for dy in dys]
+        for dy, h in zip(dys, handles):
+            _gemm_wgrad(dy, x_full, h)
+        if not ctx.needs_input_grad[0]:
+            return (None, None) + (None,) * len(handles)
+        M, d = x_full.shape
+        M_s = M // tpc.n
+        partial = None
+        for dy, h in zip(dys[:-1], handles[:-1]):
+            partial = _gemm_dgrad(dy, h, out=partial, accumulate=partial is not None)
+        stage, rs_kw = tpc.rs_begin(M_s, d)
+        _gemm_dgrad(dys[-1], handles[-1], out=partial if partial is not None else stage,
+                    accumulate=partial is not None, extra=rs_kw)
+        dx_local = tpc.rs_finish(stage, M_s, d)
+        return (dx_local, None) + (None,) * len(handles)
+
+
+class _TPRowLinearFn(torch.autograd.Function):
+    """x [M, K/tp] -> this rank's rows [M/tp, N] of sum over the group of x W^T: the reduce-scatter is the GEMM's
+    epilogue.  Backward: the all-gather of dy is fused into the dgrad GEMM; the weight gradient uses the gathered dy."""
+
+    @staticmethod
+    def forward(ctx, x, tpc, handle):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        M = x2.shape[0]
+        N = handle.tp_shape[0]
+        M_s = M // tpc.n
+        stage, rs_kw = tpc.rs_begin(M_s, N)
+        _gemm_fwd(x2, handle, out=stage, extra=rs_kw)
+        y = tpc.rs_finish(stage, M_s, N)
+        ctx.tpc, ctx.handle, ctx.shape = tpc, handle, x.shape
+        ctx.save_for_backward(x2)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy_local):
+        (x2,) = ctx.saved_tensors
+        tpc, handle = ctx.tpc, ctx.handle
+        dy_full, ag_kw = tpc.gather_begin(dy_local.contiguous())
+        dx = _gemm_dgrad(dy_full, handle, extra=ag_kw) if ctx.needs_input_grad[0] else None
+        if dx is None:   # nobody pulled the peers' rows: complete the gather with the copy kernel
+            K.gather_shards(ag_kw["ag_src"], dy_full, dy_local.numel(), dy_local.numel(), tpc.n, tpc.rank)
+        _gemm_wgrad(dy_full, x2, handle)
+        return (dx.view(ctx.shape) if dx is not None else None), None, None
+
+
+def tp_column_linears(x_local: torch.Tensor, tpc, handles):
+    """Column-parallel projections of a sequence-parallel activation with the all-gather fused into the first GEMM."""
+    return _TPColumnLinearsFn.apply(x_local, tpc, *handles)
+
+
+def tp_row_linear(x: torch.Tensor, tpc, handle) -> torch.Tensor:
+    """Row-parallel projection whose partial sums are reduce-scattered over the TP group by the GEMM epilogue."""
+    return _TPRowLinearFn.apply(x, tpc, handle)
 
 
 def glu(g: torch.Tensor, u: torch.Tensor, act: str = "silu") -> torch.Tensor:

@@ -64,6 +64,7 @@ register_signature("ob_adamw", [_vp, _vp, _vp, _vp, _vp, _ll, _f, _f, _f, _f, _f
 register_signature("ob_sumsq", [_vp, _ll, _vp, _vp])
 register_signature("ob_clip_coef", [_vp, _f, _f, _vp, _vp])
 register_signature("ob_cast_f32_bf16", [_vp, _vp, _ll, _vp])
+register_signature("ob_fold_slots_bf16", [_vp, _vp, _ll, _i, _ll, _i, _i, _vp])
 register_signature("ob_gather_shards", [_vp, _vp, _ll, _ll, _i, _i, _vp])
 register_signature("ob_scatter_add_shards", [_vp, _vp, _ll, _i, _f, _vp])
 register_signature("ob_allreduce_p2p_f32", [_vp, _ll, _i, _i, _f, _i, _vp])
@@ -120,6 +121,7 @@ def gemm(
     group_m: int = 0,
     multi_box_mn: bool = False,
     m_shard_rot: int = 0,
+    ag_on_a: bool = False,
 ) -> None:
     """``C[M, N] (+)= alpha * A[M, K] . B[K, N]``; see ``csrc/gemm.h`` for operand layouts and sharding."""
     _req_bf16(a, b, b2)
@@ -149,6 +151,7 @@ def gemm(
     args.group_m = group_m
     args.m_shard_rot = m_shard_rot
     args.multi_box_mn = int(multi_box_mn)
+    args.ag_on_a = int(ag_on_a)
     if prefetch is not None:
         table, dst_ptr, dst_stride, off, nbytes, shards, rank = prefetch
         args.pf_src, args.pf_dst, args.pf_dst_stride = table.data_ptr(), dst_ptr, dst_stride
@@ -352,6 +355,14 @@ def allreduce_p2p(table, n, me, world, scale=1.0, max_blocks=0) -> None:
 def allreduce_multimem(mc_ptr: int, n, me, world, max_blocks=0, device=None) -> None:
     """In-place sum through an NVLS multicast address (multimem.ld_reduce / multimem.st)."""
     check(lib().ob_allreduce_multimem_f32(mc_ptr, n, me, world, max_blocks, stream_ptr(device)), "allreduce_multimem")
+    _count()
+
+
+def fold_slots_bf16(out, stage, n, slots, slot_stride, *, skip=-1, accumulate=False) -> None:
+    """out[:n] = (out if accumulate) + sum over slots r != skip of stage[r * slot_stride : ... + n]  (bf16, fp32 sums)."""
+    _req_bf16(out, stage)
+    check(lib().ob_fold_slots_bf16(out.data_ptr(), stage.data_ptr(), n, slots, slot_stride, skip, int(accumulate),
+                                   stream_ptr(out.device)), "fold_slots_bf16")
     _count()
 
 

@@ -310,6 +310,7 @@ class ParamStore:
         self._in_backward = False
         self.symm_ag = None  # ... used for the all-gather side (weights fetched inside the GEMMs)
         self.symm_rs = None  # ... used for the reduce-scatter side (gradients added into the owners' shards)
+        self.tp_symm = None  # peer-memory context of the tensor-parallel group (collectives fused into the GEMMs)
 
     # ------------------------------------------------------------------ registration
     def register(
@@ -396,6 +397,14 @@ class ParamStore:
                 self.shadow = self.master
             else:
                 self.shadow = self._alloc_shadow(off)
+        if (self.mesh.tp.size > 1 and dev.type == "cuda" and self.comm_backend in ("auto", "fused")
+                and self.compute_dtype == torch.bfloat16 and os.environ.get("OLMAX_B200_FUSED_TP", "1") == "1"):
+            from .symm import TPSymmContext, symm_available
+
+            if symm_available(dev):
+                self.tp_symm = TPSymmContext(self.mesh, dev)
+            elif self.comm_backend == "fused":
+                raise OLMaxConfigurationError("comm_backend='fused' needs CUDA, NCCL and torch symmetric memory")
         self._finalized = True
         if init:
             self.init_parameters(seed)

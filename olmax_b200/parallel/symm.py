@@ -32,7 +32,7 @@ import torch.distributed as dist
 
 from ..ops import kernels as K
 
-__all__ = ["SymmContext", "symm_available"]
+__all__ = ["SymmContext", "TPSymmContext", "symm_available"]
 
 log = logging.getLogger(__name__)
 
@@ -157,3 +157,97 @@ class SymmContext:
         else:
             K.allreduce_p2p(self.replica_grad_table, n, rep.rank, rep.size)
         return 2 * (rep.size - 1) * n * 4 // rep.size
+
+
+class TPSymmContext:
+    """
+    Peer-memory buffers of a tensor-parallel group with sequence parallelism, for the two fused activation paths:
+
+    * **all-gather -> GEMM**: ``gather_begin(x_local)`` copies this rank's rows into a symmetric buffer, passes a
+      stream-ordered barrier and returns the full ``[M, d]`` activation with only the local rows filled plus the GEMM
+      arguments that make the FIRST consuming GEMM pull the other rows from the peers with its copy warps while its
+      tensor cores start on the local rows (``ag_on_a`` of ``csrc/gemm.h``).
+    * **GEMM -> reduce-scatter**: ``rs_begin(M_s, N)`` returns the pointer table that makes a GEMM epilogue store row
+      block s of its partial product into this rank's slot of GPU s's staging buffer; ``rs_finish`` passes a barrier and
+      folds the slots into the local ``[M_s, N]`` result.
+
+    Buffers alternate between two copies.  Every publish / staging buffer is reused only after a later barrier of the
+    same group, which every member passes after the kernels that read (or wrote) the buffer: gather and reduce-scatter
+    regions alternate in a transformer (each block is entered by a gather and left by a reduce-scatter, in forward,
+    recomputation and backward alike), so between two uses of a buffer there are at least two such barriers.
+    """
+
+    def __init__(self, mesh, device: torch.device):
+        self.mesh = mesh
+        self.group = mesh.tp
+        self.n = mesh.tp.size
+        self.rank = mesh.tp.rank
+        self.device = device
+        self._x: Dict[int, list] = {}       # capacity (elements) -> [(tensor, pointer table of the group's buffers)] * 2
+        self._stage: Dict[int, list] = {}   # slot elements -> [(tensor [n * slot], table of "my slot on GPU s")] * 2
+        self._flip_x = 0
+        self._flip_s = 0
+        self.flags = torch.zeros(self.n * 4096, dtype=torch.int32, device=device)
+        self._token = torch.zeros(1, dtype=torch.float32, device=device)
+        self.bytes_gathered = 0
+        self.bytes_scattered = 0
+        log.info("Tensor-parallel peer-memory context: group of %d (rank %d)", self.n, self.rank)
+
+    def _symm_pair(self, numel: int, slot_offset_elems: int):
+        """Two symmetric bf16 buffers of ``numel`` elements and, for each, the device table of the addresses
+        ``peer buffer + slot_offset_elems`` over the TP group.  Collective over the whole job (same order everywhere)."""
+        import torch.distributed._symmetric_memory as symm_mem
+
+        out = []
+        for _ in range(2):
+            t = symm_mem.empty(numel, dtype=torch.bfloat16, device=self.device)
+            t.zero_()
+            h = symm_mem.rendezvous(t, dist.group.WORLD)
+            ptrs = [int(p) for p in h.buffer_ptrs]
+            table = K.pointer_table([ptrs[r] + slot_offset_elems * 2 for r in self.group.ranks], self.device)
+            out.append((t, table, h))
+        return out
+
+    def barrier(self) -> None:
+        dist.all_reduce(self._token, group=self.group.pg)
+
+    # ---- all-gather -> GEMM -----------------------------------------------------------------------------------------
+    def gather_begin(self, x_local: torch.Tensor):
+        """x_local [M_s, d] bf16 -> (x_full [M, d] with rows of this rank filled, kwargs for the first consuming GEMM)."""
+        M_s, d = x_local.shape
+        numel = M_s * d
+        if numel not in self._x:
+            self._x[numel] = self._symm_pair(numel, 0)
+        buf, table, _ = self._x[numel][self._flip_x]
+        self._flip_x ^= 1
+        buf.view(M_s, d).copy_(x_local)
+        x_full = torch.empty((self.n * M_s, d), dtype=x_local.dtype, device=x_local.device)
+        x_full[self.rank * M_s : (self.rank + 1) * M_s].copy_(x_local)
+        self.barrier()   # every member's rows are in its buffer before anybody's GEMM pulls them
+        self.bytes_gathered += (self.n - 1) * numel * 2
+        return x_full, {"ag_src": table, "ag_flags": self.flags, "ag_rank": self.rank, "ag_on_a": True, "M_s": M_s}
+
+    def gather_now(self, x_local: torch.Tensor) -> torch.Tensor:
+        """Same, completed by a copy kernel instead of a GEMM (for consumers that are not GEMM A operands)."""
+        x_full, kw = self.gather_begin(x_local)
+        M_s, d = x_local.shape
+        K.gather_shards(kw["ag_src"], x_full, M_s * d, M_s * d, self.n, self.rank)
+        return x_full
+
+    # ---- GEMM -> reduce-scatter -------------------------------------------------------------------------------------
+    def rs_begin(self, M_s: int, N: int):
+        """(staging tensor, kwargs for the GEMM whose [n * M_s, N] output is to be reduce-scattered)."""
+        slot = M_s * N
+        if slot not in self._stage:
+            self._stage[slot] = self._symm_pair(self.n * slot, self.rank * slot)
+        buf, table, _ = self._stage[slot][self._flip_s]
+        self._flip_s ^= 1
+        # the peers' row blocks are computed first so that their transfer starts early; the local block comes last
+        return buf, {"M_s": M_s, "c_shards": table, "m_shard_rot": (self.rank + 1) % self.n}
+
+    def rs_finish(self, stage: torch.Tensor, M_s: int, N: int) -> torch.Tensor:
+        self.barrier()   # every member's stores into our slots have completed
+        out = torch.empty((M_s, N), dtype=torch.bfloat16, device=self.device)
+        K.fold_slots_bf16(out, stage, M_s * N, self.n, M_s * N, skip=-1, accumulate=False)
+        self.bytes_scattered += (self.n - 1) * M_s * N * 2
+        return out

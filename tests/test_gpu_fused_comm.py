@@ -76,6 +76,80 @@ def test_all_gather_fused_gemm_single_gpu_emulation(rank):
     _check()
 
 
+@pytest.mark.parametrize("rank,tp", [(0, 2), (1, 2), (2, 4)])
+def test_tensor_parallel_fused_kernels_single_gpu_emulation(rank, tp):
+    """The activation-side fusions of tensor parallelism on ONE GPU, the "peers" being other local buffers:
+    all-gather of the A operand's row shards inside the GEMM, the gated dual-B GEMM on such an operand, the
+    reduce-scatter epilogue (row block s stored to c_shards[s], with and without a local partial sum folded in) and the
+    bf16 slot fold."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from olmax_b200.ops import kernels as K
+
+    dev = torch.device("cuda")
+    torch.manual_seed(30 + rank)
+    M, N, Kd = 1024 * tp, 1280, 512
+    M_s = M // tp
+    x = torch.randn(M, Kd, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(N, Kd, device=dev, dtype=torch.bfloat16)
+    peers = [x[r * M_s : (r + 1) * M_s].clone() for r in range(tp)]
+    table = K.pointer_table([p.data_ptr() for p in peers], dev)
+    flags = torch.zeros(tp * 64, dtype=torch.int32, device=dev)
+
+    def full_with_local_rows():
+        buf = torch.full((M, Kd), float("nan"), device=dev, dtype=torch.bfloat16)
+        buf[rank * M_s : (rank + 1) * M_s] = peers[rank]
+        return buf
+
+    # all-gather -> GEMM
+    xf = full_with_local_rows()
+    y = torch.zeros(M, N, device=dev, dtype=torch.bfloat16)
+    K.gemm(xf, w, y, M, N, Kd, M_s=M_s, ag_src=table, ag_flags=flags, ag_rank=rank, ag_on_a=True)
+    assert torch.equal(xf, x)                                   # every row shard arrived
+    assert rel_err(y, x.float() @ w.float().t()) < 5e-3
+    # ... with the gated epilogue
+    w2 = torch.randn(N, Kd, device=dev, dtype=torch.bfloat16) * 0.1
+    xf = full_with_local_rows()
+    act, g, u = (torch.empty(M, N, device=dev, dtype=torch.bfloat16) for _ in range(3))
+    K.gemm(xf, w, act, M, N, Kd, M_s=M_s, epi=K.EPI_GEGLU, b2=w2, c2=g, c3=u, ag_src=table, ag_flags=flags, ag_rank=rank,
+           ag_on_a=True)
+    gf, uf = x.float() @ w.float().t(), x.float() @ w2.float().t()
+    assert rel_err(g, gf) < 5e-3 and rel_err(u, uf) < 5e-3
+    assert rel_err(act, torch.nn.functional.gelu(gf, approximate="tanh") * uf) < 1e-2
+    # ... as the A operand of a dgrad-layout GEMM (MN-major B)
+    wt = torch.randn(Kd, N, device=dev, dtype=torch.bfloat16)
+    xf = full_with_local_rows()
+    y2 = torch.zeros(M, N, device=dev, dtype=torch.bfloat16)
+    K.gemm(xf, wt, y2, M, N, Kd, b_mn=True, M_s=M_s, ag_src=table, ag_flags=flags, ag_rank=rank, ag_on_a=True)
+    assert rel_err(y2, x.float() @ wt.float()) < 5e-3
+
+    # GEMM -> reduce-scatter: row block s goes to "GPU" s's slot
+    slots = [torch.full((M_s * N + 64,), float("nan"), device=dev, dtype=torch.bfloat16) for _ in range(tp)]
+    ctable = K.pointer_table([t.data_ptr() for t in slots], dev)
+    want = x.float() @ w.float().t()
+    K.gemm(x, w, slots[0], M, N, Kd, ldc=N, M_s=M_s, c_shards=ctable, m_shard_rot=(rank + 1) % tp)
+    for r in range(tp):
+        assert rel_err(slots[r][: M_s * N].view(M_s, N), want[r * M_s : (r + 1) * M_s]) < 5e-3
+    # ... folding in a local partial sum (which must stay untouched)
+    prior = torch.randn(M, N, device=dev, dtype=torch.bfloat16) * 10
+    prior0 = prior.clone()
+    K.gemm(x, w, prior, M, N, Kd, ldc=N, epi=K.EPI_BF16_ACC, M_s=M_s, c_shards=ctable, m_shard_rot=(rank + 1) % tp)
+    assert torch.equal(prior, prior0)
+    for r in range(tp):
+        assert rel_err(slots[r][: M_s * N].view(M_s, N), (want + prior0.float())[r * M_s : (r + 1) * M_s]) < 5e-3
+    # fold of the staging slots
+    stage = torch.randn(tp, M_s * N, device=dev, dtype=torch.bfloat16)
+    out = torch.randn(M_s * N, device=dev, dtype=torch.bfloat16)
+    out0 = out.clone()
+    K.fold_slots_bf16(out, stage, M_s * N, tp, M_s * N, skip=-1, accumulate=False)
+    assert rel_err(out, stage.float().sum(0)) < 5e-3
+    out = out0.clone()
+    K.fold_slots_bf16(out, stage, M_s * N, tp, M_s * N, skip=rank, accumulate=True)
+    keep = [r for r in range(tp) if r != rank]
+    assert rel_err(out, out0.float() + stage[keep].float().sum(0)) < 5e-3
+    _check()
+
+
 def test_small_shard_helpers():
     if not torch.cuda.is_available():
         pytest.skip("needs a GPU")
@@ -152,7 +226,7 @@ def test_peer_memory_backend_matches_nccl(mesh_kind, world):
             assert rel_err(pf[name], pn[name]) < 1e-2, name
 
 
-def _tp_worker(mesh_kind):
+def _tp_worker(mesh_kind, backend="nccl"):
     from olmax_b200.models import DefaultTransformerConfig, GemmaTransformerLayerConfig
     from olmax_b200.nn import LMHeadConfig, MultiheadSelfAttentionConfig
     from olmax_b200.ops import _lib
@@ -172,8 +246,9 @@ def _tp_worker(mesh_kind):
                                    layer=GemmaTransformerLayerConfig(attention=attn), lm_head=LMHeadConfig(logit_softcap=30.0),
                                    tie_embeddings=True, scale_embeddings=True, sliding_window=128, sliding_window_pattern=2,
                                    ce_chunk_rows=256)
-    model = cfg.build(seed=5, mesh_resource=res, device=dev, comm_backend="nccl")
+    model = cfg.build(seed=5, mesh_resource=res, device=dev, comm_backend=backend)
     mesh = model.mesh
+    assert (model.store.tp_symm is not None) == (backend == "fused" and mesh.tp.size > 1)
     optim = AdamWConfig(lr=ConstantSchedule(1e-3)).build(model, 1)
     gen = torch.Generator().manual_seed(7)
     cache = model.get_buffer_cache(256, dev)
@@ -209,6 +284,23 @@ def test_tensor_parallel_matches_fsdp_on_two_gpus():
     assert all(abs(a - b) < 2e-2 * abs(b) for a, b in zip(lt, lf)), (lt, lf)
     for name in pf:
         assert rel_err(pt[name], pf[name]) < 1e-2, name
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_fused_tensor_parallel_matches_nccl_tensor_parallel(world):
+    """TP with the collectives fused into the GEMMs (all-gather of the activation rows in the q / gate-up / dgrad
+    GEMMs, reduce-scatter in the o / down / dgrad epilogues, over peer memory) trains like TP over NCCL collectives;
+    world 4 = FSDP 2 x TP 2."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    fused = run_distributed_test(_tp_worker, world_size=world, backend="nccl", func_args=("tp", "fused"), timeout=300)
+    nccl = run_distributed_test(_tp_worker, world_size=world, backend="nccl", func_args=("tp", "nccl"), timeout=300)
+    for r in range(world):
+        lf, pf = fused[r]
+        ln, pn = nccl[r]
+        assert all(abs(a - b) < 2e-2 * abs(b) for a, b in zip(lf, ln)), (lf, ln)
+        for name in pn:
+            assert rel_err(pf[name], pn[name]) < 1e-2, name
 
 
 @pytest.mark.parametrize("strategy", ["all_gather", "ring"])
