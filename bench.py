@@ -117,6 +117,8 @@ def main() -> int:
     ap.add_argument("--mesh", default="FSDP", choices=["FSDP", "HSDP", "DDP", "FSDP_with_TP", "FSDP_with_CP", "HSDP_with_CP"])
     ap.add_argument("--shard-degree", type=int, default=None)
     ap.add_argument("--tp-degree", type=int, default=2)
+    ap.add_argument("--kernel-timing", action="store_true",
+                    help="after the measurement run 2 more steps with per-kernel CUDA-event timing and print the table (stderr)")
     ap.add_argument("--cp-degree", type=int, default=None, help="context-parallel degree of the *_with_CP meshes")
     ap.add_argument("--cp-strategy", default=None, choices=["all_gather", "ring"])
     ap.add_argument("--microbatches", type=int, default=2)
@@ -271,7 +273,8 @@ def main() -> int:
             "config": {
                 "model": args.recipe, "global_batch": global_batch, "seq_len": seq, "microbatches": k,
                 "parallelism": f"{args.mesh.lower()}{world}", "optimizer": "AdamW fp32 master/moments",
-                "comm": "fused peer-memory kernels" if model.store.symm is not None else ("nccl" if world > 1 else "none"),
+                "comm": ("fused peer-memory kernels" if (model.store.symm is not None or model.store.tp_symm is not None)
+                         else ("nccl" if world > 1 else "none")),
                 "layers": model_cfg.num_layers, "params": model.num_params(), "activation_checkpointing": args.ac,
                 "l2": "working set (>14 GB of weights per step) exceeds L2, no explicit flush",
             },
@@ -286,6 +289,15 @@ def main() -> int:
             line["e2e"] = {"value": round(tokens_per_step / (ms_e2e / 1e3), 1), "unit": "tokens/s (whole job)",
                            "ms_per_step": round(ms_e2e, 3), "h2d_bytes_per_step": e2e[1], "d2h_bytes_per_step": e2e[2] * 1}
         print(json.dumps(line), flush=True)
+    if args.kernel_timing:
+        # profiling pass, after (and outside) the measurement: device time per kernel label from CUDA events
+        K.set_timing(True)
+        for s in range(2):
+            trainer.train_batch(dev_batches[s % len(dev_batches)])
+        report = K.timing_report()
+        K.set_timing(False)
+        if rank == 0:
+            print(f"per-kernel device time over 2 steps (rank 0):\n{K.format_timing(report)}", file=sys.stderr, flush=True)
     if world > 1:
         dist.barrier()
     dist_utils.teardown_distributed()

@@ -119,9 +119,117 @@ __global__ void __launch_bounds__(AR_THREADS)
   }
 }
 
+// Stream-ordered barrier of n GPUs through peer memory.  flags[r] is GPU r's flag array (n words, peer-mapped).  GPU
+// `me` publishes `epoch` in word `me` of every member's array (system-scope release after a system fence: whatever its
+// earlier kernels stored into peer memory is visible to a GPU that sees the flag), then waits until all n words of its
+// own array show `epoch` -- with a time limit, after which it records ERR_PEER_TIMEOUT and returns, so a missing peer
+// costs `timeout_ns` and an exception on the host, never a hung GPU.
+__global__ void peer_barrier_kernel(unsigned* const* __restrict__ flags, int me, int n, unsigned epoch,
+                                    long long timeout_ns, int* status) {
+  const int t = (int)threadIdx.x;
+  if (t >= n) return;
+  __threadfence_system();
+  unsigned* remote = flags[t] + me;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  const unsigned* own = flags[me] + t;
+  long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (unsigned it = 0;; ++it) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(own) : "memory");
+    if ((int)(v - epoch) >= 0) break;
+    if ((it & 63u) == 63u) {
+      long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (now - t0 > timeout_ns) {
+        report_error(status, ERR_PEER_TIMEOUT, 500, t);
+        break;
+      }
+    }
+    __nanosleep(200);
+  }
+}
+
+// dsts[s][i] = src[i] for every s != skip (16-byte words).  The destinations may be peer GPUs' memory: remote STORES
+// are posted, so a push runs at link rate with few bytes in flight, whereas remote loads pay a round trip each.
+template <int U>
+__global__ void __launch_bounds__(AR_THREADS)
+    push_copy_kernel(const uint4* __restrict__ src, uint4* const* __restrict__ dsts, int n_dst, int skip, long long n16) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + (U - 1) * stride < n16; i += U * stride) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) v[u] = src[i + u * stride];
+    for (int s = 0; s < n_dst; ++s) {
+      if (s == skip) continue;
+      uint4* d = dsts[s];
+#pragma unroll
+      for (int u = 0; u < U; ++u) d[i + u * stride] = v[u];
+    }
+  }
+  for (; i < n16; i += stride) {
+    const uint4 v = src[i];
+    for (int s = 0; s < n_dst; ++s)
+      if (s != skip) dsts[s][i] = v;
+  }
+}
+
+// dst[i] = src[i] (16-byte words, U loads in flight per thread); either side may be a peer GPU's memory
+template <int U>
+__global__ void __launch_bounds__(AR_THREADS)
+    copy16_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long n16) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + (U - 1) * stride < n16; i += U * stride) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) v[u] = __ldcg(src + i + u * stride);
+#pragma unroll
+    for (int u = 0; u < U; ++u) dst[i + u * stride] = v[u];
+  }
+  for (; i < n16; i += stride) dst[i] = __ldcg(src + i);
+}
+
 }  // namespace ob
 
 using namespace ob;
+
+extern "C" int ob_peer_barrier(unsigned* const* flags, int me, int n, unsigned epoch, long long timeout_ns, int* status,
+                               cudaStream_t stream) {
+  if (n <= 1) return 0;
+  if (n > 64 || me < 0 || me >= n) OB_FAIL(-7, "barrier: rank %d / group of %d not supported (max 64)", me, n);
+  if (timeout_ns <= 0) timeout_ns = 30LL * 1000 * 1000 * 1000;
+  peer_barrier_kernel<<<1, 64, 0, stream>>>(flags, me, n, epoch, timeout_ns, status);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_copy_bytes(void* dst, const void* src, long long bytes, int blocks, int unroll, cudaStream_t stream) {
+  if (bytes <= 0) return 0;
+  if ((bytes | (long long)reinterpret_cast<uintptr_t>(dst) | (long long)reinterpret_cast<uintptr_t>(src)) & 15)
+    OB_FAIL(-6, "copy: addresses and size must be multiples of 16 bytes");
+  const long long n16 = bytes >> 4;
+  if (blocks <= 0) blocks = 4 * sm_count();
+  const uint4* s = reinterpret_cast<const uint4*>(src);
+  uint4* d = reinterpret_cast<uint4*>(dst);
+  if (unroll >= 16) copy16_kernel<16><<<blocks, AR_THREADS, 0, stream>>>(s, d, n16);
+  else if (unroll >= 8) copy16_kernel<8><<<blocks, AR_THREADS, 0, stream>>>(s, d, n16);
+  else copy16_kernel<4><<<blocks, AR_THREADS, 0, stream>>>(s, d, n16);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_push_copy(void* const* dsts, const void* src, long long bytes, int n_dst, int skip, int blocks,
+                            cudaStream_t stream) {
+  if (bytes <= 0 || n_dst <= 0) return 0;
+  if ((bytes | (long long)reinterpret_cast<uintptr_t>(src)) & 15) OB_FAIL(-6, "push: source and size must be 16-byte multiples");
+  if (blocks <= 0) blocks = 2 * sm_count();
+  push_copy_kernel<4><<<blocks, AR_THREADS, 0, stream>>>(reinterpret_cast<const uint4*>(src),
+                                                         reinterpret_cast<uint4* const*>(dsts), n_dst, skip, bytes >> 4);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
 
 extern "C" int ob_fold_slots_bf16(void* out, const void* stage, long long n, int slots, long long slot_stride, int skip,
                                   int accumulate, cudaStream_t stream) {

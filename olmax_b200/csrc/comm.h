@@ -18,6 +18,18 @@ int ob_allreduce_multimem_f32(float* mc, long long n, int me, int world, int max
 int ob_reduce_slots_f32(const float* stage, float* acc, long long n, int R, long long slot_stride, float scale,
                         cudaStream_t stream);
 
+// Stream-ordered barrier of n GPUs over peer memory: flags = DEVICE array of the members' flag arrays (n words each,
+// zero-initialised, peer-mapped), epoch = 1, 2, 3, ... (the same sequence on every member).  A member that does not see
+// all others within timeout_ns (<= 0: 30 s) writes ERR_PEER_TIMEOUT (site 500) to status and returns.
+int ob_peer_barrier(unsigned* const* flags, int me, int n, unsigned epoch, long long timeout_ns, int* status,
+                    cudaStream_t stream);
+// dst = src (bytes, 16-byte multiples); either side may be peer memory.  blocks <= 0: 4 per SM; unroll 4 / 8 / 16 = 16-byte
+// loads in flight per thread (matters when src is remote).
+int ob_copy_bytes(void* dst, const void* src, long long bytes, int blocks, int unroll, cudaStream_t stream);
+// dsts[s] = src for every s != skip (dsts: DEVICE array of n_dst destination addresses, typically one per GPU of a
+// group: an all-gather as a push of the local piece into everybody's gathered buffer with posted remote stores)
+int ob_push_copy(void* const* dsts, const void* src, long long bytes, int n_dst, int skip, int blocks, cudaStream_t stream);
+
 // out[i] = (accumulate ? out[i] : 0) + sum over slots r != skip of stage[r * slot_stride + i]  (bf16 storage, fp32
 // sums, local memory): folds the staging slots of a fused GEMM -> reduce-scatter over a tensor-parallel group
 int ob_fold_slots_bf16(void* out, const void* stage, long long n, int slots, long long slot_stride, int skip,

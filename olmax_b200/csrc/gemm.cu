@@ -89,13 +89,21 @@ __device__ __forceinline__ void warp_copy16(const uint4* __restrict__ src, uint4
                                             int n_cw, int lane) {
   long long i = (long long)cw * 32 + lane;
   const long long step = (long long)n_cw * 32;
-  // 8 x 16 bytes per lane in flight: NVLink latency is a few microseconds, so the copy rate is set by the bytes in flight
-  for (; i + 7 * step < n16; i += 8 * step) {
-    uint4 v[8];
+  // COPY_UNROLL x 16 bytes per lane in flight (a 256-row block of a 4096-wide operand is ~14 words per lane)
+  constexpr int COPY_UNROLL = 8;
+  for (; i + (COPY_UNROLL - 1) * step < n16; i += COPY_UNROLL * step) {
+    uint4 v[COPY_UNROLL];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) v[u] = __ldcg(src + i + u * step);
+    for (int u = 0; u < COPY_UNROLL; ++u) v[u] = __ldcg(src + i + u * step);
 #pragma unroll
-    for (int u = 0; u < 8; ++u) dst[i + u * step] = v[u];
+    for (int u = 0; u < COPY_UNROLL; ++u) dst[i + u * step] = v[u];
+  }
+  for (; i + 3 * step < n16; i += 4 * step) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = __ldcg(src + i + u * step);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) dst[i + u * step] = v[u];
   }
   for (; i < n16; i += step) dst[i] = __ldcg(src + i);
 }
@@ -201,6 +209,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // Fused all-gather: the copy warps of every CTA fetch the shards in the order rank+1, rank+2, ... and the blocks
+      // of a shard in order, so arrival is monotone in  idx = ((shard - rank) mod S) * blocks + block.  The flag of a
+      // block is polled (an L2 round trip with acquire semantics) only while idx is beyond the newest block seen
+      // ready: once per block and CTA over the whole kernel instead of once per k-iteration.
+      int ag_ready_idx = p.ag_blocks - 1;   // the local shard is always present
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int mt, nt;
         decode_tile(tile, m_tiles, n_tiles, p.group_m, n_rot, p.m_rot, mt, nt);
@@ -215,12 +228,23 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 100);
           if (!ok) break;
           if (p.ag_shards > 0) {
-            if (p.ag_on_a)
-              ok = ag_wait(p, mt / p.m_tiles_per_shard, ((mt % p.m_tiles_per_shard) * BM) / AG_BLOCK_ROWS, abort_flag);
-            else
-              ok = B_MN ? ag_wait(p, k_shard, k_local / AG_BLOCK_ROWS, abort_flag)
-                        : ag_wait(p, n_shard, n_local0 / AG_BLOCK_ROWS, abort_flag);
-            if (!ok) break;
+            int ag_s, ag_b;
+            if (p.ag_on_a) {
+              ag_s = mt / p.m_tiles_per_shard;
+              ag_b = ((mt % p.m_tiles_per_shard) * BM) / AG_BLOCK_ROWS;
+            } else if (B_MN) {
+              ag_s = k_shard;
+              ag_b = k_local / AG_BLOCK_ROWS;
+            } else {
+              ag_s = n_shard;
+              ag_b = n_local0 / AG_BLOCK_ROWS;
+            }
+            const int ag_idx = ((ag_s - p.ag_rank + p.ag_shards) % p.ag_shards) * p.ag_blocks + ag_b;
+            if (ag_idx > ag_ready_idx) {
+              ok = ag_wait(p, ag_s, ag_b, abort_flag);
+              if (!ok) break;
+              ag_ready_idx = ag_idx;
+            }
           }
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;

@@ -240,7 +240,7 @@ class _GatedMLPFn(torch.autograd.Function):
                     M_s, d = dx.shape[0] // tpc.n, dx.shape[1]
                     stage, rs_kw = tpc.rs_begin(M_s, d)
                     _gemm_dgrad(du, up, out=dx, accumulate=True, extra=rs_kw)   # stores dx + du.Wu to the row owners
-                    dx = tpc.rs_finish(stage, M_s, d)
+                    dx = tpc.rs_finish(stage if rs_kw else dx, M_s, d)
                 else:
                     _gemm_dgrad(du, up, out=dx, accumulate=True)
         else:
@@ -298,7 +298,8 @@ class _TPColumnLinearsFn(torch.autograd.Function):
         stage, rs_kw = tpc.rs_begin(M_s, d)
         _gemm_dgrad(dys[-1], handles[-1], out=partial if partial is not None else stage,
                     accumulate=partial is not None, extra=rs_kw)
-        dx_local = tpc.rs_finish(stage, M_s, d)
+        # without the fused epilogue the sum sits in the local partial buffer and is reduce-scattered from there
+        dx_local = tpc.rs_finish(stage if (rs_kw or partial is None) else partial, M_s, d)
         return (dx_local, None) + (None,) * len(handles)
 
 
@@ -326,7 +327,7 @@ class _TPRowLinearFn(torch.autograd.Function):
         dy_full, ag_kw = tpc.gather_begin(dy_local.contiguous())
         dx = _gemm_dgrad(dy_full, handle, extra=ag_kw) if ctx.needs_input_grad[0] else None
         if dx is None:   # nobody pulled the peers' rows: complete the gather with the copy kernel
-            K.gather_shards(ag_kw["ag_src"], dy_full, dy_local.numel(), dy_local.numel(), tpc.n, tpc.rank)
+            tpc.finish_gather(dy_full, ag_kw)
         _gemm_wgrad(dy_full, x2, handle)
         return (dx.view(ctx.shape) if dx is not None else None), None, None
 

@@ -64,6 +64,9 @@ register_signature("ob_adamw", [_vp, _vp, _vp, _vp, _vp, _ll, _f, _f, _f, _f, _f
 register_signature("ob_sumsq", [_vp, _ll, _vp, _vp])
 register_signature("ob_clip_coef", [_vp, _f, _f, _vp, _vp])
 register_signature("ob_cast_f32_bf16", [_vp, _vp, _ll, _vp])
+register_signature("ob_peer_barrier", [_vp, _i, _i, ctypes.c_uint, _ll, _vp, _vp])
+register_signature("ob_copy_bytes", [_vp, _vp, _ll, _i, _i, _vp])
+register_signature("ob_push_copy", [_vp, _vp, _ll, _i, _i, _i, _vp])
 register_signature("ob_fold_slots_bf16", [_vp, _vp, _ll, _i, _ll, _i, _i, _vp])
 register_signature("ob_gather_shards", [_vp, _vp, _ll, _ll, _i, _i, _vp])
 register_signature("ob_scatter_add_shards", [_vp, _vp, _ll, _i, _f, _vp])
@@ -358,6 +361,27 @@ def allreduce_multimem(mc_ptr: int, n, me, world, max_blocks=0, device=None) -> 
     _count()
 
 
+def peer_barrier(table, me: int, n: int, epoch: int, timeout_s: float = 0.0) -> None:
+    """Stream-ordered barrier over peer memory (``csrc/comm.h``); a peer that never arrives costs ``timeout_s`` and a
+    :class:`KernelError` at the next ``check_status``, not a hang."""
+    dev = table.device
+    check(lib().ob_peer_barrier(table.data_ptr(), me, n, epoch & 0xFFFFFFFF, int(timeout_s * 1e9),
+                                status_buffer(dev).data_ptr(), stream_ptr(dev)), "peer_barrier")
+    _count()
+
+
+def copy_bytes(dst_ptr: int, src_ptr: int, nbytes: int, device, blocks: int = 0, unroll: int = 8) -> None:
+    """Raw copy between two addresses (either may be peer memory) with our copy kernel."""
+    check(lib().ob_copy_bytes(dst_ptr, src_ptr, nbytes, blocks, unroll, stream_ptr(device)), "copy_bytes")
+    _count()
+
+
+def push_copy(table, src, nbytes: int, n_dst: int, skip: int = -1, blocks: int = 0) -> None:
+    """dsts[s][:nbytes] = src for every s != skip; ``table``: device array of destination addresses (peers allowed)."""
+    check(lib().ob_push_copy(table.data_ptr(), src.data_ptr(), nbytes, n_dst, skip, blocks, stream_ptr(src.device)), "push_copy")
+    _count()
+
+
 def fold_slots_bf16(out, stage, n, slots, slot_stride, *, skip=-1, accumulate=False) -> None:
     """out[:n] = (out if accumulate) + sum over slots r != skip of stage[r * slot_stride : ... + n]  (bf16, fp32 sums)."""
     _req_bf16(out, stage)
@@ -371,3 +395,102 @@ def reduce_slots(stage, acc, n, R, slot_stride, scale=1.0) -> None:
     check(lib().ob_reduce_slots_f32(stage.data_ptr(), acc.data_ptr(), n, R, slot_stride, scale, stream_ptr(acc.device)),
           "reduce_slots")
     _count()
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# Optional per-kernel device timing (OLMAX_B200_KERNEL_TIMING=1): every wrapper above is bracketed by CUDA events on
+# the launching stream; `timing_report()` synchronises and sums them per label.  Events add a few microseconds of
+# host time per launch, so this is a profiling mode, not something to leave on for a measured run.
+# ----------------------------------------------------------------------------------------------------------------------
+import contextlib
+import functools
+import os
+
+_TIMED: list = []
+_TIMING_ON = os.environ.get("OLMAX_B200_KERNEL_TIMING", "0") == "1"
+
+
+def timing_enabled() -> bool:
+    return _TIMING_ON
+
+
+def set_timing(on: bool) -> None:
+    global _TIMING_ON
+    _TIMING_ON = bool(on)
+    _TIMED.clear()
+
+
+@contextlib.contextmanager
+def timed_region(label: str):
+    """Device time of everything enqueued on the current stream inside the block (collectives, copies, ...)."""
+    if not _TIMING_ON or not torch.cuda.is_available():
+        yield
+        return
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    try:
+        yield
+    finally:
+        e1.record()
+        _TIMED.append((label, e0, e1))
+
+
+def _gemm_label(args, kwargs) -> str:
+    M, N, Kd = args[3], args[4], args[5]
+    tags = []
+    if kwargs.get("a_mn"):
+        tags.append("A^T")
+    if kwargs.get("b_mn"):
+        tags.append("B^T")
+    epi = kwargs.get("epi", EPI_BF16)
+    tags.append(["bf16", "f32", "f32+=", "f32red", "swiglu", "geglu", "bf16+="][epi])
+    if kwargs.get("ag_src") is not None:
+        tags.append("AG(A)" if kwargs.get("ag_on_a") else "AG(B)")
+    if kwargs.get("c_shards") is not None:
+        tags.append("RS")
+    if kwargs.get("prefetch") is not None:
+        tags.append("pf")
+    return f"gemm {M}x{N}x{Kd} " + " ".join(tags)
+
+
+def _timed(name: str, fn):
+    @functools.wraps(fn)
+    def wrapper(*args, **kwargs):
+        if not _TIMING_ON:
+            return fn(*args, **kwargs)
+        label = _gemm_label(args, kwargs) if name == "gemm" else name
+        with timed_region(label):
+            return fn(*args, **kwargs)
+
+    return wrapper
+
+
+def timing_report(reset: bool = True) -> dict:
+    """{label: (launches, total device ms)} of the launches recorded since the last reset."""
+    if not _TIMED:
+        return {}
+    torch.cuda.synchronize()
+    out: dict = {}
+    for label, e0, e1 in _TIMED:
+        n, ms = out.get(label, (0, 0.0))
+        out[label] = (n + 1, ms + e0.elapsed_time(e1))
+    if reset:
+        _TIMED.clear()
+    return out
+
+
+def format_timing(report: dict, top: int = 40) -> str:
+    total = sum(ms for _, ms in report.values()) or 1.0
+    rows = sorted(report.items(), key=lambda kv: -kv[1][1])[:top]
+    lines = [f"{'label':58s} {'n':>6s} {'ms':>10s} {'share':>7s}"]
+    for label, (n, ms) in rows:
+        lines.append(f"{label[:58]:58s} {n:6d} {ms:10.3f} {100 * ms / total:6.1f}%")
+    lines.append(f"{'sum of timed regions':58s} {'':6s} {total:10.3f}")
+    return "\n".join(lines)
+
+
+for _name in ("gemm", "flash_attn_fwd", "flash_attn_bwd", "rmsnorm_fwd", "rmsnorm_bwd", "layernorm_fwd", "layernorm_bwd",
+              "rope", "glu_fwd", "glu_bwd", "embed_gather", "embed_scatter", "ce_fwd_bwd", "count_valid", "adamw", "sumsq",
+              "clip_coef", "cast_f32_bf16", "gather_shards", "scatter_add_shards", "allreduce_p2p", "allreduce_multimem",
+              "copy_bytes", "push_copy", "fold_slots_bf16", "reduce_slots", "peer_barrier"):
+    globals()[_name] = _timed(_name, globals()[_name])

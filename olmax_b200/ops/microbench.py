@@ -5,6 +5,8 @@ Kernel micro-benchmarks with CUDA-event timing (and the small cases used for ncu
     python -m olmax_b200.ops.microbench attn            # flash attention forward / backward, B=2 S=4096 H=32
     python -m olmax_b200.ops.microbench elementwise     # rmsnorm / rope / glu / adamw / cross-entropy bandwidth
     python -m olmax_b200.ops.microbench gemm --small    # one launch per variant on an 8192x4096x4096 case (for ncu)
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m olmax_b200.ops.microbench p2p
+                                                        # NVLink: remote loads (pull) vs remote stores (push)
 
 Every figure is the mean over ``--iters`` launches after 3 warm-up launches, timed with CUDA events on the launching
 stream with a synchronize on both sides; operands of a timed loop exceed the 126 MB L2 or rotate over several buffers.
@@ -166,9 +168,51 @@ def bench_elementwise(iters: int, small: bool):
     return out
 
 
+def bench_p2p(iters: int, small: bool):
+    """Peer-memory copy rates of our copy kernel between two GPUs (both ranks copy at the same time, so every figure
+    is per direction with the opposite direction busy): pull = remote loads + local stores, push = local loads +
+    remote stores.  Timed on the device, max over the two ranks."""
+    import os
+
+    import torch.distributed as dist
+    import torch.distributed._symmetric_memory as symm_mem
+
+    rank = int(os.environ.get("RANK", "0"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    if not dist.is_initialized():
+        dist.init_process_group("nccl")
+    assert dist.get_world_size() == 2, "run with 2 ranks"
+    dev = torch.device("cuda", torch.cuda.current_device())
+    nbytes = (32 if small else 256) * 2**20
+    buf = symm_mem.empty(nbytes // 2, dtype=torch.bfloat16, device=dev)
+    buf.normal_()
+    h = symm_mem.rendezvous(buf, dist.group.WORLD)
+    peer = int(h.buffer_ptrs[1 - rank])
+    local = torch.empty(nbytes // 2, dtype=torch.bfloat16, device=dev)
+    out = {}
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    for mode in ("pull", "push"):
+        for blocks_per_sm in (1, 2, 4, 8):
+            for unroll in (4, 8, 16):
+                dst, src = (local.data_ptr(), peer) if mode == "pull" else (peer, local.data_ptr())
+                fn = lambda: K.copy_bytes(dst, src, nbytes, dev, blocks=blocks_per_sm * sms, unroll=unroll)
+                dist.barrier()
+                ms = _time(fn, iters)
+                t = torch.tensor([ms], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                gbs = nbytes / t.item() / 1e6
+                out[f"{mode} blocks/SM={blocks_per_sm} unroll={unroll}"] = {"ms": round(t.item(), 4), "GB/s": round(gbs, 1)}
+                if rank == 0:
+                    print(f"{mode:5s} {blocks_per_sm} CTAs/SM x 512 thr, {unroll:2d} x 16 B in flight/thread: {t.item():7.3f} ms "
+                          f"{gbs:7.1f} GB/s per direction", flush=True)
+    dist.barrier()
+    _lib.check_status()
+    return out if rank == 0 else {}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn", "elementwise"])
+    ap.add_argument("what", choices=["gemm", "attn", "elementwise", "p2p"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--small", action="store_true", help="one launch per variant on a small case (for ncu)")
     ap.add_argument("--json", default=None, help="also write the results to this file")
@@ -176,9 +220,9 @@ def main():
     if not torch.cuda.is_available():
         print("needs a CUDA device")
         return 1
-    fn = {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise}[args.what]
+    fn = {"gemm": bench_gemm, "attn": bench_attn, "elementwise": bench_elementwise, "p2p": bench_p2p}[args.what]
     out = fn(args.iters, args.small)
-    if args.json:
+    if args.json and out:
         Path(args.json).write_text(json.dumps(out, indent=1))
     return 0
 

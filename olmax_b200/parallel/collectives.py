@@ -31,6 +31,13 @@ __all__ = [
 ]
 
 
+def _region(label: str):
+    """Device-time bracket of a collective when kernel timing is on (``ops.kernels.timed_region``)."""
+    from ..ops import kernels as K
+
+    return K.timed_region(label)
+
+
 def _is_gloo(group) -> bool:
     try:
         return dist.get_backend(group.pg) == "gloo"
@@ -118,11 +125,13 @@ class SeqAllGather(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):
         ctx.group = group
-        return all_gather(x, group, dim=0)
+        with _region("nccl seq all_gather"):
+            return all_gather(x, group, dim=0)
 
     @staticmethod
     def backward(ctx, dy):
-        return reduce_scatter(dy.contiguous(), ctx.group, dim=0), None
+        with _region("nccl seq reduce_scatter"):
+            return reduce_scatter(dy.contiguous(), ctx.group, dim=0), None
 
 
 class SeqReduceScatter(torch.autograd.Function):
@@ -131,11 +140,13 @@ class SeqReduceScatter(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):
         ctx.group = group
-        return reduce_scatter(x.contiguous(), group, dim=0)
+        with _region("nccl seq reduce_scatter"):
+            return reduce_scatter(x.contiguous(), group, dim=0)
 
     @staticmethod
     def backward(ctx, dy):
-        return all_gather(dy.contiguous(), ctx.group, dim=0), None
+        with _region("nccl seq all_gather"):
+            return all_gather(dy.contiguous(), ctx.group, dim=0), None
 
 
 class _CopyToTP(torch.autograd.Function):

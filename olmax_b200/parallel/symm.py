@@ -47,6 +47,42 @@ def symm_available(device: torch.device) -> bool:
     return dist.get_backend() == "nccl"
 
 
+class PeerBarrier:
+    """
+    Stream-ordered barrier over the GPUs ``ranks`` (global ranks) through peer-mapped flag words
+    (``ob_peer_barrier``): a single small kernel per member instead of an NCCL collective.  Every wait is bounded
+    (``OLMAX_B200_BARRIER_TIMEOUT_S``, default 600 s, the order of NCCL's own watchdog: ranks may legitimately be far
+    apart, e.g. while one of them writes a checkpoint): a member that never arrives makes the others record an error
+    that ``ops._lib.check_status`` raises, the GPUs stay usable.  ``OLMAX_B200_BARRIER=nccl`` falls back to a
+    one-element NCCL all-reduce on ``pg``.  Construction is collective over the whole job.
+    """
+
+    def __init__(self, ranks: List[int], my_index: int, pg, device: torch.device):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.n, self.me, self.pg = len(ranks), my_index, pg
+        self.use_flags = os.environ.get("OLMAX_B200_BARRIER", "flags") == "flags" and self.n <= 64
+        self.timeout_s = float(os.environ.get("OLMAX_B200_BARRIER_TIMEOUT_S", "600"))
+        self.epoch = 0
+        self._token = torch.zeros(1, dtype=torch.float32, device=device)
+        self._flags = symm_mem.empty(64, dtype=torch.int32, device=device)
+        self._flags.zero_()
+        self._h = symm_mem.rendezvous(self._flags, dist.group.WORLD)
+        self._table = K.pointer_table([int(self._h.buffer_ptrs[r]) for r in ranks], device)
+        # nobody may publish an epoch before every member has cleared its flags
+        dist.all_reduce(self._token)
+        torch.cuda.synchronize(device)
+
+    def __call__(self) -> None:
+        if self.n <= 1:
+            return
+        if not self.use_flags:
+            dist.all_reduce(self._token, group=self.pg)
+            return
+        self.epoch += 1
+        K.peer_barrier(self._table, self.me, self.n, self.epoch, self.timeout_s)
+
+
 class SymmContext:
     def __init__(self, store, numel: int):
         import torch.distributed._symmetric_memory as symm_mem
@@ -88,6 +124,10 @@ class SymmContext:
         self._tables: Dict[tuple, torch.Tensor] = {}
         self._token = torch.zeros(1, dtype=torch.float32, device=dev)
         self._sync_group = world if mesh.replicate.size > 1 else mesh.shard.pg
+        if mesh.replicate.size > 1:
+            self._barrier = PeerBarrier(list(range(mesh.world_size)), mesh.rank, world, dev)
+        else:
+            self._barrier = PeerBarrier(list(mesh.shard.ranks), mesh.shard.rank, mesh.shard.pg, dev)
         log.info("Peer-memory backend on: shard group %d, replicate group %d, %.1f MiB bf16 weights + %.1f MiB fp32 "
                  "gradients mapped per rank%s", self.R, mesh.replicate.size, numel * 2 / 2**20, numel * 4 / 2**20,
                  ", NVLS multicast" if self.multicast_ptr else "")
@@ -144,8 +184,8 @@ class SymmContext:
         return t
 
     def sync_peers(self) -> None:
-        """Stream-ordered barrier (a one-element NCCL all-reduce) over every rank that shares memory with this one."""
-        dist.all_reduce(self._token, group=self._sync_group)
+        """Stream-ordered barrier over every rank that shares memory with this one (:class:`PeerBarrier`)."""
+        self._barrier()
 
     def all_reduce_replicas(self) -> int:
         """Sum the fp32 gradient accumulator over the replicate group with our peer-memory kernel; returns the bytes
@@ -188,9 +228,20 @@ class TPSymmContext:
         self._flip_x = 0
         self._flip_s = 0
         self.flags = torch.zeros(self.n * 4096, dtype=torch.int32, device=device)
-        self._token = torch.zeros(1, dtype=torch.float32, device=device)
+        self._barrier = PeerBarrier(list(self.group.ranks), self.rank, self.group.pg, device)
         self.bytes_gathered = 0
         self.bytes_scattered = 0
+        # OLMAX_B200_TP_AG: how the row shards of a gathered activation reach this GPU.
+        #   copy (default): our copy kernel pulls them from the peers' buffers before the consuming GEMM (remote loads
+        #                   at ~640 GB/s per direction on this hardware);
+        #   gemm:           the consuming GEMM's copy warps pull them while its tensor cores work on the local rows
+        #                   (measured slower: the copy warps' loads starve next to the GEMM's own operand traffic);
+        #   nccl:           NCCL all-gather.
+        # OLMAX_B200_TP_RS=nccl reduce-scatters a row-parallel output with NCCL after the GEMM instead of in its epilogue.
+        self.ag_mode = os.environ.get("OLMAX_B200_TP_AG", "copy")
+        if self.ag_mode not in ("copy", "gemm", "nccl"):
+            raise ValueError(f"OLMAX_B200_TP_AG={self.ag_mode!r}: expected copy, gemm or nccl")
+        self.rs_in_gemm = os.environ.get("OLMAX_B200_TP_RS", "gemm") == "gemm"
         log.info("Tensor-parallel peer-memory context: group of %d (rank %d)", self.n, self.rank)
 
     def _symm_pair(self, numel: int, slot_offset_elems: int):
@@ -204,48 +255,72 @@ class TPSymmContext:
             t.zero_()
             h = symm_mem.rendezvous(t, dist.group.WORLD)
             ptrs = [int(p) for p in h.buffer_ptrs]
-            table = K.pointer_table([ptrs[r] + slot_offset_elems * 2 for r in self.group.ranks], self.device)
-            out.append((t, table, h))
+            addrs = [ptrs[r] + slot_offset_elems * 2 for r in self.group.ranks]
+            out.append((t, K.pointer_table(addrs, self.device), addrs))
         return out
 
     def barrier(self) -> None:
-        dist.all_reduce(self._token, group=self.group.pg)
+        self._barrier()
 
     # ---- all-gather -> GEMM -----------------------------------------------------------------------------------------
     def gather_begin(self, x_local: torch.Tensor):
         """x_local [M_s, d] bf16 -> (x_full [M, d] with rows of this rank filled, kwargs for the first consuming GEMM)."""
         M_s, d = x_local.shape
         numel = M_s * d
+        if self.ag_mode == "nccl":
+            from . import collectives as coll
+
+            with K.timed_region("nccl seq all_gather"):
+                return coll.all_gather(x_local, self.group, dim=0), {}
         if numel not in self._x:
             self._x[numel] = self._symm_pair(numel, 0)
-        buf, table, _ = self._x[numel][self._flip_x]
+        buf, table, addrs = self._x[numel][self._flip_x]
         self._flip_x ^= 1
-        buf.view(M_s, d).copy_(x_local)
-        x_full = torch.empty((self.n * M_s, d), dtype=x_local.dtype, device=x_local.device)
-        x_full[self.rank * M_s : (self.rank + 1) * M_s].copy_(x_local)
+        with K.timed_region("tp publish copies"):
+            buf.view(M_s, d).copy_(x_local)
+            x_full = torch.empty((self.n * M_s, d), dtype=x_local.dtype, device=x_local.device)
+            x_full[self.rank * M_s : (self.rank + 1) * M_s].copy_(x_local)
         self.barrier()   # every member's rows are in its buffer before anybody's GEMM pulls them
         self.bytes_gathered += (self.n - 1) * numel * 2
+        if self.ag_mode == "copy":
+            for ds in range(1, self.n):   # peers in the order rank+1, rank+2, ...: no two GPUs start on the same source
+                s = (self.rank + ds) % self.n
+                K.copy_bytes(x_full.data_ptr() + s * numel * 2, addrs[s], numel * 2, self.device, unroll=8)
+            return x_full, {}
         return x_full, {"ag_src": table, "ag_flags": self.flags, "ag_rank": self.rank, "ag_on_a": True, "M_s": M_s}
 
     def gather_now(self, x_local: torch.Tensor) -> torch.Tensor:
         """Same, completed by a copy kernel instead of a GEMM (for consumers that are not GEMM A operands)."""
         x_full, kw = self.gather_begin(x_local)
-        M_s, d = x_local.shape
-        K.gather_shards(kw["ag_src"], x_full, M_s * d, M_s * d, self.n, self.rank)
+        if kw:
+            self.finish_gather(x_full, kw)
         return x_full
+
+    def finish_gather(self, x_full: torch.Tensor, kw: dict) -> None:
+        """Complete a gather that no GEMM consumed (``kw`` from ``gather_begin``)."""
+        if kw:
+            numel = x_full.numel() // self.n
+            K.gather_shards(kw["ag_src"], x_full, numel, numel, self.n, self.rank)
 
     # ---- GEMM -> reduce-scatter -------------------------------------------------------------------------------------
     def rs_begin(self, M_s: int, N: int):
         """(staging tensor, kwargs for the GEMM whose [n * M_s, N] output is to be reduce-scattered)."""
         slot = M_s * N
+        if not self.rs_in_gemm:
+            full = torch.empty((self.n * M_s, N), dtype=torch.bfloat16, device=self.device)
+            return full, {}
         if slot not in self._stage:
             self._stage[slot] = self._symm_pair(self.n * slot, self.rank * slot)
-        buf, table, _ = self._stage[slot][self._flip_s]
+        buf, table, _addrs = self._stage[slot][self._flip_s]
         self._flip_s ^= 1
         # the peers' row blocks are computed first so that their transfer starts early; the local block comes last
         return buf, {"M_s": M_s, "c_shards": table, "m_shard_rot": (self.rank + 1) % self.n}
 
     def rs_finish(self, stage: torch.Tensor, M_s: int, N: int) -> torch.Tensor:
+        if not self.rs_in_gemm:
+            from . import collectives as coll
+
+            return coll.reduce_scatter(stage, self.group, dim=0)
         self.barrier()   # every member's stores into our slots have completed
         out = torch.empty((M_s, N), dtype=torch.bfloat16, device=self.device)
         K.fold_slots_bf16(out, stage, M_s * N, self.n, M_s * N, skip=-1, accumulate=False)

@@ -316,3 +316,27 @@ def test_context_parallel_matches_fsdp_on_two_gpus(strategy):
     assert all(abs(a - b) < 2e-2 * abs(b) for a, b in zip(lc, lf)), (lc, lf)
     for name in pf:
         assert rel_err(pc[name], pf[name]) < 1e-2, name
+
+
+def test_peer_barrier_times_out_and_reports():
+    """A member that never arrives: the bounded wait runs out, the kernel records the error and returns, the host
+    raises, and the GPU stays usable (the "missing peer" is a flag word that nothing sets; both flag arrays are local)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from olmax_b200.ops import _lib, kernels as K
+
+    dev = torch.device("cuda")
+    mine = torch.zeros(64, dtype=torch.int32, device=dev)
+    absent = torch.zeros(64, dtype=torch.int32, device=dev)
+    table = K.pointer_table([mine.data_ptr(), absent.data_ptr()], dev)
+    K.peer_barrier(table, 0, 2, 1, timeout_s=0.05)
+    torch.cuda.synchronize()
+    assert absent[0].item() == 1 and mine[0].item() == 1 and mine[1].item() == 0   # we published, the peer never did
+    with pytest.raises(K.KernelError, match="peer flag wait timed out"):
+        _lib.check_status()
+    # the error words were cleared by the check and the device still works; an arrived peer lets the barrier pass
+    mine[1] = 2
+    K.peer_barrier(table, 0, 2, 2, timeout_s=0.05)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert torch.ones(4, device=dev).sum().item() == 4
