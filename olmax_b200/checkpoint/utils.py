@@ -232,10 +232,10 @@ def save_sharded(directory: PathOrStr, store: ParamStore, buffers: Dict[str, tor
     def write() -> None:
         target.mkdir(parents=True, exist_ok=True)
         for key, m, idx, t in work:
-            adir = target / key
             if all(i == 0 for i in idx):
-                zarr3.write_metadata(adir, m.shape, m.local_shape, t.dtype)
-            zarr3.write_chunk(adir, idx, t)
+                zarr3.write_metadata(target / key, m.shape, m.local_shape, t.dtype)
+        # all of this rank's chunks at once: a native thread pool writes them in parallel (checksummed, atomic renames)
+        zarr3.write_chunks([(target / key, idx, t) for key, m, idx, t in work])
         if is_writer0:
             write_json(target / METADATA, meta_out)
 

@@ -2,7 +2,11 @@
 Minimal zarr v3 directory-store writer / reader for regular chunk grids.
 
 An array lives in its own directory: ``zarr.json`` (zarr v3 array metadata: shape, data_type, regular chunk grid,
-default chunk-key encoding ``c/i/j``, a single ``bytes`` little-endian codec) plus one file per chunk.  A parameter
+default chunk-key encoding ``c/i/j``, the ``bytes`` little-endian codec followed by the ``crc32c`` checksum codec, i.e.
+every chunk file ends in the 4-byte CRC-32C of its payload) plus one file per chunk.  Chunk files are written and read
+by the native library ``lib/libolmax_ckpt.so`` (``csrc/ckpt_io.cpp``: a thread pool outside the interpreter lock,
+atomic renames, checksum verification); when that library is missing (no C++ compiler) the same bytes are produced
+in Python.  A parameter
 sharded over ranks is exactly such a grid (chunk = one rank's shard), so every rank writes its own chunk files without
 gathering, and a reader can assemble any hyper-rectangle, which is what makes restoring under a different sharding
 possible.  The reference stores zarr v3 arrays too, but packed inside an OCDBT key-value database by TensorStore
@@ -11,6 +15,7 @@ possible.  The reference stores zarr v3 arrays too, but packed inside an OCDBT k
 
 from __future__ import annotations
 
+import ctypes
 import json
 import os
 from pathlib import Path
@@ -19,7 +24,8 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-__all__ = ["write_metadata", "write_chunk", "read_metadata", "read_region", "read_full", "TORCH_TO_ZARR"]
+__all__ = ["write_metadata", "write_chunk", "write_chunks", "read_metadata", "read_region", "read_full", "crc32c",
+           "TORCH_TO_ZARR"]
 
 TORCH_TO_ZARR = {
     torch.float32: "float32", torch.float64: "float64", torch.float16: "float16", torch.bfloat16: "bfloat16",
@@ -29,6 +35,67 @@ TORCH_TO_ZARR = {
 ZARR_TO_TORCH = {v: k for k, v in TORCH_TO_ZARR.items()}
 _ITEMSIZE = {"float32": 4, "float64": 8, "float16": 2, "bfloat16": 2, "int64": 8, "int32": 4, "int16": 2, "int8": 1,
              "uint8": 1, "bool": 1}
+
+
+# ---- native chunk I/O ------------------------------------------------------------------------------------------------
+_NATIVE = None
+_NATIVE_TRIED = False
+
+
+def _native():
+    """The checkpoint I/O library, built on first use when a C++ compiler exists; None otherwise."""
+    global _NATIVE, _NATIVE_TRIED
+    if _NATIVE_TRIED:
+        return _NATIVE
+    _NATIVE_TRIED = True
+    if os.environ.get("OLMAX_B200_CKPT_NATIVE", "1") != "1":
+        return None
+    try:
+        from ..csrc.build import build_host
+
+        lib = ctypes.CDLL(str(build_host()))
+        lib.ob_crc32c.restype = ctypes.c_uint32
+        lib.ob_crc32c.argtypes = [ctypes.c_void_p, ctypes.c_uint64]
+        sig = [ctypes.c_int, ctypes.POINTER(ctypes.c_char_p), ctypes.POINTER(ctypes.c_void_p),
+               ctypes.POINTER(ctypes.c_uint64), ctypes.c_int]
+        lib.ob_ckpt_write_files.restype = ctypes.c_int
+        lib.ob_ckpt_write_files.argtypes = sig + [ctypes.c_int, ctypes.c_int]
+        lib.ob_ckpt_read_files.restype = ctypes.c_int
+        lib.ob_ckpt_read_files.argtypes = sig + [ctypes.c_int]
+        lib.ob_ckpt_last_error.restype = ctypes.c_char_p
+        _NATIVE = lib
+    except Exception:  # noqa: BLE001  (no compiler, read-only tree, ...)
+        _NATIVE = None
+    return _NATIVE
+
+
+_CRC_TABLE: Optional[List[int]] = None
+
+
+def crc32c(data: bytes) -> int:
+    """CRC-32C (Castagnoli) of ``data``: native when the library is there, a table-driven loop otherwise."""
+    lib = _native()
+    if lib is not None:
+        buf = (ctypes.c_char * len(data)).from_buffer_copy(data) if len(data) else None
+        return int(lib.ob_crc32c(ctypes.cast(buf, ctypes.c_void_p) if buf is not None else None, len(data)))
+    global _CRC_TABLE
+    if _CRC_TABLE is None:
+        table = []
+        for i in range(256):
+            c = i
+            for _ in range(8):
+                c = (c >> 1) ^ 0x82F63B78 if c & 1 else c >> 1
+            table.append(c)
+        _CRC_TABLE = table
+    crc = 0xFFFFFFFF
+    for b in data:
+        crc = (crc >> 8) ^ _CRC_TABLE[(crc ^ b) & 0xFF]
+    return crc ^ 0xFFFFFFFF
+
+
+def _as_bytes_tensor(data: torch.Tensor) -> torch.Tensor:
+    t = data.detach().contiguous().cpu()
+    return t.view(torch.uint8).reshape(-1) if t.dim() else t.reshape(1).view(torch.uint8)
 
 
 def write_metadata(array_dir: Path, shape: Sequence[int], chunk_shape: Sequence[int], dtype: torch.dtype) -> None:
@@ -41,7 +108,7 @@ def write_metadata(array_dir: Path, shape: Sequence[int], chunk_shape: Sequence[
         "chunk_grid": {"name": "regular", "configuration": {"chunk_shape": [int(s) for s in chunk_shape] or [1]}},
         "chunk_key_encoding": {"name": "default", "configuration": {"separator": "/"}},
         "fill_value": 0,
-        "codecs": [{"name": "bytes", "configuration": {"endian": "little"}}],
+        "codecs": [{"name": "bytes", "configuration": {"endian": "little"}}, {"name": "crc32c"}],
         "attributes": {},
     }
     tmp = array_dir / f"zarr.json.tmp{os.getpid()}"
@@ -53,16 +120,38 @@ def _chunk_path(array_dir: Path, index: Sequence[int]) -> Path:
     return array_dir / "c" / Path(*[str(int(i)) for i in index]) if len(index) else array_dir / "c"
 
 
+def write_chunks(items: Sequence[Tuple[Path, Sequence[int], torch.Tensor]], n_threads: int = 8, fsync: bool = False) -> None:
+    """Write many chunks ``(array_dir, chunk index, tensor of exactly the chunk shape)`` atomically, in parallel."""
+    if not items:
+        return
+    paths, bufs = [], []
+    for array_dir, index, data in items:
+        path = _chunk_path(array_dir, index)
+        path.parent.mkdir(parents=True, exist_ok=True)
+        paths.append(path)
+        bufs.append(_as_bytes_tensor(data))
+    lib = _native()
+    if lib is not None:
+        n = len(items)
+        c_paths = (ctypes.c_char_p * n)(*[str(p).encode() for p in paths])
+        c_ptrs = (ctypes.c_void_p * n)(*[b.data_ptr() for b in bufs])
+        c_sizes = (ctypes.c_uint64 * n)(*[b.numel() for b in bufs])
+        rc = lib.ob_ckpt_write_files(n, c_paths, c_ptrs, c_sizes, 1, int(fsync), n_threads)
+        if rc != 0:
+            raise OSError(f"checkpoint write failed: {lib.ob_ckpt_last_error().decode()}")
+        return
+    for path, buf in zip(paths, bufs):
+        raw = buf.numpy().tobytes()
+        tmp = path.with_name(path.name + f".tmp{os.getpid()}")
+        with open(tmp, "wb") as f:
+            f.write(raw)
+            f.write(crc32c(raw).to_bytes(4, "little"))
+        os.replace(tmp, path)
+
+
 def write_chunk(array_dir: Path, index: Sequence[int], data: torch.Tensor) -> None:
     """Write one chunk (a CPU tensor of exactly the chunk shape) atomically."""
-    path = _chunk_path(array_dir, index)
-    path.parent.mkdir(parents=True, exist_ok=True)
-    t = data.detach().contiguous().cpu()
-    raw = t.view(torch.uint8).numpy().tobytes() if t.dtype == torch.bfloat16 else t.numpy().tobytes()
-    tmp = path.with_name(path.name + f".tmp{os.getpid()}")
-    with open(tmp, "wb") as f:
-        f.write(raw)
-    os.replace(tmp, path)
+    write_chunks([(array_dir, index, data)], n_threads=1)
 
 
 def read_metadata(array_dir: Path) -> Dict:
@@ -72,16 +161,35 @@ def read_metadata(array_dir: Path) -> Dict:
     return meta
 
 
-def _read_chunk(array_dir: Path, index: Sequence[int], chunk_shape: Sequence[int], dtype_name: str) -> torch.Tensor:
+def _has_crc(meta: Dict) -> bool:
+    return any(c.get("name") == "crc32c" for c in meta.get("codecs", []))
+
+
+def _read_chunk(array_dir: Path, index: Sequence[int], chunk_shape: Sequence[int], dtype_name: str,
+                has_crc: bool = False) -> torch.Tensor:
     path = _chunk_path(array_dir, index)
     n = int(np.prod(chunk_shape)) if len(chunk_shape) else 1
     if not path.exists():
         return torch.zeros(tuple(chunk_shape), dtype=ZARR_TO_TORCH[dtype_name])
-    raw = path.read_bytes()
     expect = n * _ITEMSIZE[dtype_name]
-    if len(raw) != expect:
-        raise ValueError(f"chunk {path} has {len(raw)} bytes, expected {expect} (truncated or corrupt checkpoint)")
-    buf = torch.frombuffer(bytearray(raw), dtype=torch.uint8)
+    lib = _native()
+    if lib is not None:
+        buf = torch.empty(expect, dtype=torch.uint8)
+        c_paths = (ctypes.c_char_p * 1)(str(path).encode())
+        c_ptrs = (ctypes.c_void_p * 1)(buf.data_ptr())
+        c_sizes = (ctypes.c_uint64 * 1)(expect)
+        if lib.ob_ckpt_read_files(1, c_paths, c_ptrs, c_sizes, int(has_crc), 1) != 0:
+            raise ValueError(lib.ob_ckpt_last_error().decode())
+    else:
+        raw = path.read_bytes()
+        if len(raw) != expect + (4 if has_crc else 0):
+            raise ValueError(f"chunk {path} has {len(raw)} bytes, expected {expect + (4 if has_crc else 0)} "
+                             f"(truncated or corrupt checkpoint)")
+        if has_crc:
+            raw, tail = raw[:expect], raw[expect:]
+            if crc32c(raw) != int.from_bytes(tail, "little"):
+                raise ValueError(f"chunk {path} checksum mismatch: corrupt checkpoint")
+        buf = torch.frombuffer(bytearray(raw), dtype=torch.uint8)
     return buf.view(ZARR_TO_TORCH[dtype_name]).reshape(tuple(chunk_shape))
 
 
@@ -90,8 +198,9 @@ def read_region(array_dir: Path, start: Sequence[int], shape: Sequence[int]) -> 
     meta = read_metadata(array_dir)
     full_shape = meta["shape"]
     dtype_name = meta["data_type"]
+    has_crc = _has_crc(meta)
     if len(full_shape) == 0:
-        return _read_chunk(array_dir, (), (), dtype_name).reshape(())
+        return _read_chunk(array_dir, (), (), dtype_name, has_crc).reshape(())
     cshape = meta["chunk_grid"]["configuration"]["chunk_shape"]
     out = torch.zeros(tuple(shape), dtype=ZARR_TO_TORCH[dtype_name])
     ranges = []
@@ -101,7 +210,7 @@ def read_region(array_dir: Path, start: Sequence[int], shape: Sequence[int]) -> 
     import itertools
 
     for idx in itertools.product(*ranges):
-        chunk = _read_chunk(array_dir, idx, cshape, dtype_name)
+        chunk = _read_chunk(array_dir, idx, cshape, dtype_name, has_crc)
         src_sl, dst_sl = [], []
         for d, ci in enumerate(idx):
             c0 = ci * cshape[d]

@@ -7,6 +7,9 @@ plain C interface (``extern "C"``) that :mod:`olmax_b200.ops._lib` loads with :m
 the PyTorch headers nor a GPU: nvcc cross-compiles on a CPU-only machine and the resulting ``.so`` is what runs on the
 B200.
 
+A second, host-only library, ``olmax_b200/lib/libolmax_ckpt.so`` (``ckpt_io.cpp``: threaded checkpoint chunk I/O with
+CRC-32C), is compiled with g++ by :func:`build_host`.
+
 Run as a script (``python -m olmax_b200.csrc.build``) or call :func:`build`.
 """
 
@@ -106,6 +109,27 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+CKPT_LIB_PATH = LIB_DIR / "libolmax_ckpt.so"
+
+
+def build_host(force: bool = False) -> Path:
+    """Compile the host-only checkpoint I/O library with the C++ compiler (no CUDA involved)."""
+    src = CSRC / "ckpt_io.cpp"
+    LIB_DIR.mkdir(exist_ok=True)
+    if not force and CKPT_LIB_PATH.exists() and CKPT_LIB_PATH.stat().st_mtime >= src.stat().st_mtime:
+        return CKPT_LIB_PATH
+    cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
+    if cxx is None:
+        raise RuntimeError("no C++ compiler found (set CXX)")
+    tmp = CKPT_LIB_PATH.with_suffix(".so.tmp%d" % os.getpid())
+    cmd = [cxx, "-O3", "-std=c++17", "-fPIC", "-shared", "-pthread", "-msse4.2", str(src), "-o", str(tmp)]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"{cxx} failed for ckpt_io.cpp:\n{res.stdout}\n{res.stderr}")
+    os.replace(tmp, CKPT_LIB_PATH)
+    return CKPT_LIB_PATH
+
+
 def is_stale() -> bool:
     """True when the library is missing or older than any source/header."""
     if not LIB_PATH.exists():
@@ -117,3 +141,4 @@ def is_stale() -> bool:
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(path)
+    print(build_host(force="--force" in sys.argv))

@@ -231,3 +231,43 @@ def test_persist_and_write_files(tmp_path):
     (tmp_path / "work" / "sub" / "f").write_text("x")
     trainer.persist_working_subdir("sub")
     assert (tmp_path / "save" / "sub" / "f").read_text() == "x"
+
+
+def test_native_chunk_io_checksums(tmp_path, monkeypatch):
+    """The native chunk writer / reader: known CRC-32C vector, same bytes as the Python fallback, a flipped byte of
+    equal length is detected on read, many chunks are written by the thread pool in one call."""
+    from olmax_b200.checkpoint import zarr3
+
+    assert zarr3._native() is not None, "the host checkpoint library should build wherever g++ exists"
+    assert zarr3.crc32c(b"123456789") == 0xE3069283
+    assert zarr3.crc32c(b"") == 0
+    data = torch.arange(4 * 6, dtype=torch.float32).view(4, 6)
+    a = tmp_path / "a"
+    zarr3.write_metadata(a, (8, 6), (4, 6), torch.float32)
+    zarr3.write_chunks([(a, (0, 0), data), (a, (1, 0), data + 100)])
+    raw = (a / "c" / "0" / "0").read_bytes()
+    assert len(raw) == 4 * 6 * 4 + 4
+    assert int.from_bytes(raw[-4:], "little") == zarr3.crc32c(raw[:-4])
+    assert torch.equal(zarr3.read_full(a), torch.cat([data, data + 100]))
+    assert torch.equal(zarr3.read_region(a, (2, 1), (4, 3)), torch.cat([data, data + 100])[2:6, 1:4])
+    # the Python fallback writes the same bytes and reads what the native writer wrote
+    monkeypatch.setattr(zarr3, "_NATIVE", None)
+    monkeypatch.setattr(zarr3, "_NATIVE_TRIED", True)
+    b = tmp_path / "b"
+    zarr3.write_metadata(b, (8, 6), (4, 6), torch.float32)
+    zarr3.write_chunks([(b, (0, 0), data)])
+    assert (b / "c" / "0" / "0").read_bytes() == raw
+    assert zarr3.crc32c(b"123456789") == 0xE3069283
+    assert torch.equal(zarr3.read_region(a, (0, 0), (4, 6)), data)
+    monkeypatch.undo()
+    # silent corruption: same length, one bit flipped
+    damaged = bytearray(raw)
+    damaged[10] ^= 0x01
+    (a / "c" / "0" / "0").write_bytes(bytes(damaged))
+    with pytest.raises(ValueError, match="checksum mismatch"):
+        zarr3.read_full(a)
+    # a bf16 scalar and a 0-d array survive the byte view
+    s = tmp_path / "s"
+    zarr3.write_metadata(s, (), (), torch.bfloat16)
+    zarr3.write_chunk(s, (), torch.tensor(1.5, dtype=torch.bfloat16))
+    assert zarr3.read_full(s).item() == 1.5

@@ -135,3 +135,18 @@ def test_env_configs(monkeypatch):
     assert x.gpu_all_gather_combine_threshold_bytes == 1024 * 1024 * 1024
     assert "--xla_gpu_enable_triton_gemm=false" in x.get_env_flags()
     assert ("NCCL_LL128_BUFFSIZE", "-2") in NCCLConfig().get_env_vars()
+
+
+def test_kernel_utils_without_a_gpu():
+    import torch
+
+    from olmax_b200.kernel_utils import assert_kernels, host_library_path, kernel_library_path, kernels_available
+
+    assert kernel_library_path().name == "libolmax_b200.so" and host_library_path().name == "libolmax_ckpt.so"
+    if torch.cuda.is_available():
+        assert kernels_available()
+        assert_kernels("anything")
+    else:
+        assert not kernels_available()
+        with pytest.raises(RuntimeError, match="flash attention requires a CUDA device"):
+            assert_kernels("flash attention")
