@@ -112,7 +112,9 @@ def build_mesh(mesh_type: str, world: int, local: int, shard_degree: Optional[in
     raise ValueError(mesh_type)
 
 
-def train(config: IntegrationTestConfig) -> Trainer:
+def train(config: IntegrationTestConfig, callbacks: Optional[Dict[str, Any]] = None) -> Trainer:
+    """Build mesh, model, trainer and synthetic data from ``config`` and run ``Trainer.fit``; ``callbacks`` (name ->
+    Callback) are attached in addition to the profiler."""
     mesh = config.mesh.build()
     set_mesh(mesh)
     seq = config.sequence_length
@@ -142,6 +144,8 @@ def train(config: IntegrationTestConfig) -> Trainer:
     )
     if config.profile:
         trainer.add_callback("profiler", ProfilerCallback())
+    for name, cb in (callbacks or {}).items():
+        trainer.add_callback(name, cb)
     loader = SyntheticDataLoader(
         fold_in(config.seed, 2), kind=config.data, vocab_size=config.model.vocab_size, sequence_length=seq,
         global_microbatch_instances=instances_per_dp_rank * dp, num_microbatches=config.num_microbatches,

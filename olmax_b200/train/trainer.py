@@ -279,7 +279,8 @@ class Trainer:
 
     def train_batch(self, batch: Sequence[Any]) -> torch.Tensor:
         """One optimizer step over the micro-batches of ``batch`` (host tensors, ideally pinned).  Returns the mean
-        micro-batch loss as a device scalar (not synchronised)."""
+        loss over the micro-batches and over all ranks (the global-batch loss, as the reference reports it) as a
+        device scalar; the host is not synchronised (the cross-rank mean is one asynchronous scalar all-reduce)."""
         model, optim = self._model, self._optimizer
         if len(batch) != optim.num_microbatches:
             optim.num_microbatches = len(batch)
@@ -296,7 +297,12 @@ class Trainer:
                 total = loss.detach() if total is None else total + loss.detach()
         with _nvtx("step_optimizer"):
             optim.step()
-        return total / len(batch)
+        mean = total / len(batch)
+        world = dist_utils.get_world_size()
+        if world > 1 and dist.is_initialized():
+            dist.all_reduce(mean)
+            mean = mean / world
+        return mean
 
     # ------------------------------------------------------------------ fit
     def fit(self, model, data_loader: DataLoader, load_path: Optional[PathOrStr] = None, buffer_cache: Any = None):
