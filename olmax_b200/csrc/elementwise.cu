@@ -59,7 +59,7 @@ __device__ __forceinline__ float row_sum(float v, float* red) {
 }
 
 constexpr int NORM_THREADS = 256;
-constexpr int MAX_VPT = 4;  // 8-element vectors per thread kept in registers
+constexpr int MAX_VPT = 4;  // most 8-element vectors per thread kept in registers (kernels are instantiated for 1, 2, 4)
 
 // Rows are addressed as  base + (row / heads) * ld + (row % heads) * d   (heads = 1, ld = d: plain 2-D tensor).
 __device__ __forceinline__ long long row_offset(long long row, int heads, long long ld, int d) {
@@ -67,7 +67,7 @@ __device__ __forceinline__ long long row_offset(long long row, int heads, long l
 }
 
 // t = x (+ res if add_before);  sum_out = t (optional);  y = t * rstd * w (+ res if !add_before and res given)
-template <int TPR>
+template <int TPR, int VPT>
 __global__ void __launch_bounds__(NORM_THREADS)
     rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res, const bf16* __restrict__ w,
                        bf16* __restrict__ y, bf16* __restrict__ sum_out, float* __restrict__ rstd_out, long long rows,
@@ -82,10 +82,10 @@ __global__ void __launch_bounds__(NORM_THREADS)
     const long long ox = live ? row_offset(row, heads, ld_x, d) : 0;
     const long long ores = live ? row_offset(row, heads, ld_res, d) : 0;
     const long long oy = live ? row_offset(row, heads, ld_y, d) : 0;
-    float t[MAX_VPT][8];
+    float t[VPT][8];
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAX_VPT; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       const int vi = tr + i * TPR;
       if (live && vi < nvec) {
         load8(x + ox + vi * 8, t[i]);
@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(NORM_THREADS)
     const float rstd = rsqrtf(ss / (float)d + eps);
     if (live && tr == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
 #pragma unroll
-    for (int i = 0; i < MAX_VPT; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       const int vi = tr + i * TPR;
       if (live && vi < nvec) {
         float wv[8], o[8];
@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(NORM_THREADS)
 }
 
 // dx = rstd * (w*dy - xhat * mean(w*dy*xhat)) (+ dsum);  dw += sum_rows dy * xhat  (fp32 atomics, accumulating)
-template <int TPR>
+template <int TPR, int VPT>
 __global__ void __launch_bounds__(NORM_THREADS)
     rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
                        const float* __restrict__ rstd_in, const bf16* __restrict__ dsum, bf16* __restrict__ dx,
@@ -135,9 +135,9 @@ __global__ void __launch_bounds__(NORM_THREADS)
   constexpr int ROWS_PER_BLOCK = NORM_THREADS / TPR;
   const int sub = threadIdx.x / TPR, tr = threadIdx.x % TPR;
   const int nvec = d / 8;
-  float dwacc[MAX_VPT][8];
+  float dwacc[VPT][8];
 #pragma unroll
-  for (int i = 0; i < MAX_VPT; ++i)
+  for (int i = 0; i < VPT; ++i)
 #pragma unroll
     for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
   for (long long row0 = (long long)blockIdx.x * ROWS_PER_BLOCK; row0 < rows; row0 += (long long)gridDim.x * ROWS_PER_BLOCK) {
@@ -147,10 +147,10 @@ __global__ void __launch_bounds__(NORM_THREADS)
     const long long ox = live ? row_offset(row, heads, ld_x, d) : 0;
     const long long odx = live ? row_offset(row, heads, ld_dx, d) : 0;
     const float rstd = live ? rstd_in[row] : 0.f;
-    float g[MAX_VPT][8], xh[MAX_VPT][8];
+    float g[VPT][8], xh[VPT][8];
     float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAX_VPT; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       const int vi = tr + i * TPR;
       if (live && vi < nvec) {
         float wv[8];
@@ -168,7 +168,7 @@ __global__ void __launch_bounds__(NORM_THREADS)
     }
     dot = row_sum<TPR>(dot, red) / (float)d;
 #pragma unroll
-    for (int i = 0; i < MAX_VPT; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       const int vi = tr + i * TPR;
       if (live && vi < nvec) {
         float o[8];
@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(NORM_THREADS)
   for (int i = threadIdx.x; i < d; i += NORM_THREADS) dw_part[i] = 0.f;
   __syncthreads();
 #pragma unroll
-  for (int i = 0; i < MAX_VPT; ++i) {
+  for (int i = 0; i < VPT; ++i) {
     const int vi = tr + i * TPR;
     if (vi < nvec) {
 #pragma unroll
@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(NORM_THREADS)
 
 // LayerNorm (`olmax/nn/functional.py:30-49`): y = (x - mean) * rstd * w (+ b), statistics over the row in fp32 (the
 // variance is taken around the mean from the registers that hold the row, not as E[x^2] - mean^2).
-template <int TPR>
+template <int TPR, int VPT>
 __global__ void __launch_bounds__(NORM_THREADS)
     layernorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ b,
                          bf16* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
@@ -218,10 +218,10 @@ __global__ void __launch_bounds__(NORM_THREADS)
     const long long row = row0 + sub;
     const bool live = row < rows;
     const long long off = live ? row * (long long)d : 0;
-    float t[MAX_VPT][8];
+    float t[VPT][8];
     float s1 = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAX_VPT; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       const int vi = tr + i * TPR;
       if (live && vi < nvec) {
         load8(x + off + vi * 8, t[i]);
@@ -232,7 +232,7 @@ __global__ void __launch_bounds__(NORM_THREADS)
     const float mean = row_sum<TPR>(s1, red) / (float)d;
     float s2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAX_VPT; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       const int vi = tr + i * TPR;
       if (live && vi < nvec) {
 #pragma unroll
@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(NORM_THREADS)
       rstd_out[row] = rstd;
     }
 #pragma unroll
-    for (int i = 0; i < MAX_VPT; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       const int vi = tr + i * TPR;
       if (live && vi < nvec) {
         float wv[8], o[8];
@@ -268,7 +268,7 @@ __global__ void __launch_bounds__(NORM_THREADS)
 }
 
 // g = w*dy;  dx = rstd * (g - mean(g) - xhat * mean(g*xhat));  dw += scale * sum_rows dy*xhat;  db += scale * sum_rows dy
-template <int TPR>
+template <int TPR, int VPT>
 __global__ void __launch_bounds__(NORM_THREADS)
     layernorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
                          const float* __restrict__ mean_in, const float* __restrict__ rstd_in, bf16* __restrict__ dx,
@@ -278,9 +278,9 @@ __global__ void __launch_bounds__(NORM_THREADS)
   constexpr int ROWS_PER_BLOCK = NORM_THREADS / TPR;
   const int sub = threadIdx.x / TPR, tr = threadIdx.x % TPR;
   const int nvec = d / 8;
-  float dwacc[MAX_VPT][8], dbacc[MAX_VPT][8];
+  float dwacc[VPT][8], dbacc[VPT][8];
 #pragma unroll
-  for (int i = 0; i < MAX_VPT; ++i)
+  for (int i = 0; i < VPT; ++i)
 #pragma unroll
     for (int j = 0; j < 8; ++j) dwacc[i][j] = dbacc[i][j] = 0.f;
   for (long long row0 = (long long)blockIdx.x * ROWS_PER_BLOCK; row0 < rows; row0 += (long long)gridDim.x * ROWS_PER_BLOCK) {
@@ -289,10 +289,10 @@ __global__ void __launch_bounds__(NORM_THREADS)
     const long long off = live ? row * (long long)d : 0;
     const float mean = live ? mean_in[row] : 0.f;
     const float rstd = live ? rstd_in[row] : 0.f;
-    float g[MAX_VPT][8], xh[MAX_VPT][8];
+    float g[VPT][8], xh[VPT][8];
     float sg = 0.f, sgx = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAX_VPT; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       const int vi = tr + i * TPR;
       if (live && vi < nvec) {
         float wv[8];
@@ -313,7 +313,7 @@ __global__ void __launch_bounds__(NORM_THREADS)
     sg = row_sum<TPR>(sg, red) / (float)d;
     sgx = row_sum<TPR>(sgx, red) / (float)d;
 #pragma unroll
-    for (int i = 0; i < MAX_VPT; ++i) {
+    for (int i = 0; i < VPT; ++i) {
       const int vi = tr + i * TPR;
       if (live && vi < nvec) {
         float o[8];
@@ -327,7 +327,7 @@ __global__ void __launch_bounds__(NORM_THREADS)
   for (int i = threadIdx.x; i < 2 * d; i += NORM_THREADS) part[i] = 0.f;
   __syncthreads();
 #pragma unroll
-  for (int i = 0; i < MAX_VPT; ++i) {
+  for (int i = 0; i < VPT; ++i) {
     const int vi = tr + i * TPR;
     if (vi < nvec) {
 #pragma unroll
@@ -507,96 +507,78 @@ static inline int grid_for(long long work_items, int threads, int max_blocks_per
 
 using namespace ob;
 
+// Thread layout of the normalisation kernels for a row of d elements: TPR threads share a row and each keeps VPT
+// 8-element vectors of it in registers.  Instantiating the smallest VPT that covers d keeps the register count (and
+// with it the number of resident blocks, i.e. the bytes in flight) right for the common widths.
+template <int T, int V>
+struct NormShape {
+  static constexpr int TPR = T, VPT = V;
+};
+template <typename F>
+static inline int norm_dispatch(int d, const char* what, F&& launch) {
+  if (d % 8 != 0) OB_FAIL(-1, "%s: d (%d) must be a multiple of 8", what, d);
+  if (d <= 128) launch(NormShape<16, 1>{});
+  else if (d <= 512) launch(NormShape<16, 4>{});
+  else if (d <= 2048) launch(NormShape<NORM_THREADS, 1>{});
+  else if (d <= 4096) launch(NormShape<NORM_THREADS, 2>{});
+  else if (d <= NORM_THREADS * 8 * MAX_VPT) launch(NormShape<NORM_THREADS, 4>{});
+  else OB_FAIL(-2, "%s: d (%d) too large (max %d)", what, d, NORM_THREADS * 8 * MAX_VPT);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 extern "C" int ob_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* sum_out, float* rstd,
                               long long rows, int d, int heads, long long ld_x, long long ld_res, long long ld_y,
                               int add_before, float eps, cudaStream_t stream) {
-  if (d % 8 != 0) OB_FAIL(-1, "rmsnorm: d (%d) must be a multiple of 8", d);
   if (rows <= 0) return 0;
-  const bf16* xp = (const bf16*)x; const bf16* rp = (const bf16*)res; const bf16* wp = (const bf16*)w;
-  bf16* yp = (bf16*)y; bf16* sp = (bf16*)sum_out;
-  if (d <= 512) {
-    constexpr int TPR = 16;
-    const int rpb = NORM_THREADS / TPR;
-    const int grid = grid_for((rows + rpb - 1) / rpb, 1);
-    rmsnorm_fwd_kernel<TPR><<<grid, NORM_THREADS, 0, stream>>>(xp, rp, wp, yp, sp, rstd, rows, d, heads, ld_x, ld_res,
-                                                                ld_y, add_before, eps);
-  } else {
-    if (d > NORM_THREADS * 8 * MAX_VPT) OB_FAIL(-2, "rmsnorm: d (%d) too large (max %d)", d, NORM_THREADS * 8 * MAX_VPT);
-    const int grid = grid_for(rows, 1);
-    rmsnorm_fwd_kernel<NORM_THREADS><<<grid, NORM_THREADS, 0, stream>>>(xp, rp, wp, yp, sp, rstd, rows, d, heads, ld_x,
-                                                                        ld_res, ld_y, add_before, eps);
-  }
-  OB_CUDA_OK(cudaGetLastError());
-  return 0;
+  return norm_dispatch(d, "rmsnorm", [&](auto shape) {
+    using S = decltype(shape);
+    const int rpb = NORM_THREADS / S::TPR;
+    rmsnorm_fwd_kernel<S::TPR, S::VPT><<<grid_for((rows + rpb - 1) / rpb, 1), NORM_THREADS, 0, stream>>>(
+        (const bf16*)x, (const bf16*)res, (const bf16*)w, (bf16*)y, (bf16*)sum_out, rstd, rows, d, heads, ld_x, ld_res,
+        ld_y, add_before, eps);
+  });
 }
 
 extern "C" int ob_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dsum,
                               void* dx, float* dw, long long rows, int d, int heads, long long ld_dy, long long ld_x,
                               long long ld_dx, float dw_scale, cudaStream_t stream) {
-  if (d % 8 != 0) OB_FAIL(-1, "rmsnorm: d (%d) must be a multiple of 8", d);
   if (rows <= 0) return 0;
   const size_t smem = (size_t)d * sizeof(float);
-  if (d <= 512) {
-    constexpr int TPR = 16;
-    const int rpb = NORM_THREADS / TPR;
-    int grid = grid_for((rows + rpb - 1) / rpb, 1, 4);
-    rmsnorm_bwd_kernel<TPR><<<grid, NORM_THREADS, smem, stream>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
-                                                                   (const bf16*)dsum, (bf16*)dx, dw, rows, d, heads,
-                                                                   ld_dy, ld_x, ld_dx, dw_scale);
-  } else {
-    if (d > NORM_THREADS * 8 * MAX_VPT) OB_FAIL(-2, "rmsnorm: d (%d) too large", d);
-    int grid = grid_for(rows, 1, 4);
-    rmsnorm_bwd_kernel<NORM_THREADS><<<grid, NORM_THREADS, smem, stream>>>(
+  return norm_dispatch(d, "rmsnorm", [&](auto shape) {
+    using S = decltype(shape);
+    const int rpb = NORM_THREADS / S::TPR;
+    rmsnorm_bwd_kernel<S::TPR, S::VPT><<<grid_for((rows + rpb - 1) / rpb, 1, 4), NORM_THREADS, smem, stream>>>(
         (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dsum, (bf16*)dx, dw, rows, d, heads, ld_dy,
         ld_x, ld_dx, dw_scale);
-  }
-  OB_CUDA_OK(cudaGetLastError());
-  return 0;
+  });
 }
 
 extern "C" int ob_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
                                 long long rows, int d, float eps, cudaStream_t stream) {
-  if (d % 8 != 0) OB_FAIL(-1, "layernorm: d (%d) must be a multiple of 8", d);
   if (mean == nullptr || rstd == nullptr) OB_FAIL(-3, "layernorm: the mean and rstd outputs are required");
   if (rows <= 0) return 0;
-  if (d <= 512) {
-    constexpr int TPR = 16;
-    const int rpb = NORM_THREADS / TPR;
-    layernorm_fwd_kernel<TPR><<<grid_for((rows + rpb - 1) / rpb, 1), NORM_THREADS, 0, stream>>>(
+  return norm_dispatch(d, "layernorm", [&](auto shape) {
+    using S = decltype(shape);
+    const int rpb = NORM_THREADS / S::TPR;
+    layernorm_fwd_kernel<S::TPR, S::VPT><<<grid_for((rows + rpb - 1) / rpb, 1), NORM_THREADS, 0, stream>>>(
         (const bf16*)x, (const bf16*)w, (const bf16*)b, (bf16*)y, mean, rstd, rows, d, eps);
-  } else {
-    if (d > NORM_THREADS * 8 * MAX_VPT) OB_FAIL(-2, "layernorm: d (%d) too large (max %d)", d, NORM_THREADS * 8 * MAX_VPT);
-    layernorm_fwd_kernel<NORM_THREADS><<<grid_for(rows, 1), NORM_THREADS, 0, stream>>>(
-        (const bf16*)x, (const bf16*)w, (const bf16*)b, (bf16*)y, mean, rstd, rows, d, eps);
-  }
-  OB_CUDA_OK(cudaGetLastError());
-  return 0;
+  });
 }
 
 extern "C" int ob_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
                                 void* dx, float* dw, float* db, long long rows, int d, float scale,
                                 cudaStream_t stream) {
-  if (d % 8 != 0) OB_FAIL(-1, "layernorm: d (%d) must be a multiple of 8", d);
   if (rows <= 0) return 0;
-  const size_t smem = (size_t)2 * d * sizeof(float);
-  if (d <= 512) {
-    constexpr int TPR = 16;
-    const int rpb = NORM_THREADS / TPR;
-    layernorm_bwd_kernel<TPR><<<grid_for((rows + rpb - 1) / rpb, 1, 4), NORM_THREADS, smem, stream>>>(
+  const size_t smem = (size_t)2 * d * sizeof(float);   // up to 64 KB for the widest rows
+  return norm_dispatch(d, "layernorm", [&](auto shape) {
+    using S = decltype(shape);
+    const int rpb = NORM_THREADS / S::TPR;
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(layernorm_bwd_kernel<S::TPR, S::VPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    layernorm_bwd_kernel<S::TPR, S::VPT><<<grid_for((rows + rpb - 1) / rpb, 1, 4), NORM_THREADS, smem, stream>>>(
         (const bf16*)dy, (const bf16*)x, (const bf16*)w, mean, rstd, (bf16*)dx, dw, db, rows, d, scale);
-  } else {
-    if (d > NORM_THREADS * 8 * MAX_VPT) OB_FAIL(-2, "layernorm: d (%d) too large", d);
-    static bool attr_set = false;   // 2 * d floats of shared memory: up to 64 KB
-    if (!attr_set) {
-      OB_CUDA_OK(cudaFuncSetAttribute(layernorm_bwd_kernel<NORM_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      2 * NORM_THREADS * 8 * MAX_VPT * (int)sizeof(float)));
-      attr_set = true;
-    }
-    layernorm_bwd_kernel<NORM_THREADS><<<grid_for(rows, 1, 4), NORM_THREADS, smem, stream>>>(
-        (const bf16*)dy, (const bf16*)x, (const bf16*)w, mean, rstd, (bf16*)dx, dw, db, rows, d, scale);
-  }
-  OB_CUDA_OK(cudaGetLastError());
-  return 0;
+  });
 }
 
 extern "C" int ob_rope(const void* x, void* y, const float* cos_t, const float* sin_t, int B, int S, int H, int D,

@@ -209,7 +209,8 @@ def test_blockwise_attention_composes_to_full_attention(K):
     _check_status()
 
 
-@pytest.mark.parametrize("rows,d,bias", [(300, 512, True), (70, 4096, True), (33, 8192, False), (257, 128, True)])
+@pytest.mark.parametrize("rows,d,bias", [(300, 512, True), (70, 4096, True), (33, 8192, False), (257, 128, True),
+                                           (65, 2048, True)])
 def test_layernorm(K, rows, d, bias):
     dev = "cuda"
     torch.manual_seed(8)
@@ -239,7 +240,7 @@ def test_layernorm(K, rows, d, bias):
     _check_status()
 
 
-@pytest.mark.parametrize("rows,d,heads", [(300, 512, 1), (64, 4096, 1), (100, 128, 6)])
+@pytest.mark.parametrize("rows,d,heads", [(300, 512, 1), (64, 4096, 1), (100, 128, 6), (77, 2048, 1), (40, 5120, 1)])
 def test_rmsnorm(K, rows, d, heads):
     dev = "cuda"
     torch.manual_seed(4)
