@@ -172,8 +172,12 @@ def test_small_shard_helpers():
     _check()
 
 
-def _train_worker(backend, mesh_kind="fsdp"):
+def _train_worker(backend, mesh_kind="fsdp", barrier="nccl"):
+    import os
+
     import torch.distributed as dist
+
+    os.environ["OLMAX_B200_BARRIER"] = barrier   # read when the peer-memory context is built
 
     from olmax_b200.models import DefaultTransformerConfig, ReorderedNormTransformerLayerConfig
     from olmax_b200.nn import MultiheadSelfAttentionConfig, RMSNormConfig
@@ -211,11 +215,13 @@ def _train_worker(backend, mesh_kind="fsdp"):
     return losses, first_grads.cpu(), full
 
 
-@pytest.mark.parametrize("mesh_kind,world", [("fsdp", 2), ("ddp", 2), ("hsdp", 4)])
-def test_peer_memory_backend_matches_nccl(mesh_kind, world):
+@pytest.mark.parametrize("mesh_kind,world,barrier", [("fsdp", 2, "nccl"), ("fsdp", 2, "flags"), ("ddp", 2, "nccl"),
+                                                      ("hsdp", 4, "flags")])
+def test_peer_memory_backend_matches_nccl(mesh_kind, world, barrier):
     if not torch.cuda.is_available() or torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    fused = run_distributed_test(_train_worker, world_size=world, backend="nccl", func_args=("fused", mesh_kind), timeout=300)
+    fused = run_distributed_test(_train_worker, world_size=world, backend="nccl", func_args=("fused", mesh_kind, barrier),
+                                 timeout=300)
     nccl = run_distributed_test(_train_worker, world_size=world, backend="nccl", func_args=("nccl", mesh_kind), timeout=300)
     for r in range(world):
         lf, gf, pf = fused[r]
