@@ -272,7 +272,7 @@ def main() -> int:
             "data": "synthetic uniform token ids, random-init weights",
             "config": {
                 "model": args.recipe, "global_batch": global_batch, "seq_len": seq, "microbatches": k,
-                "parallelism": f"{args.mesh.lower()}{world}", "optimizer": "AdamW fp32 master/moments",
+                "parallelism": f"{args.mesh.lower()}{world}", "optimizer": "AdamW fp32 master/moments, no gradient clipping (as in the reference's benchmark runs)",
                 "comm": ("fused peer-memory kernels" if (model.store.symm is not None or model.store.tp_symm is not None)
                          else ("nccl" if world > 1 else "none")),
                 "layers": model_cfg.num_layers, "params": model.num_params(), "activation_checkpointing": args.ac,

@@ -62,9 +62,15 @@ class AdamW:
         return float(self.schedule(self.count))
 
     @property
-    def grad_norm(self) -> torch.Tensor:
-        """Global gradient norm of the last step (device scalar; reading it synchronises)."""
-        return self._coef[1]
+    def tracks_grad_norm(self) -> bool:
+        cfg = self.config
+        return cfg.max_grad_norm is not None if cfg.track_grad_norm is None else bool(cfg.track_grad_norm)
+
+    @property
+    def grad_norm(self) -> Optional[torch.Tensor]:
+        """Global gradient norm of the last step (device scalar; reading it synchronises); None when it is not
+        computed (no clipping configured and ``track_grad_norm`` off)."""
+        return self._coef[1] if self.tracks_grad_norm else None
 
     def step(self) -> None:
         cfg, st = self.config, self.store
@@ -77,28 +83,32 @@ class AdamW:
         max_norm = float(cfg.max_grad_norm) if cfg.max_grad_norm is not None else 0.0
         decay_runs, nodecay_runs = st.decay_runs()
         if st.grad.is_cuda:
-            self._sumsq.zero_()
-            if st.mesh.tp.size > 1:
-                self._sumsq.copy_(st.global_grad_sumsq().double().view(1))
-            else:
-                K.sumsq(st.grad, self._sumsq)
-                if st.mesh.shard.size > 1:
-                    dist.all_reduce(self._sumsq, group=st.mesh.shard.pg)
-            K.clip_coef(self._sumsq, max_norm, 1.0, self._coef)
+            gscale = None
+            if self.tracks_grad_norm:
+                self._sumsq.zero_()
+                if st.mesh.tp.size > 1:
+                    self._sumsq.copy_(st.global_grad_sumsq().double().view(1))
+                else:
+                    K.sumsq(st.grad, self._sumsq)
+                    if st.mesh.shard.size > 1:
+                        dist.all_reduce(self._sumsq, group=st.mesh.shard.pg)
+                K.clip_coef(self._sumsq, max_norm, 1.0, self._coef)
+                gscale = self._coef
             for runs, wd in ((decay_runs, cfg.weight_decay), (nodecay_runs, 0.0)):
                 for s, e in runs:
                     K.adamw(st.master[s:e], self.exp_avg[s:e], self.exp_avg_sq[s:e], st.grad[s:e],
                             st.shadow[s:e] if st.shadow is not st.master else None, lr=lr, b1=cfg.b1, b2=cfg.b2,
-                            eps=cfg.eps, wd=wd, bias_corr1=bc1, bias_corr2=bc2, gscale=self._coef, zero_grad=True)
+                            eps=cfg.eps, wd=wd, bias_corr1=bc1, bias_corr2=bc2, gscale=gscale, zero_grad=True)
             st.invalidate_gathered()
             st.sync_peers()  # peers may read the new weights / add into the cleared accumulator only after this
         else:
-            norm = st.global_grad_sumsq().sqrt()
             coef = 1.0
-            if max_norm > 0.0:
-                coef = max_norm / max(max_norm, float(norm))
-            self._coef[0] = coef
-            self._coef[1] = norm
+            if self.tracks_grad_norm:
+                norm = st.global_grad_sumsq().sqrt()
+                if max_norm > 0.0:
+                    coef = max_norm / max(max_norm, float(norm))
+                self._coef[0] = coef
+                self._coef[1] = norm
             g = st.grad * coef if coef != 1.0 else st.grad
             self.exp_avg.mul_(cfg.b1).add_(g, alpha=1.0 - cfg.b1)
             self.exp_avg_sq.mul_(cfg.b2).addcmul_(g, g, value=1.0 - cfg.b2)

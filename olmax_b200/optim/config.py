@@ -147,6 +147,10 @@ class AdamWConfig(OptimConfig):
     weight_decay: float = 1e-4
     no_decay_modules: Optional[List[str]] = None
     max_grad_norm: Optional[float] = None
+    track_grad_norm: Optional[bool] = None
+    """Compute the global gradient norm every step (one pass over the gradient + a scalar all-reduce) for the
+    ``optim/g_norm`` metric.  None: only when ``max_grad_norm`` is set, which is when the reference has that metric
+    (it reads it from the clipping state, ``olmax/optim/utils.py:22-38``)."""
 
     def __post_init__(self):
         if self.lr is None:

@@ -379,7 +379,8 @@ class Trainer:
                 loss = self.train_batch(batch)
             self.record_metric(TrainMetrics.loss, loss)
             self.record_metric(TrainMetrics.lr, self._optimizer.last_lr)
-            self.record_metric(TrainMetrics.g_norm, self._optimizer.grad_norm)
+            if self._optimizer.grad_norm is not None:
+                self.record_metric(TrainMetrics.g_norm, self._optimizer.grad_norm)
             peak = get_peak_local_device_memory_usage()
             if peak is not None:
                 self.record_metric("system/peak device mem usage (MiB)", peak / 2**20)

@@ -130,7 +130,7 @@ def _loader(seed=0, k=2, num_batches=None):
 def _trainer(tmp_path, steps, **kw):
     from olmax_b200.optim import AdamWConfig, ConstantSchedule
 
-    return Trainer(work_dir=tmp_path, save_folder=tmp_path, optim=AdamWConfig(lr=ConstantSchedule(3e-3)),
+    return Trainer(work_dir=tmp_path, save_folder=tmp_path, optim=AdamWConfig(lr=ConstantSchedule(3e-3), track_grad_norm=True),
                    max_duration=Duration.steps(steps), global_tokens_per_batch=2 * 32 * 2, **kw)
 
 

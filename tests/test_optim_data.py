@@ -101,6 +101,18 @@ def test_clipping_and_microbatch_accumulation():
     assert clipped["a"].norm().item() == pytest.approx(min(0.5, norm.item()), rel=1e-4)
 
 
+def test_grad_norm_is_only_computed_when_asked_for():
+    model = _tiny()
+    plain = AdamWConfig(lr=ConstantSchedule(1e-3)).build(model)
+    assert not plain.tracks_grad_norm and plain.grad_norm is None          # as in the reference: no clipping, no norm
+    assert AdamWConfig(lr=ConstantSchedule(1e-3), max_grad_norm=1.0).build(model).tracks_grad_norm
+    tracked = AdamWConfig(lr=ConstantSchedule(1e-3), track_grad_norm=True).build(model)
+    model.store.grad.fill_(0.5)
+    want = model.store.grad.double().norm().item()
+    tracked.step()
+    assert tracked.grad_norm.item() == pytest.approx(want, rel=1e-5)
+
+
 def test_synthetic_data_generators():
     a = next(generate_batches_of_sequential_tokens(0, vocab_size=100, sequence_length=16, global_microbatch_instances=8,
                                                    num_microbatches=2, pin_memory=False))
