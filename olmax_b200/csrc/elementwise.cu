@@ -507,6 +507,17 @@ static inline int grid_for(long long work_items, int threads, int max_blocks_per
 
 using namespace ob;
 
+// Grid of a grid-stride normalisation kernel: exactly the number of blocks that are resident at once (occupancy x
+// SMs), never more -- a second, partly filled wave of blocks would run at a fraction of the memory parallelism.
+template <typename Kernel>
+static inline int resident_grid(Kernel kernel, long long work_blocks, size_t smem) {
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, NORM_THREADS, smem) != cudaSuccess || per_sm < 1)
+    per_sm = 1;
+  long long cap = (long long)sm_count() * per_sm;
+  return (int)(work_blocks < cap ? (work_blocks < 1 ? 1 : work_blocks) : cap);
+}
+
 // Thread layout of the normalisation kernels for a row of d elements: TPR threads share a row and each keeps VPT
 // 8-element vectors of it in registers.  Instantiating the smallest VPT that covers d keeps the register count (and
 // with it the number of resident blocks, i.e. the bytes in flight) right for the common widths.
@@ -534,7 +545,8 @@ extern "C" int ob_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
   return norm_dispatch(d, "rmsnorm", [&](auto shape) {
     using S = decltype(shape);
     const int rpb = NORM_THREADS / S::TPR;
-    rmsnorm_fwd_kernel<S::TPR, S::VPT><<<grid_for((rows + rpb - 1) / rpb, 1), NORM_THREADS, 0, stream>>>(
+    auto kernel = rmsnorm_fwd_kernel<S::TPR, S::VPT>;
+    kernel<<<resident_grid(kernel, (rows + rpb - 1) / rpb, 0), NORM_THREADS, 0, stream>>>(
         (const bf16*)x, (const bf16*)res, (const bf16*)w, (bf16*)y, (bf16*)sum_out, rstd, rows, d, heads, ld_x, ld_res,
         ld_y, add_before, eps);
   });
@@ -548,7 +560,8 @@ extern "C" int ob_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
   return norm_dispatch(d, "rmsnorm", [&](auto shape) {
     using S = decltype(shape);
     const int rpb = NORM_THREADS / S::TPR;
-    rmsnorm_bwd_kernel<S::TPR, S::VPT><<<grid_for((rows + rpb - 1) / rpb, 1, 4), NORM_THREADS, smem, stream>>>(
+    auto kernel = rmsnorm_bwd_kernel<S::TPR, S::VPT>;
+    kernel<<<resident_grid(kernel, (rows + rpb - 1) / rpb, smem), NORM_THREADS, smem, stream>>>(
         (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dsum, (bf16*)dx, dw, rows, d, heads, ld_dy,
         ld_x, ld_dx, dw_scale);
   });
@@ -561,7 +574,8 @@ extern "C" int ob_layernorm_fwd(const void* x, const void* w, const void* b, voi
   return norm_dispatch(d, "layernorm", [&](auto shape) {
     using S = decltype(shape);
     const int rpb = NORM_THREADS / S::TPR;
-    layernorm_fwd_kernel<S::TPR, S::VPT><<<grid_for((rows + rpb - 1) / rpb, 1), NORM_THREADS, 0, stream>>>(
+    auto kernel = layernorm_fwd_kernel<S::TPR, S::VPT>;
+    kernel<<<resident_grid(kernel, (rows + rpb - 1) / rpb, 0), NORM_THREADS, 0, stream>>>(
         (const bf16*)x, (const bf16*)w, (const bf16*)b, (bf16*)y, mean, rstd, rows, d, eps);
   });
 }
@@ -576,7 +590,8 @@ extern "C" int ob_layernorm_bwd(const void* dy, const void* x, const void* w, co
     const int rpb = NORM_THREADS / S::TPR;
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(layernorm_bwd_kernel<S::TPR, S::VPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    layernorm_bwd_kernel<S::TPR, S::VPT><<<grid_for((rows + rpb - 1) / rpb, 1, 4), NORM_THREADS, smem, stream>>>(
+    auto kernel = layernorm_bwd_kernel<S::TPR, S::VPT>;
+    kernel<<<resident_grid(kernel, (rows + rpb - 1) / rpb, smem), NORM_THREADS, smem, stream>>>(
         (const bf16*)dy, (const bf16*)x, (const bf16*)w, mean, rstd, (bf16*)dx, dw, db, rows, d, scale);
   });
 }
