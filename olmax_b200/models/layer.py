@@ -42,20 +42,24 @@ class _LayerBase(Module):
             self.attention = cfg.attention.build(d_model, window_size=window_size, init_std=init_std)
         with ctx.scope("mlp"):
             self.mlp = GatedMLP(d_model, hidden_size, bias=cfg.bias, activation=self.activation, init_std=init_std)
-        self._attn_fn = policy.wrap(self._attention_block, f"{self.checkpoint_name}.attention")
-        self._mlp_fn = policy.wrap(self._mlp_block, f"{self.checkpoint_name}.mlp")
         self._layer_fn = policy.wrap(self._forward_impl, self.checkpoint_name)
         self._whole_layer = policy.should_recompute(self.checkpoint_name)
+        # sub-block regions (`layers.i.attention`, `layers.i.mlp`): recomputed on their own unless the whole layer
+        # already is (a nested checkpoint would run the sub-block's forward a third time)
+        self._attn_fn, self._mlp_fn = self._attention_block, self._mlp_block
+        if not self._whole_layer:
+            self._attn_fn = policy.wrap(self._attention_block, f"{self.checkpoint_name}.attention")
+            self._mlp_fn = policy.wrap(self._mlp_block, f"{self.checkpoint_name}.mlp")
 
     def _norm(self, name: str, cfg: "TransformerLayerConfig", size: int):
         with current_build_context().scope(name):
             return cfg.norm.build(size)
 
     def _attention_block(self, x, batch_size, cache):
-        raise NotImplementedError
+        return self.attention(x, batch_size, cache)
 
     def _mlp_block(self, x):
-        raise NotImplementedError
+        return self.mlp(x)
 
     def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor], batch_size: int,
                 cache: Optional[BufferCache] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
@@ -84,9 +88,9 @@ class TransformerLayer(_LayerBase):
             x, n = self.attention_norm(delta, residual=x, mode="pre")
         else:
             n = self.attention_norm(x)
-        a = self.attention(n, batch_size, cache)
+        a = self._attn_fn(n, batch_size, cache)
         h, n2 = self.mlp_norm(a, residual=x, mode="pre")
-        m = self.mlp(n2)
+        m = self._mlp_fn(n2)
         return h, m
 
 
@@ -100,9 +104,9 @@ class ReorderedNormTransformerLayer(_LayerBase):
 
     def _forward_impl(self, x, delta, batch_size, cache):
         assert delta is None
-        a = self.attention(x, batch_size, cache)
+        a = self._attn_fn(x, batch_size, cache)
         h = self.attention_norm(a, residual=x, mode="post")
-        m = self.mlp(h)
+        m = self._mlp_fn(h)
         out = self.mlp_norm(m, residual=h, mode="post")
         return out, None
 
@@ -121,9 +125,9 @@ class GemmaTransformerLayer(_LayerBase):
 
     def _forward_impl(self, x, delta, batch_size, cache):
         assert delta is None
-        a = self.attention(self.attention_input_norm(x), batch_size, cache)
+        a = self._attn_fn(self.attention_input_norm(x), batch_size, cache)
         h = self.attention_norm(a, residual=x, mode="post")
-        m = self.mlp(self.mlp_input_norm(h))
+        m = self._mlp_fn(self.mlp_input_norm(h))
         out = self.mlp_norm(m, residual=h, mode="post")
         return out, None
 

@@ -96,16 +96,27 @@ def test_recomputation_does_not_change_loss_or_gradients(policy):
         cfg = DefaultTransformerConfig(vocab_size=48, d_model=32, hidden_size=64, num_layers=2,
                                        layer=GemmaTransformerLayerConfig(attention=attn), layer_ac_policy=pol)
         model = cfg.build(seed=2, mesh_resource=MeshResource.FSDP(1), device=torch.device("cpu"))
+        calls = {"attention": 0, "mlp": 0}
+        # forward executions of the sub-blocks, recomputation included (pre-hooks: a recomputation stops as soon as the
+        # last tensor the backward pass needs has been produced, so it may never reach the end of the block)
+        for layer in model.layers:
+            layer.attention.register_forward_pre_hook(lambda *a: calls.__setitem__("attention", calls["attention"] + 1))
+            layer.mlp.register_forward_pre_hook(lambda *a: calls.__setitem__("mlp", calls["mlp"] + 1))
         ids = torch.randint(0, 48, (2, 12), generator=torch.Generator().manual_seed(1))
         loss, _ = model(ids, torch.roll(ids, -1, 1))
         loss.backward()
         model.store.finish_backward()
-        return loss.item(), model.store.grad.clone()
+        return loss.item(), model.store.grad.clone(), calls
 
-    want_loss, want_grad = run(None)
-    loss, grad = run(policy)
+    want_loss, want_grad, base_calls = run(None)
+    assert base_calls == {"attention": 2, "mlp": 2}
+    loss, grad, calls = run(policy)
     assert loss == pytest.approx(want_loss, rel=1e-6)
     assert torch.allclose(grad, want_grad, rtol=1e-5, atol=1e-7)
+    # what is not saved runs exactly twice (forward + one recomputation), what is saved runs once
+    want_calls = {NothingSaveable: {"attention": 4, "mlp": 4}, SaveAnythingExceptTheseNames: {"attention": 2, "mlp": 4},
+                  SaveOnlyTheseNames: {"attention": 2, "mlp": 4}}[type(policy)]
+    assert calls == want_calls
 
 
 def test_profiler_callback_schedule(tmp_path):
