@@ -28,5 +28,8 @@ from .mesh import (
     TPStyle,
     get_mesh,
     set_mesh,
+    shard_map,
 )
+from .context import (CPStrategy, context_parallel_attention, cp_local_positions,
+                      inverse_reorder_causal_load_balancing, reorder_causal_load_balancing, shard_sequence_for_cp)
 from .param_store import FSDPUnit, ParamHandle, ParamMeta, ParamStore

@@ -27,6 +27,7 @@ from ..types import StrEnum
 from . import dist_utils
 
 __all__ = [
+    "shard_map",
     "TPStyle",
     "DataParallelType",
     "DataParallelConfig",
@@ -386,3 +387,11 @@ def set_mesh(mesh: Optional[DeviceMesh]) -> None:
 
 def get_mesh() -> Optional[DeviceMesh]:
     return _CURRENT
+
+
+def shard_map(fun, mesh: Optional[DeviceMesh] = None, in_specs=None, out_specs=None, **_ignored):
+    """Counterpart of the reference's ``shard_map`` wrapper (``olmax/distributed/parallel.py:404-407``).  Under JAX it
+    turns a function over global arrays into a per-shard function; with one process per device every function already
+    runs on this rank's shards and calls the collectives of :mod:`olmax_b200.parallel.collectives` explicitly, so the
+    function is returned unchanged (the specs are accepted so that call sites keep their shape)."""
+    return fun

@@ -24,6 +24,12 @@ __all__ = [
     "fold_in",
     "split_seed",
     "shaped_rng_split",
+    "maybe_rng_split",
+    "vmap_multiple",
+    "abs_sq",
+    "is_in_jit",
+    "uncommit_single_device_arrays",
+    "with_optional_sharding_contraint",
 ]
 
 
@@ -120,3 +126,46 @@ def shaped_rng_split(seed: int, shape: Sequence[int]) -> Any:
     if len(shape) == 0:
         return seed
     return [shaped_rng_split(fold_in(seed, i), shape[1:]) for i in range(shape[0])]
+
+
+def maybe_rng_split(seed: Optional[int], num: int = 2) -> List[Optional[int]]:
+    """``num`` seeds derived from ``seed``, or ``num`` Nones when there is no seed (``olmax/jax_utils.py:127-135``)."""
+    if seed is None:
+        return [None] * num
+    return split_seed(seed, num)
+
+
+def vmap_multiple(fun: Callable, n: int) -> Callable:
+    """``fun`` vectorised over ``n`` leading dimensions (``olmax/jax_utils.py:15-21``; ``torch.func.vmap`` applied n times)."""
+    for _ in range(n):
+        fun = torch.func.vmap(fun)
+    return fun
+
+
+def abs_sq(x: torch.Tensor) -> torch.Tensor:
+    """|x|^2 without a square root, also for complex tensors (``olmax/jax_utils.py:93-102``)."""
+    if x.is_complex():
+        return x.real.square() + x.imag.square()
+    return x.square()
+
+
+def is_in_jit() -> bool:
+    """True while a graph compiler traces the caller (``olmax/jax_utils.py:76-77``).  The hot path here is eager kernels
+    on streams, so this is only ever true when a user wraps something in ``torch.compile`` themselves."""
+    try:
+        return bool(torch.compiler.is_compiling())
+    except Exception:
+        return False
+
+
+def uncommit_single_device_arrays(tree: Any) -> Any:
+    """Accepted for source compatibility (``olmax/jax_utils.py:32-44``): JAX arrays can be "committed" to a device, which
+    restricts where later computations may run; PyTorch tensors have no such state, so the tree is returned as is."""
+    return tree
+
+
+def with_optional_sharding_contraint(tree: Any, sharding: Any = None, cond: Optional[Callable[[torch.Tensor], bool]] = None) -> Any:
+    """Accepted for source compatibility (``olmax/jax_utils.py:61-73``, spelling as in the reference): a sharding
+    constraint is a hint to an SPMD partitioner.  Here every process holds exactly its shard and placement is explicit
+    (``parallel/param_store.py``), so there is nothing to constrain and the tree is returned as is."""
+    return tree

@@ -150,3 +150,25 @@ def test_kernel_utils_without_a_gpu():
         assert not kernels_available()
         with pytest.raises(RuntimeError, match="flash attention requires a CUDA device"):
             assert_kernels("flash attention")
+
+
+def test_tree_compat_helpers():
+    import torch
+
+    from olmax_b200.parallel import shard_map
+    from olmax_b200.utils.tree import (abs_sq, is_in_jit, maybe_rng_split, uncommit_single_device_arrays, vmap_multiple,
+                                       with_optional_sharding_contraint)
+
+    assert maybe_rng_split(None, 3) == [None, None, None]
+    a, b = maybe_rng_split(7, 2)
+    assert a != b and maybe_rng_split(7, 2) == [a, b]
+    f = vmap_multiple(lambda v: v.sum(), 2)
+    x = torch.arange(24.0).view(2, 3, 4)
+    assert torch.equal(f(x), x.sum(-1))
+    z = torch.tensor([3 + 4j])
+    assert abs_sq(z).item() == 25 and abs_sq(torch.tensor([-2.0])).item() == 4
+    assert is_in_jit() is False
+    tree = {"w": torch.ones(2)}
+    assert uncommit_single_device_arrays(tree) is tree and with_optional_sharding_contraint(tree, None, None) is tree
+    g = lambda t: t + 1  # noqa: E731
+    assert shard_map(g, None, in_specs=(), out_specs=()) is g
