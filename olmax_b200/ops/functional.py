@@ -194,22 +194,24 @@ class _GatedMLPFn(torch.autograd.Function):
             kw.update(ag_kw)
             K.gemm(x2, gfirst, a, M, h, d, epi=K.EPI_GEGLU if act != "silu" else K.EPI_SWIGLU, b2=ufirst, c2=g, c3=u,
                    ldb=d, **kw)
+            # Everything the backward pass needs exists now.  Saving it BEFORE the down projection lets a recomputation
+            # of this block (activation checkpointing stops as soon as the saved tensors are back) skip that GEMM.
+            ctx.save_for_backward(x2, g, u)
             if tpc is not None:
                 M_s = M // tpc.n
                 stage, rs_kw = tpc.rs_begin(M_s, d)
                 _gemm_fwd(a, down, out=stage, extra=rs_kw)
                 del a
                 y = tpc.rs_finish(stage, M_s, d)
-                ctx.save_for_backward(x2, g, u)
                 return y.view(*shp[:-1], d)
             y = _gemm_fwd(a, down)
             del a
-        else:
-            g = x2 @ gate.full().t()
-            u = x2 @ up.full().t()
-            a = ref.glu(g, u, act)
-            y = a @ down.full().t()
+            return y.view(*shp[:-1], y.shape[-1])
+        g = x2 @ gate.full().t()
+        u = x2 @ up.full().t()
+        a = ref.glu(g, u, act)
         ctx.save_for_backward(x2, g, u)
+        y = a @ down.full().t()
         return y.view(*shp[:-1], y.shape[-1])
 
     @staticmethod

@@ -6,7 +6,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-from olmax_b200.activation_checkpointing import NothingSaveable
+from olmax_b200.activation_checkpointing import NothingSaveable, SaveAnythingExceptTheseNames
 from olmax_b200.models import (
     DefaultTransformerConfig,
     DefaultTransformerLayerConfig,
@@ -36,6 +36,10 @@ CASES = {
     "olmo2_head_qk_gqa": dict(layer_cls=ReorderedNormTransformerLayerConfig, qk=True, headwise=True, kv=2),
     "gemma": dict(layer_cls=GemmaTransformerLayerConfig, kv=2, softcap=50.0, fsoft=30.0, tie=True, window=100),
     "llama_remat": dict(layer_cls=DefaultTransformerLayerConfig, ac=NothingSaveable()),
+    "gemma_mlp_remat": dict(layer_cls=GemmaTransformerLayerConfig, kv=2, softcap=50.0,
+                            ac=SaveAnythingExceptTheseNames(names=["layers.*.mlp"])),
+    "olmo2_attention_remat": dict(layer_cls=ReorderedNormTransformerLayerConfig, qk=True, headwise=True,
+                                  ac=SaveAnythingExceptTheseNames(names=["layers.*.attention"])),
 }
 
 
