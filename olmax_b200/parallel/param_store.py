@@ -373,6 +373,7 @@ class ParamStore:
             u.numel_full_2d = max(1, sum(int(math.prod(h.meta.tp_shape)) for h in u.params if len(h.meta.shape) == 2))
             off += uoff
         self.numel_local = off
+        self.validate_layout()
         dev = self.device
         self.master = torch.zeros(off, dtype=self.param_dtype, device=dev)
         use_symm = False
@@ -408,6 +409,34 @@ class ParamStore:
         self._finalized = True
         if init:
             self.init_parameters(seed)
+
+    def validate_layout(self) -> None:
+        """Host-side check of the flat layout the kernels rely on: units tile the buffer in order, parameter slices lie
+        inside their unit without overlapping, every slice starts on a 64-element boundary (128 bytes in bf16: TMA
+        descriptors, 16-byte vector accesses and the line-coalesced peer stores all assume it) and every 2-D parameter's
+        rows are a multiple of 8 elements long.  Raises ``OLMaxConfigurationError`` with the offending parameter."""
+        end_prev_unit = 0
+        for u in self.units:
+            if u.offset != end_prev_unit:
+                raise OLMaxConfigurationError(f"unit {u.name} starts at {u.offset}, expected {end_prev_unit}")
+            end_prev = 0
+            for h in u.params:
+                m = h.meta
+                if m.unit_offset % 64 or m.offset != u.offset + m.unit_offset:
+                    raise OLMaxConfigurationError(f"{m.name}: slice offset {m.offset} (unit offset {m.unit_offset}) is misplaced")
+                if m.unit_offset < end_prev:
+                    raise OLMaxConfigurationError(f"{m.name}: slice overlaps the previous parameter of unit {u.name}")
+                if m.numel_local != int(math.prod(m.local_shape)) or m.numel_local <= 0:
+                    raise OLMaxConfigurationError(f"{m.name}: local shape {m.local_shape} does not match {m.numel_local} elements")
+                if len(m.local_shape) == 2 and m.local_shape[1] % 8 and self.device.type == "cuda":
+                    raise OLMaxConfigurationError(f"{m.name}: rows of {m.local_shape[1]} elements are not a multiple of 8 "
+                                                  f"(16 bytes), which the TMA descriptors of the GEMM need")
+                end_prev = m.unit_offset + m.numel_local
+            if end_prev > u.numel_local:
+                raise OLMaxConfigurationError(f"unit {u.name}: parameters extend past the unit ({end_prev} > {u.numel_local})")
+            end_prev_unit = u.offset + u.numel_local
+        if end_prev_unit != self.numel_local:
+            raise OLMaxConfigurationError(f"flat buffer has {self.numel_local} elements, units cover {end_prev_unit}")
 
     def _alloc_shadow(self, numel: int) -> torch.Tensor:
         return torch.zeros(numel, dtype=self.compute_dtype, device=self.device)

@@ -238,3 +238,22 @@ def test_layer_variants_and_model_shapes():
         loss, _ = model(ids, torch.roll(ids, -1, 1))
         assert loss.ndim == 0 and abs(loss.item() - math.log(32)) < 0.5      # near-uniform prediction at init
         assert model.num_params() == sum(model.store.full_parameter(n).numel() for n in names)
+
+
+def test_param_store_layout_validation():
+    from olmax_b200.exceptions import OLMaxConfigurationError
+
+    lin = _build(lambda: Linear(24, 16, bias=True))
+    store = lin.store
+    store.validate_layout()                                   # a finalized store is consistent
+    metas = {m.name: m for m in store.metas}
+    assert metas["weight"].offset % 64 == 0 and metas["bias"].offset % 64 == 0
+    assert metas["bias"].offset >= metas["weight"].offset + metas["weight"].numel_local
+    saved = metas["bias"].unit_offset
+    metas["bias"].unit_offset = metas["weight"].unit_offset   # two parameters on top of each other
+    metas["bias"].offset = metas["weight"].offset
+    with pytest.raises(OLMaxConfigurationError, match="overlaps"):
+        store.validate_layout()
+    metas["bias"].unit_offset, metas["bias"].offset = saved + 8, store.units[0].offset + saved + 8
+    with pytest.raises(OLMaxConfigurationError, match="misplaced"):
+        store.validate_layout()
