@@ -194,9 +194,7 @@ class _GatedMLPFn(torch.autograd.Function):
             kw.update(ag_kw)
             K.gemm(x2, gfirst, a, M, h, d, epi=K.EPI_GEGLU if act != "silu" else K.EPI_SWIGLU, b2=ufirst, c2=g, c3=u,
                    ldb=d, **kw)
-            # Everything the backward pass needs exists now.  Saving it BEFORE the down projection lets a recomputation
-            # of this block (activation checkpointing stops as soon as the saved tensors are back) skip that GEMM.
-            ctx.save_for_backward(x2, g, u)
+            ctx.save_for_backward(x2, g, u)   # act(g) * u is not kept: backward recomputes it inside glu_bwd
             if tpc is not None:
                 M_s = M // tpc.n
                 stage, rs_kw = tpc.rs_begin(M_s, d)
