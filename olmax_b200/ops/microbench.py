@@ -5,6 +5,7 @@ Kernel micro-benchmarks with CUDA-event timing (and the small cases used for ncu
     python -m olmax_b200.ops.microbench attn            # flash attention forward / backward, B=2 S=4096 H=32
     python -m olmax_b200.ops.microbench elementwise     # rmsnorm / rope / glu / adamw / cross-entropy bandwidth
     python -m olmax_b200.ops.microbench gemm --small    # one launch per variant on an 8192x4096x4096 case (for ncu)
+    python -m olmax_b200.ops.microbench elementwise --small   # one rmsnorm fwd + bwd launch on [8192, 4096] (for ncu)
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m olmax_b200.ops.microbench p2p
                                                         # NVLink: remote loads (pull) vs remote stores (push)
 
@@ -129,6 +130,18 @@ def bench_elementwise(iters: int, small: bool):
         out[name] = {"ms": round(ms, 4), "GB/s": round(gbs, 1), "of_measured_copy": round(gbs / bw, 3)}
         print(f"{name:28s} {ms:7.3f} ms  {gbs:8.1f} GB/s  {gbs / bw:5.2f} of measured copy bandwidth", flush=True)
 
+    if small:   # one launch of each normalisation kernel on [8192, 4096] (201 MB of traffic in the backward: beyond L2)
+        rows, d = 8192, 4096
+        x = torch.randn(rows, d, device=dev, dtype=torch.bfloat16)
+        w = torch.ones(d, device=dev, dtype=torch.bfloat16)
+        y, dx = torch.empty_like(x), torch.empty_like(x)
+        rstd = torch.empty(rows, device=dev, dtype=torch.float32)
+        dw = torch.zeros(d, device=dev, dtype=torch.float32)
+        K.rmsnorm_fwd(x, w, y, rows=rows, d=d, eps=1e-5, rstd=rstd)
+        K.rmsnorm_bwd(y, x, w, rstd, dx, rows=rows, d=d, dw=dw)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        return {}
     rows, d = 32768, 4096          # 256 MiB per tensor: larger than L2
     x = torch.randn(rows, d, device=dev, dtype=torch.bfloat16)
     res = torch.randn_like(x)
