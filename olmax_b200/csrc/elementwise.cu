@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(NORM_THREADS)
 
 // dx = rstd * (w*dy - xhat * mean(w*dy*xhat)) (+ dsum);  dw += sum_rows dy * xhat  (fp32 atomics, accumulating)
 template <int TPR, int VPT>
-__global__ void __launch_bounds__(NORM_THREADS)
+__global__ void __launch_bounds__(NORM_THREADS, VPT <= 2 ? 4 : 2)
     rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
                        const float* __restrict__ rstd_in, const bf16* __restrict__ dsum, bf16* __restrict__ dx,
                        float* __restrict__ dw, long long rows, int d, int heads, long long ld_dy, long long ld_x,
