@@ -49,7 +49,9 @@ class _LayerBase(Module):
         self._attn_fn, self._mlp_fn = self._attention_block, self._mlp_block
         if not self._whole_layer:
             self._attn_fn = policy.wrap(self._attention_block, f"{self.checkpoint_name}.attention")
-            self._mlp_fn = policy.wrap(self._mlp_block, f"{self.checkpoint_name}.mlp")
+            # the MLP block recomputes inside its own autograd node (only its gate/up GEMM runs again) instead of being
+            # wrapped in a checkpoint, which would also repeat the down projection
+            self.mlp.recompute = policy.should_recompute(f"{self.checkpoint_name}.mlp")
 
     def _norm(self, name: str, cfg: "TransformerLayerConfig", size: int):
         with current_build_context().scope(name):

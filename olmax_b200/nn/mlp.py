@@ -20,6 +20,9 @@ class GatedMLP(Module):
             raise ValueError("GatedMLP has no bias (the fused kernels and tensor parallelism do not support one)")
         ctx = current_build_context()
         self.activation = activation
+        self.recompute = False
+        """Set by the layer when the activation-checkpointing policy recomputes this block: only the block input is
+        kept for backward and the gate/up GEMM runs again there."""
         with ctx.scope("gate_proj"):
             self.gate_proj = Linear(d_model, hidden_size, tp_style=TPStyle.colwise, init_std=init_std)
         with ctx.scope("up_proj"):
@@ -31,7 +34,9 @@ class GatedMLP(Module):
         tp = self.mesh.tp
         tpc = self.store.tp_symm if x.is_cuda else None
         if tpc is not None:   # both tensor-parallel collectives are fused into the GEMMs of the block
-            return F.gated_mlp(x, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight, self.activation, tpc)
+            return F.gated_mlp(x, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight, self.activation, tpc,
+                               recompute=self.recompute)
         x = coll.seq_all_gather(x, tp)
-        y = F.gated_mlp(x, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight, self.activation)
+        y = F.gated_mlp(x, self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight, self.activation,
+                        recompute=self.recompute)
         return coll.seq_reduce_scatter(y, tp)

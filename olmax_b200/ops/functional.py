@@ -170,13 +170,31 @@ class _GatedMLPFn(torch.autograd.Function):
     """``tpc`` (a ``TPSymmContext``; GPU only): x holds this rank's rows of the sequence-parallel activation; their
     all-gather is fused into the gate/up GEMM and the reduce-scatter of the output into the down GEMM's epilogue
     (forward), and symmetrically in backward (gather of dy into the down dgrad, reduce-scatter of dx out of the
-    up dgrad, which folds in the gate dgrad's partial sum)."""
+    up dgrad, which folds in the gate dgrad's partial sum).
+
+    ``recompute``: keep only the block's input for backward and run the gate/up GEMM again there (activation
+    checkpointing of the block at the price of that one GEMM: the gate / up pre-activations, 2 x [tokens, hidden],
+    are neither written in forward nor held until backward)."""
 
     @staticmethod
-    def forward(ctx, x, gate, up, down, act, tpc=None):
+    def _gate_up(x2, gate, up, act, a, g, u, ag_kw):
+        """a = act(x2 Wg^T) * (x2 Wu^T); g / u receive the two pre-activations when given."""
+        M, d = x2.shape
+        h = gate.tp_shape[0]
+        gfirst, kw = _b_operand(gate)
+        ufirst, _ = up.pieces()
+        kw.update(_ag_kwargs(gate, up))
+        kw["prefetch"] = gate.store.prefetch_slice(2 * h * d)
+        if ag_kw:
+            kw.update(ag_kw)
+        K.gemm(x2, gfirst, a, M, h, d, epi=K.EPI_GEGLU if act != "silu" else K.EPI_SWIGLU, b2=ufirst, c2=g, c3=u,
+               ldb=d, **kw)
+
+    @staticmethod
+    def forward(ctx, x, gate, up, down, act, tpc=None, recompute=False):
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
-        ctx.handles, ctx.act, ctx.shape, ctx.tpc = (gate, up, down), act, shp, tpc
+        ctx.handles, ctx.act, ctx.shape, ctx.tpc, ctx.recompute = (gate, up, down), act, shp, tpc, recompute
         if _on_gpu(x):
             x2 = x2.contiguous()
             ag_kw = {}
@@ -185,16 +203,13 @@ class _GatedMLPFn(torch.autograd.Function):
             M, d = x2.shape
             h = gate.tp_shape[0]
             a = torch.empty((M, h), dtype=torch.bfloat16, device=x.device)
-            g = torch.empty_like(a)
-            u = torch.empty_like(a)
-            gfirst, kw = _b_operand(gate)
-            ufirst, _ = up.pieces()
-            kw.update(_ag_kwargs(gate, up))
-            kw["prefetch"] = gate.store.prefetch_slice(2 * h * d)
-            kw.update(ag_kw)
-            K.gemm(x2, gfirst, a, M, h, d, epi=K.EPI_GEGLU if act != "silu" else K.EPI_SWIGLU, b2=ufirst, c2=g, c3=u,
-                   ldb=d, **kw)
-            ctx.save_for_backward(x2, g, u)   # act(g) * u is not kept: backward recomputes it inside glu_bwd
+            g = u = None
+            if not recompute:
+                g = torch.empty_like(a)
+                u = torch.empty_like(a)
+            _GatedMLPFn._gate_up(x2, gate, up, act, a, g, u, ag_kw)
+            # act(g) * u is never kept: backward gets it back from glu_bwd
+            ctx.save_for_backward(*((x2,) if recompute else (x2, g, u)))
             if tpc is not None:
                 M_s = M // tpc.n
                 stage, rs_kw = tpc.rs_begin(M_s, d)
@@ -208,25 +223,33 @@ class _GatedMLPFn(torch.autograd.Function):
         g = x2 @ gate.full().t()
         u = x2 @ up.full().t()
         a = ref.glu(g, u, act)
-        ctx.save_for_backward(x2, g, u)
+        ctx.save_for_backward(*((x2,) if recompute else (x2, g, u)))
         y = a @ down.full().t()
         return y.view(*shp[:-1], y.shape[-1])
 
     @staticmethod
     def backward(ctx, dy):
-        x2, g, u = ctx.saved_tensors
         gate, up, down = ctx.handles
         dy2 = dy.reshape(-1, dy.shape[-1])
         tpc = ctx.tpc
+        if ctx.recompute:
+            (x2,) = ctx.saved_tensors
+            g = u = None
+        else:
+            x2, g, u = ctx.saved_tensors
         if _on_gpu(dy2):
             dy2 = dy2.contiguous()
             ag_kw = None
             if tpc is not None:
                 dy2, ag_kw = tpc.gather_begin(dy2)
             da = _gemm_dgrad(dy2, down, extra=ag_kw)
+            a = torch.empty((x2.shape[0], gate.tp_shape[0]), dtype=torch.bfloat16, device=dy2.device)
+            if ctx.recompute:   # the gate / up pre-activations again (x2 is already the gathered activation under TP)
+                g = torch.empty_like(a)
+                u = torch.empty_like(a)
+                _GatedMLPFn._gate_up(x2, gate, up, ctx.act, a, g, u, None)
             dg = torch.empty_like(g)
             du = torch.empty_like(u)
-            a = torch.empty_like(g)
             K.glu_bwd(g, u, da, dg, du, a, gelu=ctx.act != "silu")
             del da
             _gemm_wgrad(dy2, a, down)
@@ -244,6 +267,9 @@ class _GatedMLPFn(torch.autograd.Function):
                 else:
                     _gemm_dgrad(du, up, out=dx, accumulate=True)
         else:
+            if ctx.recompute:
+                g = x2 @ gate.full().t()
+                u = x2 @ up.full().t()
             with torch.enable_grad():
                 gg = g.detach().requires_grad_(True)
                 uu = u.detach().requires_grad_(True)
@@ -254,13 +280,14 @@ class _GatedMLPFn(torch.autograd.Function):
             gate.add_grad(dg.t() @ x2)
             up.add_grad(du.t() @ x2)
             dx = dg @ gate.full() + du @ up.full() if ctx.needs_input_grad[0] else None
-        return (dx.view(ctx.shape) if dx is not None else None), None, None, None, None, None
+        return (dx.view(ctx.shape) if dx is not None else None), None, None, None, None, None, None
 
 
-def gated_mlp(x: torch.Tensor, gate, up, down, act: str = "silu", tpc=None) -> torch.Tensor:
+def gated_mlp(x: torch.Tensor, gate, up, down, act: str = "silu", tpc=None, recompute: bool = False) -> torch.Tensor:
     """``down(act(gate(x)) * up(x))``.  With ``tpc`` x is this rank's row shard of a sequence-parallel activation and
-    so is the result (the tensor-parallel collectives are fused into the GEMMs)."""
-    return _GatedMLPFn.apply(x, gate, up, down, act, tpc if x.is_cuda else None)
+    so is the result (the tensor-parallel collectives are fused into the GEMMs).  ``recompute``: hold only x for the
+    backward pass and run the gate/up GEMM again there."""
+    return _GatedMLPFn.apply(x, gate, up, down, act, tpc if x.is_cuda else None, bool(recompute) and torch.is_grad_enabled())
 
 
 # ----------------------------------------------------------------------------------------------------------------------

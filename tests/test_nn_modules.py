@@ -257,3 +257,25 @@ def test_param_store_layout_validation():
     metas["bias"].unit_offset, metas["bias"].offset = saved + 8, store.units[0].offset + saved + 8
     with pytest.raises(OLMaxConfigurationError, match="misplaced"):
         store.validate_layout()
+
+
+def test_gated_mlp_selective_recomputation_keeps_only_its_input():
+    """recompute=True: same values and gradients, and the autograd node holds one tensor (x) instead of three."""
+    from olmax_b200.ops import functional as F
+
+    mlp = _build(lambda: GatedMLP(16, 40))
+    w = (mlp.gate_proj.weight, mlp.up_proj.weight, mlp.down_proj.weight)
+    x = torch.randn(7, 16)
+    outs = {}
+    for recompute in (False, True):
+        mlp.store.zero_grad()
+        xi = x.clone().requires_grad_(True)
+        y = F.gated_mlp(xi, *w, "silu", recompute=recompute)
+        saved = len(y.grad_fn.saved_tensors)
+        y.square().sum().backward()
+        outs[recompute] = (y.detach(), xi.grad.clone(), mlp.store.grad.clone(), saved)
+    assert outs[False][3] == 3 and outs[True][3] == 1
+    for a, b in zip(outs[False][:3], outs[True][:3]):
+        assert torch.allclose(a, b, atol=1e-6)
+    with torch.no_grad():      # nothing to recompute without a backward pass
+        assert F.gated_mlp(x, *w, "silu", recompute=True).shape == (7, 16)
