@@ -9,8 +9,11 @@ A launch counter (:func:`launch_count`) records how many of our kernels were enq
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
+import functools
 import math
+import os
 from typing import Optional, Sequence, Tuple
 
 import torch
@@ -22,7 +25,10 @@ __all__ = [
     "EPI_BF16", "EPI_F32", "EPI_F32_ACC", "EPI_F32_RED", "EPI_SWIGLU", "EPI_GEGLU", "EPI_BF16_ACC",
     "gemm", "flash_attn_fwd", "flash_attn_bwd", "rmsnorm_fwd", "rmsnorm_bwd", "rope", "glu_fwd", "glu_bwd",
     "embed_gather", "embed_scatter", "ce_fwd_bwd", "count_valid", "adamw", "sumsq", "clip_coef", "cast_f32_bf16",
+    "layernorm_fwd", "layernorm_bwd", "gather_shards", "scatter_add_shards", "allreduce_p2p", "allreduce_multimem",
+    "peer_barrier", "copy_bytes", "push_copy", "fold_slots_bf16", "reduce_slots",
     "launch_count", "reset_launch_count", "pointer_table",
+    "timing_enabled", "set_timing", "timed_region", "timing_report", "format_timing",
 ]
 
 EPI_BF16, EPI_F32, EPI_F32_ACC, EPI_F32_RED, EPI_SWIGLU, EPI_GEGLU, EPI_BF16_ACC = range(7)
@@ -402,10 +408,6 @@ def reduce_slots(stage, acc, n, R, slot_stride, scale=1.0) -> None:
 # the launching stream; `timing_report()` synchronises and sums them per label.  Events add a few microseconds of
 # host time per launch, so this is a profiling mode, not something to leave on for a measured run.
 # ----------------------------------------------------------------------------------------------------------------------
-import contextlib
-import functools
-import os
-
 _TIMED: list = []
 _TIMING_ON = os.environ.get("OLMAX_B200_KERNEL_TIMING", "0") == "1"
 

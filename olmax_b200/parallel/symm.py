@@ -290,13 +290,6 @@ class TPSymmContext:
             return x_full, {}
         return x_full, {"ag_src": table, "ag_flags": self.flags, "ag_rank": self.rank, "ag_on_a": True, "M_s": M_s}
 
-    def gather_now(self, x_local: torch.Tensor) -> torch.Tensor:
-        """Same, completed by a copy kernel instead of a GEMM (for consumers that are not GEMM A operands)."""
-        x_full, kw = self.gather_begin(x_local)
-        if kw:
-            self.finish_gather(x_full, kw)
-        return x_full
-
     def finish_gather(self, x_full: torch.Tensor, kw: dict) -> None:
         """Complete a gather that no GEMM consumed (``kw`` from ``gather_begin``)."""
         if kw:

@@ -169,6 +169,16 @@ def test_small_shard_helpers():
     K.scatter_add_shards(src, gtable, n, R, 0.5)
     K.scatter_add_shards(src, gtable, n, R, 0.5)
     assert torch.allclose(torch.cat(grads), src, rtol=1e-6)
+    # raw copy (every unroll variant, a ragged tail) and the one-to-many push
+    big = torch.randn(1_000_003 * 8, device=dev).to(torch.bfloat16)            # 16,000,048 bytes: a multiple of 16
+    for unroll in (4, 8, 16):
+        out = torch.zeros_like(big)
+        K.copy_bytes(out.data_ptr(), big.data_ptr(), big.numel() * 2, dev, blocks=37, unroll=unroll)
+        assert torch.equal(out, big)
+    dsts = [torch.zeros_like(big) for _ in range(3)]
+    ptable = K.pointer_table([d.data_ptr() for d in dsts], dev)
+    K.push_copy(ptable, big, big.numel() * 2, 3, skip=1)
+    assert torch.equal(dsts[0], big) and torch.equal(dsts[2], big) and not dsts[1].any()
     _check()
 
 
