@@ -271,3 +271,57 @@ def test_native_chunk_io_checksums(tmp_path, monkeypatch):
     zarr3.write_metadata(s, (), (), torch.bfloat16)
     zarr3.write_chunk(s, (), torch.tensor(1.5, dtype=torch.bfloat16))
     assert zarr3.read_full(s).item() == 1.5
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# Failures injected on the host, among CPU (gloo) ranks
+# ----------------------------------------------------------------------------------------------------------------------
+def _two_rank_fit(tmp, mode):
+    import time
+
+    from olmax_b200.launch.train_transformer import SyntheticDataLoader
+    from olmax_b200.parallel import MeshResource, dist_utils
+
+    rank = dist_utils.get_rank()
+
+    @dataclass
+    class Saboteur(Callback):
+        def post_step(self):
+            if rank == 1 and self.step == 2:
+                if mode == "cancel":
+                    self.trainer.cancel_run("rank 1 wants out")
+                elif mode == "die":
+                    os._exit(17)          # the process disappears between two steps, nothing in flight
+
+    model = _tiny_model(MeshResource.FSDP(2), seed=1)
+    loader = SyntheticDataLoader(0, kind="uniform", vocab_size=1024, sequence_length=32, global_microbatch_instances=2,
+                                 num_microbatches=1, dp_rank=rank, dp_size=2)
+    trainer = _trainer(Path(tmp) / f"rank{rank}", 40, callbacks=OrderedDict(s=Saboteur()), cancel_check_interval=1)
+    t0 = time.monotonic()
+    try:
+        trainer.fit(model, loader)
+        outcome = ("finished", trainer.step, trainer.is_canceled)
+    except BaseException as e:  # noqa: BLE001
+        outcome = ("raised", type(e).__name__, round(time.monotonic() - t0, 1))
+        (Path(tmp) / f"outcome{rank}.txt").write_text(repr(outcome))
+        if mode == "die":
+            os._exit(0)   # the process group is broken: do not try to barrier on the way out
+        raise
+    return outcome
+
+
+def test_cancellation_requested_on_one_rank_stops_every_rank(tmp_path):
+    r0, r1 = run_distributed_test(_two_rank_fit, world_size=2, func_args=(str(tmp_path), "cancel"))
+    assert r0[0] == r1[0] == "finished"
+    assert r0[1] == r1[1] and 2 <= r0[1] <= 4          # both stopped at the same step, right after the request
+    assert r0[2] and r1[2]
+
+
+def test_surviving_rank_notices_a_dead_peer(tmp_path):
+    """Rank 1 exits between two steps.  Rank 0's next collective fails (gloo reports the closed connection), the
+    trainer runs its error path and re-raises instead of waiting forever."""
+    with pytest.raises(Exception):
+        run_distributed_test(_two_rank_fit, world_size=2, func_args=(str(tmp_path), "die"), timeout=90)
+    outcome = eval((tmp_path / "outcome0.txt").read_text())   # noqa: S307  (written by this test)
+    assert outcome[0] == "raised" and outcome[2] < 60, outcome
+    assert not (tmp_path / "outcome1.txt").exists()
