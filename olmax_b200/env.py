@@ -29,17 +29,19 @@ class RuntimeConfig:
 
     comm_backend: str = "auto"
     """``nccl``: collectives through NCCL; ``fused``: peer-memory kernels fused with the GEMMs; ``auto``: fused when
-    symmetric memory is available on every rank of the shard group, else nccl."""
-    prefetch_layers: int = 1
-    """How many FSDP units ahead the parameter all-gather runs (NCCL path)."""
+    symmetric memory is available on every rank of the shard group, else nccl.  Read by the parameter store
+    (``OLMAX_B200_COMM_BACKEND``) unless a model is built with an explicit ``comm_backend``."""
     reshard_after_forward: bool = True
-    """Free gathered weights after the forward use and gather again for backward."""
-    peer_wait_timeout_ms: int = 10000
-    """Upper bound of any device-side wait on another GPU; exceeded waits raise instead of hanging."""
-    ce_chunk_rows: int = 2048
-    """Rows of logits materialised at a time by the fused linear + cross-entropy."""
-    nvtx: bool = False
-    """Emit NVTX ranges named like the reference's profiler scopes."""
+    """Free gathered weights after the forward use and gather again for backward (the entrypoint passes it to
+    ``TransformerConfig.build``)."""
+    peer_barrier: str = "nccl"
+    """How the peer-memory backend separates its phases: ``nccl`` (a one-element all-reduce) or ``flags`` (the bounded
+    flag-word barrier kernel); ``OLMAX_B200_BARRIER``."""
+    peer_wait_timeout_ms: int = 600_000
+    """Upper bound of the flag barrier's wait for another GPU (``OLMAX_B200_BARRIER_TIMEOUT_S``); a wait that runs out
+    raises on the host instead of hanging the GPU.  The waits inside the GEMMs have a fixed iteration limit."""
+    nvtx: bool = True
+    """Emit NVTX ranges named like the reference's profiler scopes around the trainer's phases (``OLMAX_B200_NVTX``)."""
 
     @classmethod
     def recommended(cls, gpu_architecture: Optional[GPUArchitecture] = None, **overrides) -> "RuntimeConfig":
@@ -48,7 +50,9 @@ class RuntimeConfig:
 
     def apply(self) -> None:
         set_env_var("OLMAX_B200_COMM_BACKEND", self.comm_backend, override=True)
-        set_env_var("OLMAX_B200_PEER_WAIT_MS", str(self.peer_wait_timeout_ms), override=True)
+        set_env_var("OLMAX_B200_BARRIER", self.peer_barrier, override=True)
+        set_env_var("OLMAX_B200_BARRIER_TIMEOUT_S", str(self.peer_wait_timeout_ms / 1000.0), override=True)
+        set_env_var("OLMAX_B200_NVTX", "1" if self.nvtx else "0", override=True)
 
 
 @dataclass
@@ -199,7 +203,7 @@ class JAXConfig:
 
     def apply(self) -> None:
         if self.disable_jit:
-            set_env_var("OLMAX_B200_NO_GRAPHS", "1", override=True)
+            log.info("jax.disable_jit has no counterpart here (kernels are launched eagerly): ignored")
 
 
 @dataclass

@@ -128,7 +128,9 @@ def train(config: IntegrationTestConfig, callbacks: Optional[Dict[str, Any]] = N
     global_tokens = instances_per_dp_rank * dp * seq * config.num_microbatches
     dist_utils.barrier("pre-model-init")
     model = config.model.build(seed=fold_in(config.seed, 1), mesh=mesh, param_dtype=config.param_dtype,
-                               compute_dtype=config.compute_dtype if mesh.device.type == "cuda" else config.param_dtype)
+                               compute_dtype=config.compute_dtype if mesh.device.type == "cuda" else config.param_dtype,
+                               reshard_after_forward=config.env.runtime.reshard_after_forward,
+                               comm_backend=config.env.runtime.comm_backend)
     n = model.num_params()
     log.info("Model has %s parameters (%s per device)", format_scalar(n), format_scalar(model.store.numel_local))
     cache = model.get_buffer_cache(seq)

@@ -18,6 +18,7 @@ import fnmatch
 import gc
 import logging
 import math
+import os
 import re
 import signal
 import time
@@ -55,7 +56,8 @@ class TrainMetrics:
 
 
 def _nvtx(name: str):
-    if torch.cuda.is_available():
+    """NVTX range around a trainer phase (names as in the reference's profiler scopes); ``OLMAX_B200_NVTX=0`` disables."""
+    if torch.cuda.is_available() and os.environ.get("OLMAX_B200_NVTX", "1") == "1":
         return torch.cuda.nvtx.range(name)
     import contextlib
 

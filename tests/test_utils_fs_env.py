@@ -172,3 +172,15 @@ def test_tree_compat_helpers():
     assert uncommit_single_device_arrays(tree) is tree and with_optional_sharding_contraint(tree, None, None) is tree
     g = lambda t: t + 1  # noqa: E731
     assert shard_map(g, None, in_specs=(), out_specs=()) is g
+
+
+def test_runtime_config_maps_to_the_environment(monkeypatch):
+    from olmax_b200.env import RuntimeConfig
+
+    for k in ("OLMAX_B200_COMM_BACKEND", "OLMAX_B200_BARRIER", "OLMAX_B200_BARRIER_TIMEOUT_S", "OLMAX_B200_NVTX"):
+        monkeypatch.delenv(k, raising=False)
+    RuntimeConfig(comm_backend="nccl", peer_barrier="flags", peer_wait_timeout_ms=2500, nvtx=False).apply()
+    assert os.environ["OLMAX_B200_COMM_BACKEND"] == "nccl" and os.environ["OLMAX_B200_BARRIER"] == "flags"
+    assert float(os.environ["OLMAX_B200_BARRIER_TIMEOUT_S"]) == 2.5 and os.environ["OLMAX_B200_NVTX"] == "0"
+    for k in ("OLMAX_B200_COMM_BACKEND", "OLMAX_B200_BARRIER", "OLMAX_B200_BARRIER_TIMEOUT_S", "OLMAX_B200_NVTX"):
+        monkeypatch.delenv(k, raising=False)
