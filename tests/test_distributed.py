@@ -10,7 +10,8 @@ import torch
 from olmax_b200.testing import run_distributed_test
 
 
-def _model(mesh_resource, seed=0, layer="default", tie=False, kv=None, cp_strategy=None, window=None, softcap=None):
+def _model(mesh_resource, seed=0, layer="default", tie=False, kv=None, cp_strategy=None, window=None, softcap=None,
+           ac=None):
     from olmax_b200.models import (DefaultTransformerConfig, DefaultTransformerLayerConfig, GemmaTransformerLayerConfig,
                                    ReorderedNormTransformerLayerConfig)
     from olmax_b200.nn import MultiheadSelfAttentionConfig, RMSNormConfig
@@ -21,8 +22,15 @@ def _model(mesh_resource, seed=0, layer="default", tie=False, kv=None, cp_strate
                                         qk_norm=RMSNormConfig() if layer != "default" else None, use_head_qk_norm=True,
                                         cp_strategy=cp_strategy, window_size=window, logit_softcap=softcap)
     cfg = DefaultTransformerConfig(vocab_size=64, d_model=64, hidden_size=96, num_layers=2, layer=layer_cls(attention=attn),
-                                   tie_embeddings=tie, scale_embeddings=tie, ce_chunk_rows=16)
+                                   tie_embeddings=tie, scale_embeddings=tie, ce_chunk_rows=16, layer_ac_policy=_policy(ac))
     return cfg.build(seed=seed, mesh_resource=mesh_resource)
+
+
+def _policy(ac):
+    from olmax_b200.activation_checkpointing import NothingSaveable, SaveAnythingExceptTheseNames
+
+    return {None: None, "full": NothingSaveable(), "mlp": SaveAnythingExceptTheseNames(names=["layers.*.mlp"]),
+            "attention": SaveAnythingExceptTheseNames(names=["layers.*.attention"])}[ac]
 
 
 def _global_batch(ignore_last=True):
@@ -166,6 +174,42 @@ def test_dual_chunk_swap_reordering():
     assert len(set(work)) == 1
     with pytest.raises(ValueError):
         reorder_causal_load_balancing(torch.zeros(1, 6), 2, seq_dim=1)
+
+
+def _recompute_worker(mesh_kind, ac, cp_strategy):
+    import torch.distributed as dist
+
+    from olmax_b200.parallel import MeshResource, dist_utils
+    from olmax_b200.parallel.context import shard_sequence_for_cp
+
+    world = dist_utils.get_world_size()
+    res = MeshResource.FSDP_with_TP(2, world) if mesh_kind == "tp" else MeshResource.FSDP_with_CP(world, 2)
+    model = _model(res, layer="gemma", kv=2, ac=ac, cp_strategy=cp_strategy)
+    mesh = model.mesh
+    ids, labels = _global_batch(ignore_last=False)
+    if mesh.cp.size > 1:
+        ids, labels = (shard_sequence_for_cp(t, mesh.cp.size, mesh.cp.rank) for t in (ids, labels))
+    model.store.set_grad_scale(1.0 / world)
+    loss, _ = model(ids, labels)
+    loss.backward()
+    model.store.finish_backward()
+    model.store.reduce_replicated_grads()
+    t = loss.detach().clone()
+    dist.all_reduce(t, group=dist_utils.control_group())
+    return (t / world).item(), {n: model.store.full_gradient(n) for n, _ in model.store.named_parameters()}
+
+
+@pytest.mark.parametrize("mesh_kind,ac,cp_strategy", [("tp", "full", None), ("tp", "mlp", None), ("cp", "attention", "ring"),
+                                                      ("cp", "full", "all_gather")])
+def test_recomputation_repeats_the_collectives_consistently(mesh_kind, ac, cp_strategy):
+    """Recomputing a block in backward re-runs its collectives (sequence-parallel gathers, the K/V ring) on every rank
+    in the same order: loss and gradients equal the run without recomputation."""
+    base = run_distributed_test(_recompute_worker, world_size=2, func_args=(mesh_kind, None, cp_strategy))
+    remat = run_distributed_test(_recompute_worker, world_size=2, func_args=(mesh_kind, ac, cp_strategy))
+    for (l0, g0), (l1, g1) in zip(base, remat):
+        assert l1 == pytest.approx(l0, rel=1e-6)
+        for n in g0:
+            assert torch.allclose(g1[n], g0[n], rtol=1e-5, atol=1e-7), n
 
 
 def _collectives_worker():
