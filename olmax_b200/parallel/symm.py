@@ -1,6 +1,10 @@
 """
 Peer-memory ("fused") communication backend.
 
+Replaces the collectives XLA inserts for the reference's shardings (all-gather of dim-0 sharded parameters, reduce-
+scatter of their gradients: ``olmax/distributed/parallel.py:97-144,309-334``; explicit forms ``:409-436``) and fixes the
+known issue that HSDP with gradient accumulation all-reduces after every micro-batch (``README.md:30`` of the reference).
+
 The bf16 compute copy of the parameters and the fp32 gradient accumulator are allocated in symmetric memory
 (``torch.distributed._symmetric_memory``: every rank of the job maps every other rank's buffer over NVLink), which
 lets our kernels fuse the collectives into the compute instead of calling NCCL:
@@ -9,8 +13,9 @@ lets our kernels fuse the collectives into the compute instead of calling NCCL:
   warps, a slice of the NEXT FSDP unit's remote shards (so the transfer of layer i+1 runs under the math of layer i);
   whatever a weight still misses when its own GEMM starts is fetched by that GEMM itself, whose tiles then wait on
   per-block arrival counters (``csrc/gemm.cu``).  The embedding gather reads rows straight from the owner GPU.
-* **GEMM -> reduce-scatter**: the weight-gradient GEMM's epilogue adds each row block into the owner GPU's fp32
-  accumulator with ``red.global.add`` (scaled by 1 / (ranks x micro-batches)), so there is no reduce-scatter at all.
+* **GEMM -> reduce-scatter**: the weight-gradient GEMM's epilogue stores each row block (line-coalesced plain stores)
+  into this rank's slot of the owner GPU's staging buffer; after one barrier per FSDP unit the owner folds its slots
+  into its fp32 accumulator (scaled by 1 / (ranks x micro-batches)).  No atomics, deterministic summation order.
 * **HSDP / DDP all-reduce**: once per optimizer step a two-shot kernel sums the fp32 accumulator over the replicas
   (plain peer loads / stores, or ``multimem.ld_reduce`` + ``multimem.st`` through NVSwitch when the group is the whole
   job and a multicast mapping exists).
