@@ -7,8 +7,9 @@
 // the B operand / the output a third "shard" coordinate:
 //   * forward with gathered weights:  B rows (output columns) come from R buffers `b_shard_stride` apart,
 //   * dgrad:                          the contraction runs over R weight shards,
-//   * wgrad with reduce-scatter:      output row block s is added into the buffer `c_shards[s]`, which may live in
-//                                     another GPU's memory (plain red.global over NVLink; never TMA).
+//   * wgrad with reduce-scatter:      output row block s goes to the buffer `c_shards[s]`, which may live in another
+//                                     GPU's memory (staged in shared memory, then line-coalesced plain stores or
+//                                     red.global over NVLink; never TMA).
 // Tensor parallelism with sequence parallelism uses the same two mechanisms on the ACTIVATION side: the all-gather of
 // the A operand's row shards is fused in (`ag_on_a`: the copy warps pull the peers' rows while the tensor cores work
 // on the local rows), and the reduce-scatter of a row-parallel output is fused into the epilogue (row block s of
