@@ -15,6 +15,7 @@ background: tensors are first copied to host memory, then a thread writes the fi
 
 from __future__ import annotations
 
+import concurrent.futures
 import json
 import logging
 import os
@@ -255,6 +256,7 @@ def restore_sharded(directory: PathOrStr, store: ParamStore, buffers: Dict[str, 
     d = Path(fs.normalize_path(directory))
     meta = get_metadata(d)
     tp, sh = store.mesh.tp, store.mesh.shard
+    jobs = []
     for prefix, flat in buffers.items():
         for m in store.metas:
             key = f"{prefix}.{m.name}" if prefix else m.name
@@ -266,7 +268,17 @@ def restore_sharded(directory: PathOrStr, store: ParamStore, buffers: Dict[str, 
             if m.tp_dim is not None and tp.size > 1:
                 start[m.tp_dim] = tp.rank * m.tp_shape[m.tp_dim]
             start[0] += sh.rank * m.local_shape[0]
-            region = zarr3.read_region(d / key, start, m.local_shape)
+            jobs.append((key, start, m, flat))
+
+    def read(job):
+        key, start, m, _flat = job
+        return zarr3.read_region(d / key, start, m.local_shape)
+
+    # the chunk reads (native code: file I/O + checksum, outside the interpreter lock) run on a few threads; the copies
+    # into the flat buffers stay on this thread, in order
+    with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as pool:
+        for job, region in zip(jobs, pool.map(read, jobs)):
+            _key, _start, m, flat = job
             dst = flat[m.offset : m.offset + m.numel_local].view(m.local_shape)
             dst.copy_(region.to(dst.dtype))
     return meta.get("scalars", {})
