@@ -226,7 +226,7 @@ def _train_worker(backend, mesh_kind="fsdp", barrier="nccl"):
 
 
 @pytest.mark.parametrize("mesh_kind,world,barrier", [("fsdp", 2, "nccl"), ("fsdp", 2, "flags"), ("ddp", 2, "nccl"),
-                                                      ("hsdp", 4, "flags")])
+                                                      ("hsdp", 4, "nccl")])
 def test_peer_memory_backend_matches_nccl(mesh_kind, world, barrier):
     if not torch.cuda.is_available() or torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
