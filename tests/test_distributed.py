@@ -258,3 +258,38 @@ def test_reduce_divide_factor_and_mesh_math():
     assert cp.data_parallel_size == 4 and cp.fsdp_size == 8 and cp.cp_size == 2
     with pytest.raises(Exception):
         MeshResource(axes=((2, "a"),), batch_sharding_axis="b")
+
+
+def _hsdp_accumulation_worker(num_microbatches):
+    from olmax_b200.optim import AdamWConfig, ConstantSchedule
+    from olmax_b200.parallel import MeshResource, dist_utils
+
+    world = dist_utils.get_world_size()
+    model = _model(MeshResource.HSDP(2, world, 2))
+    optim = AdamWConfig(lr=ConstantSchedule(1e-3)).build(model, num_microbatches)
+    ids, labels = _global_batch()
+    dp, r = model.mesh.data_parallel_size, model.mesh.data_parallel_rank
+    per = ids.shape[0] // dp
+    mine_ids, mine_labels = ids[r * per : (r + 1) * per], labels[r * per : (r + 1) * per]
+    per_step = []
+    for _ in range(2):
+        before = dict(model.store.stats)
+        for mb in range(num_microbatches):
+            loss, _ = model(mine_ids.chunk(num_microbatches)[mb], mine_labels.chunk(num_microbatches)[mb])
+            loss.backward()
+            assert optim.accumulate() == (mb == num_microbatches - 1)
+        optim.step()
+        per_step.append({k: model.store.stats[k] - before[k] for k in before})
+    return per_step, model.store.grad.numel(), model.mesh.replicate.size
+
+
+def test_hsdp_all_reduces_once_per_optimizer_step():
+    """The cross-replica all-reduce runs after the LAST micro-batch only (the reference all-reduces after every
+    micro-batch, its README's known issue): its byte count per optimizer step does not depend on the number of
+    micro-batches, while the reduce-scatter inside the shard group runs once per micro-batch."""
+    one = run_distributed_test(_hsdp_accumulation_worker, world_size=4, func_args=(1,))
+    two = run_distributed_test(_hsdp_accumulation_worker, world_size=4, func_args=(2,))
+    for (steps1, numel, rep), (steps2, _, _) in zip(one, two):
+        want = 2 * (rep - 1) * numel * 4 // rep
+        assert all(s["all_reduce_bytes"] == want for s in steps1 + steps2)
+        assert all(s2["reduce_scatter_bytes"] == 2 * s1["reduce_scatter_bytes"] for s1, s2 in zip(steps1, steps2))
