@@ -2,6 +2,18 @@
 // CTAs (one per SM), warp-specialised (TMA producer / MMA issuer / 4 epilogue warps), double-buffered accumulators
 // so that the epilogue of tile i overlaps the main loop of tile i+1.
 //
+// Two tile geometries share one kernel body (template parameter CG):
+//   CG = 2 (default): a CTA PAIR (2-CTA cluster on the two SMs of a TPC) computes a 256 x 256 tile with
+//          tcgen05.mma.cta_group::2.  Each CTA TMA-loads its own 128 rows of A and its own 128 columns of B per
+//          k-block (32 KiB instead of 48 KiB per 128 x 256 x 64 of work), six stages deep; both CTAs' loads complete on
+//          the leader's mbarrier, the leader's MMA thread issues for the pair and frees the stages / publishes the
+//          accumulator in both CTAs with one tcgen05.commit per CTA (no multicast of any kind).  Each CTA's epilogue
+//          drains its own 128 rows from its own TMEM.
+//   CG = 1: one CTA computes a 128 x 256 tile (cta_group::1), four stages; used for problems with too few tiles to
+//          fill the pairs, and selectable for comparison.
+// Accumulating fp32 epilogues (weight gradients) get a split-K tail: the tiles of the last, partly filled wave are
+// cut into k slices so that every SM stays busy; the slices meet in the output through the reduce-add epilogue.
+//
 // One kernel covers the three layouts a Linear layer needs (forward Y = X W^T, dgrad dX = dY W, wgrad dW = dY^T X)
 // by letting either operand be K-major or MN-major in shared memory, and covers dim-0-sharded weights by giving
 // the B operand / the output a third "shard" coordinate:
@@ -21,25 +33,34 @@
 // `olmax/nn/mlp.py:69-73` (gated MLP).
 #include "gemm.h"
 
+#include <stdlib.h>
+
 #include "host_common.h"
 #include "sm100.cuh"
 
 namespace ob {
 
-constexpr int BM = 128;
-constexpr int BN = 256;
+constexpr int BM = 128;   // output rows per CTA (the pair tile has CG * BM rows)
+constexpr int BN = 256;   // accumulator columns (MMA N)
 constexpr int BK = 64;
-constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
-constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int MN_BLOCK_BYTES = 64 * BK * 2;  // one 64(MN) x 64(K) MN-major block: 8 KiB
 constexpr int TMEM_COLS = 512;
 constexpr int GEMM_THREADS = 256;  // warp 0 TMA, 1 MMA, 2-5 epilogue, 6-7 peer-copy (fused all-gather)
 constexpr int COPY_WARPS = 2;
 constexpr int AG_BLOCK_ROWS = 256;  // granularity of the all-gather ready flags
 constexpr int EPI_STAGE_BYTES = 128 * 128;  // one 128-row x 128-byte output chunk
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * EPI_STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int MAX_STAGES = 6;
+
+// Per-CTA geometry of the two variants: B columns held per CTA, stage size, pipeline depth, shared-memory size.
+template <int CG>
+struct Geo {
+  static constexpr int BNL = BN / CG;                    // B columns (rows of the K-major weight) per CTA
+  static constexpr int B_STAGE_BYTES = BNL * BK * 2;     // 32 KiB / 16 KiB
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int STAGES = CG == 1 ? 4 : 6;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * EPI_STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+};
 
 struct KernelParams {
   int M, N, Kc;
@@ -56,6 +77,7 @@ struct KernelParams {
   long long c_shard_stride;
   long long ldc;
   int* status;
+  int split, full_items, total_items;   // split-K tail: work items [full_items, total_items) are k slices of tiles
   int group_m;                 // tile rasterisation group (M tiles)
   int m_rot;                   // rotation of the M tile order (tiles), see decode_tile
   int a_single, b_single;      // MN-major operand fetched with one 4-D TMA box per stage instead of 64-wide boxes
@@ -150,24 +172,44 @@ __device__ __forceinline__ float gelu_tanh(float x) {
 }
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
 
-template <bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-    gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                     const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmC,
-                     const KernelParams p) {
+// Work item w of a launch: a whole tile, or (in the split-K tail) one k slice of a tile.
+__device__ __forceinline__ void decode_work(const KernelParams& p, int w, int k_iters, int& tile, int& k_begin, int& k_count) {
+  if (w < p.full_items) {
+    tile = w;
+    k_begin = 0;
+    k_count = k_iters;
+  } else {
+    const int idx = w - p.full_items;
+    tile = p.full_items + idx / p.split;
+    const int sl = idx % p.split;
+    k_begin = (int)((long long)k_iters * sl / p.split);
+    k_count = (int)((long long)k_iters * (sl + 1) / p.split) - k_begin;
+  }
+}
+
+template <bool A_MN, bool B_MN, int CG>
+__device__ __forceinline__ void gemm_body(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmB2,
+                                          const CUtensorMap& tmC, const KernelParams& p) {
+  using G = Geo<CG>;
+  constexpr int STAGES = G::STAGES;
+  constexpr int STAGE_BYTES = G::STAGE_BYTES;
+  constexpr int BNL = G::BNL;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_smem = smem + STAGES * STAGE_BYTES;   // 2 x 16 KiB output staging, 1024-byte aligned
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES + 2 * EPI_STAGE_BYTES);
-  uint64_t* full_bar = bars;                       // [STAGES]
-  uint64_t* empty_bar = bars + STAGES;             // [STAGES]
-  uint64_t* tfull_bar = bars + 2 * STAGES;         // [2]
-  uint64_t* tempty_bar = bars + 2 * STAGES + 2;    // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint64_t* full_bar = bars;                           // [STAGES]  (CG = 2: only the leader's are used)
+  uint64_t* empty_bar = bars + MAX_STAGES;             // [STAGES]
+  uint64_t* tfull_bar = bars + 2 * MAX_STAGES;         // [2]
+  uint64_t* tempty_bar = bars + 2 * MAX_STAGES + 2;    // [2]       (CG = 2: only the leader's are used)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * MAX_STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int cta_rank = CG == 2 ? (int)cluster_ctarank() : 0;   // 0 = leader
+  const int worker = (int)blockIdx.x / CG;                     // index of this CTA (pair) among the persistent workers
+  const int n_workers = (int)gridDim.x / CG;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -176,24 +218,31 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull_bar[b], 1);
-      mbar_init(&tempty_bar[b], 128);
+      mbar_init(&tempty_bar[b], 4 * CG);   // lane 0 of every epilogue warp of the CTA (pair)
     }
     *abort_flag = 0;
     mbar_fence_init();
     fence_proxy_async();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, TMEM_COLS);
-    tmem_relinquish();
+    if (CG == 2) {
+      tmem_alloc_pair(tmem_slot, TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if (CG == 2) cluster_sync_all(); else __syncthreads();   // barriers of BOTH CTAs exist before any remote signal
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // shared::cluster addresses of the leader's and the peer's barrier arrays (CG = 2)
+  const uint32_t bars_leader = CG == 2 ? mapa_shared(smem_u32(bars), 0) : smem_u32(bars);
+  const uint32_t bars_peer = CG == 2 ? mapa_shared(smem_u32(bars), 1) : smem_u32(bars);
 
-  const int m_tiles = p.m_shards * p.m_tiles_per_shard;
+  const int m_tiles = p.m_shards * p.m_tiles_per_shard;     // tiles of CG * BM rows
   const int n_tiles = p.n_shards * p.n_tiles_per_shard;
-  const int total_tiles = m_tiles * n_tiles;
   const int k_iters = p.k_shards * p.k_iters_per_shard;
   const bool glu = (p.epi == EPI_SWIGLU || p.epi == EPI_GEGLU);
   // With a fused all-gather the tile order is rotated so that work on the local shard comes first and the other
@@ -201,126 +250,193 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   const int n_rot = (p.ag_shards > 0 && !p.ag_on_a && !B_MN) ? p.ag_rank * p.n_tiles_per_shard : 0;
   const int k_rot = (p.ag_shards > 0 && !p.ag_on_a && B_MN) ? p.ag_rank * p.k_iters_per_shard : 0;
 
+  // The producer and MMA warps run their loops with all 32 lanes (loop state stays warp-uniform); the one elected
+  // lane issues the TMA / tcgen05 instructions.  A wait that gives up marks the warp `dead`: the loops then run to
+  // their end without issuing anything, and the other roles give up at their own next wait.
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
-    if (lane == 0) {
+    const bool leader = elect_one();
+    if (leader) {
       tma_prefetch_desc(&tmA);
       tma_prefetch_desc(&tmB);
       if (glu) tma_prefetch_desc(&tmB2);
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      // Fused all-gather: the copy warps of every CTA fetch the shards in the order rank+1, rank+2, ... and the blocks
-      // of a shard in order, so arrival is monotone in  idx = ((shard - rank) mod S) * blocks + block.  The flag of a
-      // block is polled (an L2 round trip with acquire semantics) only while idx is beyond the newest block seen
-      // ready: once per block and CTA over the whole kernel instead of once per k-iteration.
-      int ag_ready_idx = p.ag_blocks - 1;   // the local shard is always present
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        int mt, nt;
-        decode_tile(tile, m_tiles, n_tiles, p.group_m, n_rot, p.m_rot, mt, nt);
-        const int m0 = (mt / p.m_tiles_per_shard) * p.M_s + (mt % p.m_tiles_per_shard) * BM;
-        const int n_shard = nt / p.n_tiles_per_shard;
-        const int n_local0 = (nt % p.n_tiles_per_shard) * p.bn_out;
-        for (int kit0 = 0; kit0 < k_iters; ++kit0) {
-          const int kit = (kit0 + k_rot) % k_iters;
-          const int k_shard = kit / p.k_iters_per_shard;
-          const int k_local = (kit % p.k_iters_per_shard) * BK;
-          const int k_glob = k_shard * p.Kc_s + k_local;
-          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 100);
-          if (!ok) break;
-          if (p.ag_shards > 0) {
-            int ag_s, ag_b;
-            if (p.ag_on_a) {
-              ag_s = mt / p.m_tiles_per_shard;
-              ag_b = ((mt % p.m_tiles_per_shard) * BM) / AG_BLOCK_ROWS;
-            } else if (B_MN) {
-              ag_s = k_shard;
-              ag_b = k_local / AG_BLOCK_ROWS;
-            } else {
-              ag_s = n_shard;
-              ag_b = n_local0 / AG_BLOCK_ROWS;
-            }
-            const int ag_idx = ((ag_s - p.ag_rank + p.ag_shards) % p.ag_shards) * p.ag_blocks + ag_b;
-            if (ag_idx > ag_ready_idx) {
-              ok = ag_wait(p, ag_s, ag_b, abort_flag);
-              if (!ok) break;
-              ag_ready_idx = ag_idx;
-            }
-          }
-          uint8_t* sa = smem + stage * STAGE_BYTES;
-          uint8_t* sb = sa + A_STAGE_BYTES;
-          mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
-          if (A_MN) {
-            if (p.a_single) {
-              // one 4-D box: (64 elements, 64 k-rows, 2 column blocks): lands as [block][k][128 B]
-              tma_load_4d(sa, &tmA, &full_bar[stage], 0, k_glob, m0 >> 6, 0);
-            } else {
-              tma_load_3d(sa, &tmA, &full_bar[stage], m0, k_glob, 0);
-              tma_load_3d(sa + MN_BLOCK_BYTES, &tmA, &full_bar[stage], m0 + 64, k_glob, 0);
-            }
+    }
+    int stage = 0;
+    uint32_t phase = 0;
+    bool dead = false;
+    // Fused all-gather: the copy warps of every CTA fetch the shards in the order rank+1, rank+2, ... and the blocks
+    // of a shard in order, so arrival is monotone in  idx = ((shard - rank) mod S) * blocks + block.  The flag of a
+    // block is polled (an L2 round trip with acquire semantics) only while idx is beyond the newest block seen
+    // ready: once per block and CTA over the whole kernel instead of once per k-iteration.
+    int ag_ready_idx = p.ag_blocks - 1;   // the local shard is always present
+    for (int w = worker; w < p.total_items; w += n_workers) {
+      int tile, k_begin, k_count, mt, nt;
+      decode_work(p, w, k_iters, tile, k_begin, k_count);
+      decode_tile(tile, m_tiles, n_tiles, p.group_m, n_rot, p.m_rot, mt, nt);
+      const int m_local0 = (mt % p.m_tiles_per_shard) * (BM * CG) + cta_rank * BM;   // this CTA's rows in the shard
+      const int m0 = (mt / p.m_tiles_per_shard) * p.M_s + m_local0;
+      const int n_shard = nt / p.n_tiles_per_shard;
+      const int n_local0 = (nt % p.n_tiles_per_shard) * p.bn_out;
+      // k position, advanced without divisions inside the loop
+      const int kit_first = (k_begin + k_rot) % k_iters;
+      int k_shard = kit_first / p.k_iters_per_shard;
+      int k_local = (kit_first % p.k_iters_per_shard) * BK;
+      const int k_local_end = p.k_iters_per_shard * BK;
+      for (int i = 0; i < k_count; ++i) {
+        const int k_glob = k_shard * p.Kc_s + k_local;
+        if (!dead) dead = !mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, 100);
+        if (p.ag_shards > 0 && !dead) {
+          int ag_s, ag_b;
+          if (p.ag_on_a) {
+            ag_s = mt / p.m_tiles_per_shard;
+            ag_b = min(m_local0, p.M_s - 1) / AG_BLOCK_ROWS;
+          } else if (B_MN) {
+            ag_s = k_shard;
+            ag_b = k_local / AG_BLOCK_ROWS;
           } else {
-            tma_load_3d(sa, &tmA, &full_bar[stage], k_glob, m0, 0);
+            ag_s = n_shard;
+            ag_b = n_local0 / AG_BLOCK_ROWS;
           }
-          if (B_MN) {
-            // dims (N, Kc_s, k_shards): four 64-wide blocks along N
-            const int n0 = n_local0;  // MN-major B is never N-sharded
-            if (p.b_single) {
-              tma_load_4d(sb, &tmB, &full_bar[stage], 0, k_local, n0 >> 6, k_shard);
+          const int ag_idx = ((ag_s - p.ag_rank + p.ag_shards) % p.ag_shards) * p.ag_blocks + ag_b;
+          if (ag_idx > ag_ready_idx) {
+            dead = !ag_wait(p, ag_s, ag_b, abort_flag);
+            ag_ready_idx = ag_idx;
+          }
+        }
+        uint8_t* sa = smem + stage * STAGE_BYTES;
+        uint8_t* sb = sa + A_STAGE_BYTES;
+        if (leader && !dead) {
+          if (CG == 1) {
+            mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+            if (A_MN) {
+              if (p.a_single) {
+                // one 4-D box: (64 elements, 64 k-rows, 2 column blocks): lands as [block][k][128 B]
+                tma_load_4d(sa, &tmA, &full_bar[stage], 0, k_glob, m0 >> 6, 0);
+              } else {
+                tma_load_3d(sa, &tmA, &full_bar[stage], m0, k_glob, 0);
+                tma_load_3d(sa + MN_BLOCK_BYTES, &tmA, &full_bar[stage], m0 + 64, k_glob, 0);
+              }
             } else {
+              tma_load_3d(sa, &tmA, &full_bar[stage], k_glob, m0, 0);
+            }
+            if (B_MN) {
+              // dims (N, Kc_s, k_shards): four 64-wide blocks along N
+              const int n0 = n_local0;  // MN-major B is never N-sharded
+              if (p.b_single) {
+                tma_load_4d(sb, &tmB, &full_bar[stage], 0, k_local, n0 >> 6, k_shard);
+              } else {
 #pragma unroll
-              for (int j = 0; j < 4; ++j)
-                tma_load_3d(sb + j * MN_BLOCK_BYTES, &tmB, &full_bar[stage], n0 + j * 64, k_local, k_shard);
+                for (int j = 0; j < 4; ++j)
+                  tma_load_3d(sb + j * MN_BLOCK_BYTES, &tmB, &full_bar[stage], n0 + j * 64, k_local, k_shard);
+              }
+            } else if (glu) {
+              tma_load_3d(sb, &tmB, &full_bar[stage], k_glob, n_local0, n_shard);
+              tma_load_3d(sb + G::B_STAGE_BYTES / 2, &tmB2, &full_bar[stage], k_glob, n_local0, n_shard);
+            } else {
+              tma_load_3d(sb, &tmB, &full_bar[stage], k_glob, n_local0, n_shard);
             }
-          } else if (glu) {
-            tma_load_3d(sb, &tmB, &full_bar[stage], k_glob, n_local0, n_shard);
-            tma_load_3d(sb + B_STAGE_BYTES / 2, &tmB2, &full_bar[stage], k_glob, n_local0, n_shard);
           } else {
-            tma_load_3d(sb, &tmB, &full_bar[stage], k_glob, n_local0, n_shard);
+            // CTA pair: both CTAs' copies complete on the leader's barrier, which expects the bytes of both
+            const uint32_t fb = bars_leader + (uint32_t)stage * 8u;
+            if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
+            if (A_MN) {
+              if (p.a_single) {
+                tma_load_4d_pair(sa, &tmA, fb, 0, k_glob, m0 >> 6, 0);
+              } else {
+                tma_load_3d_pair(sa, &tmA, fb, m0, k_glob, 0);
+                tma_load_3d_pair(sa + MN_BLOCK_BYTES, &tmA, fb, m0 + 64, k_glob, 0);
+              }
+            } else {
+              tma_load_3d_pair(sa, &tmA, fb, k_glob, m0, 0);
+            }
+            if (B_MN) {
+              const int n0 = n_local0 + cta_rank * BNL;   // this CTA's half of the tile's columns: two 64-wide blocks
+              if (p.b_single) {
+                tma_load_4d_pair(sb, &tmB, fb, 0, k_local, n0 >> 6, k_shard);
+              } else {
+#pragma unroll
+                for (int j = 0; j < BNL / 64; ++j)
+                  tma_load_3d_pair(sb + j * MN_BLOCK_BYTES, &tmB, fb, n0 + j * 64, k_local, k_shard);
+              }
+            } else if (glu) {
+              // accumulator columns [0,128) = gate (leader's B half), [128,256) = up (peer's B half)
+              tma_load_3d_pair(sb, cta_rank == 0 ? &tmB : &tmB2, fb, k_glob, n_local0, n_shard);
+            } else {
+              tma_load_3d_pair(sb, &tmB, fb, k_glob, n_local0 + cta_rank * BNL, n_shard);
+            }
           }
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
-          }
+        }
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+        k_local += BK;
+        if (k_local == k_local_end) {
+          k_local = 0;
+          if (++k_shard == p.k_shards) k_shard = 0;
         }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+    // ------------------------------- MMA issuer (CG = 2: the leader CTA issues for the pair) ----------------------
+    const bool leader = elect_one();
+    if (cta_rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM * CG, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      bool dead = false;
+      // descriptors of stage 0; the loop only adds to the low word (start address, 16-byte units, never carries out)
+      const uint64_t da0 = A_MN ? make_smem_desc(smem_u32(smem), MN_BLOCK_BYTES, 1024) : make_smem_desc(smem_u32(smem), 0, 1024);
+      const uint64_t db0 = B_MN ? make_smem_desc(smem_u32(smem) + A_STAGE_BYTES, MN_BLOCK_BYTES, 1024)
+                                : make_smem_desc(smem_u32(smem) + A_STAGE_BYTES, 0, 1024);
+      const uint32_t a_lo0 = (uint32_t)da0, a_hi = (uint32_t)(da0 >> 32);
+      const uint32_t b_lo0 = (uint32_t)db0, b_hi = (uint32_t)(db0 >> 32);
+      for (int w = worker; w < p.total_items; w += n_workers, ++it) {
+        int tile, k_begin, k_count;
+        decode_work(p, w, k_iters, tile, k_begin, k_count);
         const int buf = it & 1;
         const uint32_t tphase = (uint32_t)(it >> 1) & 1u;
-        ok = mbar_wait(&tempty_bar[buf], tphase ^ 1u, abort_flag, p.status, 200);
-        if (!ok) break;
+        if (!dead) dead = !mbar_wait(&tempty_bar[buf], tphase ^ 1u, abort_flag, p.status, 200);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-        for (int kit = 0; kit < k_iters; ++kit) {
-          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 201);
-          if (!ok) break;
+        for (int kit = 0; kit < k_count; ++kit) {
+          if (!dead) dead = !mbar_wait(&full_bar[stage], phase, abort_flag, p.status, 201);
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-          const uint32_t sb = sa + A_STAGE_BYTES;
+          if (leader && !dead) {
+            const uint32_t a_lo = a_lo0 + (uint32_t)stage * (uint32_t)(STAGE_BYTES >> 4);
+            const uint32_t b_lo = b_lo0 + (uint32_t)stage * (uint32_t)(STAGE_BYTES >> 4);
 #pragma unroll
-          for (int k4 = 0; k4 < BK / 16; ++k4) {
-            const uint64_t da = A_MN ? make_smem_desc(sa + k4 * 2048, MN_BLOCK_BYTES, 1024)
-                                     : make_smem_desc(sa + k4 * 32, 0, 1024);
-            const uint64_t db = B_MN ? make_smem_desc(sb + k4 * 2048, MN_BLOCK_BYTES, 1024)
-                                     : make_smem_desc(sb + k4 * 32, 0, 1024);
-            umma_ss(d_tmem, da, db, idesc, (kit | k4) != 0 ? 1u : 0u);
+            for (int k4 = 0; k4 < BK / 16; ++k4) {
+              // advancing 16 elements along K: 32 bytes inside the 128-byte swizzle row of a K-major tile, 16 rows of
+              // 128 bytes in an MN-major tile; the start-address field counts 16-byte units
+              const uint32_t al = a_lo + (uint32_t)k4 * (A_MN ? 128u : 2u);
+              const uint32_t bl = b_lo + (uint32_t)k4 * (B_MN ? 128u : 2u);
+              if (CG == 2) umma_ss_pair_lohi(d_tmem, al, a_hi, bl, b_hi, idesc, (kit | k4) != 0 ? 1u : 0u);
+              else umma_ss_lohi(d_tmem, al, a_hi, bl, b_hi, idesc, (kit | k4) != 0 ? 1u : 0u);
+            }
+            // free the stage (in both CTAs) once these MMAs have read it
+            if (CG == 2) {
+              umma_commit_pair(bars_leader + (uint32_t)(MAX_STAGES + stage) * 8u);
+              umma_commit_pair(bars_peer + (uint32_t)(MAX_STAGES + stage) * 8u);
+            } else {
+              umma_commit(&empty_bar[stage]);
+            }
           }
-          umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) umma_commit(&tfull_bar[buf]);
+        if (leader && !dead) {
+          if (CG == 2) {
+            umma_commit_pair(bars_leader + (uint32_t)(2 * MAX_STAGES + buf) * 8u);
+            umma_commit_pair(bars_peer + (uint32_t)(2 * MAX_STAGES + buf) * 8u);
+          } else {
+            umma_commit(&tfull_bar[buf]);
+          }
+        }
       }
     }
     __syncwarp();
@@ -365,16 +481,17 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     const int row_in_tile = q * 32 + lane;
     int it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+    for (int w = worker; w < p.total_items && ok; w += n_workers, ++it) {
       const int buf = it & 1;
       const uint32_t tphase = (uint32_t)(it >> 1) & 1u;
-      int mt, nt;
-        decode_tile(tile, m_tiles, n_tiles, p.group_m, n_rot, p.m_rot, mt, nt);
+      int tile, k_begin, k_count, mt, nt;
+      decode_work(p, w, k_iters, tile, k_begin, k_count);
+      decode_tile(tile, m_tiles, n_tiles, p.group_m, n_rot, p.m_rot, mt, nt);
       const int m_shard = mt / p.m_tiles_per_shard;
-      const int m_local0 = (mt % p.m_tiles_per_shard) * BM;
+      const int m_local0 = (mt % p.m_tiles_per_shard) * (BM * CG) + cta_rank * BM;   // this CTA's 128 rows
       const int n_shard = nt / p.n_tiles_per_shard;
       const int n_local0 = (nt % p.n_tiles_per_shard) * p.bn_out;
-      const int m_valid = min(BM, p.M_s - m_local0);
+      const int m_valid = max(0, min(BM, p.M_s - m_local0));
       const int n_valid = min(p.bn_out, p.N_s - n_local0);
       const int n_glob0 = n_shard * p.N_s + n_local0;
       ok = mbar_wait(&tfull_bar[buf], tphase, abort_flag, p.status, 300);
@@ -456,8 +573,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             fence_proxy_async();
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (store_thread) {
-              if (p.epi == EPI_F32_ACC) tma_reduce_add_3d(&tmC, stage_buf, n_glob0 + c0, out_row, out_z);
-              else tma_store_3d(&tmC, stage_buf, n_glob0 + c0, out_row, out_z);
+              if (m_valid > 0) {   // a pair tile's second half may lie wholly below the shard
+                if (p.epi == EPI_F32_ACC) tma_reduce_add_3d(&tmC, stage_buf, n_glob0 + c0, out_row, out_z);
+                else tma_store_3d(&tmC, stage_buf, n_glob0 + c0, out_row, out_z);
+              }
               tma_store_commit();
             }
           } else {
@@ -626,31 +745,99 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           }
         }
       }
+      // hand the accumulator buffer back to the MMA thread (of the leader): one arrival per epilogue warp
       tc_fence_before_sync();
-      mbar_arrive(&tempty_bar[buf]);
+      __syncwarp();
+      if (lane == 0) {
+        if (CG == 2) mbar_arrive_cluster(bars_leader + (uint32_t)(2 * MAX_STAGES + 2 + buf) * 8u);
+        else mbar_arrive(&tempty_bar[buf]);
+      }
     }
   }
 
-  // teardown: everyone meets here (also after an aborted wait), then the allocating warp frees TMEM
+  // teardown: everyone meets here (also after an aborted wait; with CG = 2 both CTAs, so that neither leaves while
+  // the other may still signal its barriers or read its shared memory), then the allocating warp frees TMEM
   if (threadIdx.x == 64) tma_store_wait<0>();
   tc_fence_before_sync();
-  __syncthreads();
+  if (CG == 2) cluster_sync_all(); else __syncthreads();
   tc_fence_after_sync();
-  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (warp == 1) {
+    if (CG == 2) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
+  }
 }
 
 template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmC,
+                     const KernelParams p) {
+  gemm_body<A_MN, B_MN, 1>(tmA, tmB, tmB2, tmC, p);
+}
+
+// The CTA-pair variant: the grid is a whole number of 2-CTA clusters.
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+    gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                          const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmC,
+                          const KernelParams p) {
+  gemm_body<A_MN, B_MN, 2>(tmA, tmB, tmB2, tmC, p);
+}
+
+constexpr int MAX_DEVICES = 64;
+
+template <bool A_MN, bool B_MN, int CG>
 static int launch(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2, const CUtensorMap& tC,
                   const KernelParams& kp, int grid, cudaStream_t stream) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    OB_CUDA_OK(cudaFuncSetAttribute(gemm_bf16_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    SMEM_BYTES));
-    attr_set = true;
+  // the shared-memory opt-in is a per-device attribute of the function
+  static bool attr_set[MAX_DEVICES] = {};
+  int dev = 0;
+  OB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= MAX_DEVICES) OB_FAIL(-20, "device index %d out of range", dev);
+  if (CG == 2) {
+    if (!attr_set[dev]) {
+      OB_CUDA_OK(cudaFuncSetAttribute(gemm_bf16_pair_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Geo<2>::SMEM_BYTES));
+      attr_set[dev] = true;
+    }
+    gemm_bf16_pair_kernel<A_MN, B_MN><<<grid, GEMM_THREADS, Geo<2>::SMEM_BYTES, stream>>>(tA, tB, tB2, tC, kp);
+  } else {
+    if (!attr_set[dev]) {
+      OB_CUDA_OK(cudaFuncSetAttribute(gemm_bf16_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Geo<1>::SMEM_BYTES));
+      attr_set[dev] = true;
+    }
+    gemm_bf16_kernel<A_MN, B_MN><<<grid, GEMM_THREADS, Geo<1>::SMEM_BYTES, stream>>>(tA, tB, tB2, tC, kp);
   }
-  gemm_bf16_kernel<A_MN, B_MN><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(tA, tB, tB2, tC, kp);
   OB_CUDA_OK(cudaGetLastError());
   return 0;
+}
+
+template <int CG>
+static int launch_layout(bool a_mn, bool b_mn, const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2,
+                         const CUtensorMap& tC, const KernelParams& kp, int grid, cudaStream_t stream) {
+  if (a_mn) return b_mn ? launch<true, true, CG>(tA, tB, tB2, tC, kp, grid, stream)
+                        : launch<true, false, CG>(tA, tB, tB2, tC, kp, grid, stream);
+  return b_mn ? launch<false, true, CG>(tA, tB, tB2, tC, kp, grid, stream)
+              : launch<false, false, CG>(tA, tB, tB2, tC, kp, grid, stream);
+}
+
+// 1: force single-CTA tiles, 2: force CTA pairs, 0: choose per problem (OLMAX_B200_GEMM_CTA_GROUP)
+static int cta_group_override() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("OLMAX_B200_GEMM_CTA_GROUP");
+    v = (e != nullptr && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0;
+  }
+  return v;
+}
+static bool split_k_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("OLMAX_B200_GEMM_SPLIT_K");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
 }
 
 }  // namespace ob
@@ -678,12 +865,25 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
   kp.m_shards = a->M / M_s;
   kp.n_shards = a->N / N_s;
   kp.k_shards = a->Kc / Kc_s;
-  kp.m_tiles_per_shard = (M_s + BM - 1) / BM;
+  const int cap = a->max_ctas > 0 ? a->max_ctas : sm_count();
+  // Tile geometry: CTA pairs (256-row tiles) unless forced, or unless the problem has so few 256-row tiles that
+  // 128-row tiles on single CTAs keep more SMs busy.
+  int CG = cta_group_override();
+  if (CG == 0) {
+    const long long n_t = (long long)kp.n_shards * ((N_s + kp.bn_out - 1) / kp.bn_out);
+    const long long pair_tiles = (long long)kp.m_shards * ((M_s + 2 * BM - 1) / (2 * BM)) * n_t;
+    const long long single_tiles = (long long)kp.m_shards * ((M_s + BM - 1) / BM) * n_t;
+    CG = (pair_tiles >= cap / 2 || single_tiles == pair_tiles) ? 2 : 1;
+  }
+  if (cap < 2) CG = 1;
+  const int BMT = BM * CG;            // tile rows
+  const int BNL = BN / CG;            // B columns held per CTA
+  kp.m_tiles_per_shard = (M_s + BMT - 1) / BMT;
   kp.n_tiles_per_shard = (N_s + kp.bn_out - 1) / kp.bn_out;
   kp.k_iters_per_shard = (Kc_s + BK - 1) / BK;
   kp.epi = a->epi;
-  kp.group_m = a->group_m > 0 ? a->group_m : 16;
-  kp.m_rot = (a->m_shard_rot > 0 ? a->m_shard_rot : 0) * ((M_s + BM - 1) / BM);
+  kp.group_m = a->group_m > 0 ? a->group_m : (CG == 2 ? 8 : 16);
+  kp.m_rot = (a->m_shard_rot > 0 ? a->m_shard_rot : 0) * kp.m_tiles_per_shard;
   if (kp.group_m > kp.m_shards * kp.m_tiles_per_shard) kp.group_m = kp.m_shards * kp.m_tiles_per_shard;
   kp.alpha = a->alpha;
   kp.c = a->c; kp.c2 = a->c2; kp.c3 = a->c3;
@@ -736,7 +936,7 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
     uint64_t sstride = kp.k_shards > 1 ? (uint64_t)bss * 2 : (uint64_t)a->ldb * 2 * (uint64_t)Kc_s;
     uint64_t dims[4] = {64, (uint64_t)Kc_s, (uint64_t)a->N / 64, (uint64_t)kp.k_shards};
     uint64_t str[3] = {(uint64_t)a->ldb * 2, 128, sstride};
-    uint32_t box[4] = {64, (uint32_t)BK, 4, 1};
+    uint32_t box[4] = {64, (uint32_t)BK, (uint32_t)(BNL / 64), 1};
     rc = encode_tmap(&tB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, a->b, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     kp.b_single = 1;
@@ -751,7 +951,7 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
     uint64_t dims[3] = {(uint64_t)a->Kc, (uint64_t)N_s, (uint64_t)kp.n_shards};
     uint64_t sstride = kp.n_shards > 1 ? (uint64_t)bss * 2 : (uint64_t)a->ldb * 2 * (uint64_t)N_s;
     uint64_t str[2] = {(uint64_t)a->ldb * 2, sstride};
-    uint32_t box[3] = {(uint32_t)BK, (uint32_t)(glu ? 128 : BN), 1};
+    uint32_t box[3] = {(uint32_t)BK, (uint32_t)(glu ? 128 : BNL), 1};
     rc = encode_tmap(&tB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a->b, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     if (glu) {
@@ -761,9 +961,31 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
   }
   if ((kp.n_shards > 1 || kp.k_shards > 1) && bss <= 0) OB_FAIL(-9, "sharded B needs b_shard_stride");
 
+  // Work list: whole tiles, then (accumulating fp32 epilogues only) the tiles of the last partial wave cut into k
+  // slices that meet in the output through reduce-add.
   const int total = kp.m_shards * kp.m_tiles_per_shard * kp.n_shards * kp.n_tiles_per_shard;
-  int cap = a->max_ctas > 0 ? a->max_ctas : sm_count();
-  int grid = total < cap ? total : cap;
+  const int max_workers = cap / CG;
+  const int k_iters_total = kp.k_shards * kp.k_iters_per_shard;
+  kp.split = 1;
+  kp.full_items = total;
+  kp.total_items = total;
+  const bool split_ok = split_k_enabled() && !a->no_split_k && a->ag_src == nullptr &&
+                        ((a->epi == EPI_F32_ACC && a->c_shards == nullptr && !a->no_tma_epilogue) || a->epi == EPI_F32_RED);
+  if (split_ok) {
+    const int rem = total % max_workers;
+    if (rem > 0 && max_workers / rem >= 2) {
+      int split = max_workers / rem;
+      if (split > 8) split = 8;
+      while (split > 1 && k_iters_total / split < 16) --split;
+      if (split > 1) {
+        kp.split = split;
+        kp.full_items = total - rem;
+        kp.total_items = kp.full_items + rem * split;
+      }
+    }
+  }
+  const int workers = kp.total_items < max_workers ? kp.total_items : max_workers;
+  const int grid = workers * CG;
   if (a->ag_src != nullptr && a->ag_on_a) {
     // all-gather of the A operand's row shards (sequence-parallel activations): shard s = rows [s*M_s, (s+1)*M_s)
     const int shards = kp.m_shards;
@@ -826,6 +1048,10 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
       kp.tma_epi = 1;
     }
   }
+  if (kp.split > 1 && a->epi == EPI_F32_ACC && kp.tma_epi != 1) {   // no atomic path for the slices: whole tiles only
+    kp.split = 1;
+    kp.full_items = kp.total_items = total;
+  }
   // peer destinations: staged, line-coalesced stores / reductions (needs 16-byte aligned rows)
   if (kp.tma_epi == 0 && a->c_shards != nullptr && !a->no_tma_epilogue &&
       (a->epi == EPI_F32 || a->epi == EPI_F32_RED || a->epi == EPI_BF16 || (a->epi == EPI_BF16_ACC && a->c != nullptr)) &&
@@ -833,10 +1059,8 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
     kp.tma_epi = 2;
   if (a->c_shards != nullptr && a->epi == EPI_BF16_ACC && kp.tma_epi != 2)
     OB_FAIL(-18, "EPI_BF16_ACC towards c_shards needs the staged epilogue (16-byte aligned rows, local partial in c)");
-  if (a->a_mn) {
-    return a->b_mn ? launch<true, true>(tA, tB, tB2, tC, kp, grid, stream) : launch<true, false>(tA, tB, tB2, tC, kp, grid, stream);
-  }
-  return a->b_mn ? launch<false, true>(tA, tB, tB2, tC, kp, grid, stream) : launch<false, false>(tA, tB, tB2, tC, kp, grid, stream);
+  return CG == 2 ? launch_layout<2>(a->a_mn != 0, a->b_mn != 0, tA, tB, tB2, tC, kp, grid, stream)
+                 : launch_layout<1>(a->a_mn != 0, a->b_mn != 0, tA, tB, tB2, tC, kp, grid, stream);
 }
 
 extern "C" const char* ob_last_error() { return ob::last_error_buf(); }

@@ -69,6 +69,8 @@ typedef struct ObGemmArgs {
   // buffer of M / M_s row shards of which only shard ag_rank is filled; the copy warps fetch shard s from ag_src[s]
   // (a contiguous [M_s, Kc] piece with the same row stride in GPU s's memory) and the tiles of shard s wait for it.
   int ag_on_a;
+  // 1: never cut the tiles of the last partial wave into k slices (accumulating fp32 epilogues do by default)
+  int no_split_k;
 } ObGemmArgs;
 
 int ob_gemm_bf16(const ObGemmArgs* args, cudaStream_t stream);

@@ -20,7 +20,8 @@ import torch
 _LIB: Optional[ctypes.CDLL] = None
 _LOCK = threading.Lock()
 
-LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libolmax_b200.so"
+# OLMAX_B200_LIB selects another build of the kernel library (e.g. one compiled with experimental -D switches)
+LIB_PATH = Path(os.environ.get("OLMAX_B200_LIB") or (Path(__file__).resolve().parent.parent / "lib" / "libolmax_b200.so"))
 
 
 class KernelError(RuntimeError):
@@ -69,6 +70,7 @@ class ObGemmArgs(ctypes.Structure):
         ("multi_box_mn", ctypes.c_int),
         ("no_tma_epilogue", ctypes.c_int),
         ("ag_on_a", ctypes.c_int),
+        ("no_split_k", ctypes.c_int),
     ]
 
 

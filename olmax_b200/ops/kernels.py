@@ -131,6 +131,7 @@ def gemm(
     multi_box_mn: bool = False,
     m_shard_rot: int = 0,
     ag_on_a: bool = False,
+    no_split_k: bool = False,
 ) -> None:
     """``C[M, N] (+)= alpha * A[M, K] . B[K, N]``; see ``csrc/gemm.h`` for operand layouts and sharding."""
     _req_bf16(a, b, b2)
@@ -161,6 +162,7 @@ def gemm(
     args.m_shard_rot = m_shard_rot
     args.multi_box_mn = int(multi_box_mn)
     args.ag_on_a = int(ag_on_a)
+    args.no_split_k = int(no_split_k)
     if prefetch is not None:
         table, dst_ptr, dst_stride, off, nbytes, shards, rank = prefetch
         args.pf_src, args.pf_dst, args.pf_dst_stride = table.data_ptr(), dst_ptr, dst_stride

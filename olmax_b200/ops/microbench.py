@@ -78,8 +78,15 @@ def bench_gemm(iters: int, small: bool):
             continue
         ms = _time(fn, iters)
         tf = 2.0 * M * N * Kd / ms / 1e9
-        out[name] = {"M": M, "N": N, "K": Kd, "ms": round(ms, 4), "tflops": round(tf, 1), "of_measured_burst": round(tf / peak, 3)}
-        print(f"{name:24s} {M:6d}x{N:6d}x{Kd:6d}  {ms:7.3f} ms  {tf:7.1f} TFLOP/s  {tf / peak:5.2f} of measured", flush=True)
+        # the library GEMM on the same operands and layout (comparison only; fp32 outputs compare against a bf16 matmul)
+        am, bm = (a.t() if a_mn else a), (b if b_mn else b.t())
+        lib_out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        ms_lib = _time(lambda: torch.matmul(am, bm, out=lib_out), iters)
+        tf_lib = 2.0 * M * N * Kd / ms_lib / 1e9
+        out[name] = {"M": M, "N": N, "K": Kd, "ms": round(ms, 4), "tflops": round(tf, 1), "of_measured_burst": round(tf / peak, 3),
+                     "cublas_ms": round(ms_lib, 4), "cublas_tflops": round(tf_lib, 1)}
+        print(f"{name:24s} {M:6d}x{N:6d}x{Kd:6d}  {ms:7.3f} ms  {tf:7.1f} TFLOP/s  {tf / peak:5.2f} of measured"
+              f"   | torch.matmul {ms_lib:7.3f} ms {tf_lib:7.1f} TFLOP/s", flush=True)
     # gated-MLP epilogue (two B operands)
     if not small:
         M, N, Kd = 8192, 11008, 4096

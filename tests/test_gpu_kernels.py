@@ -55,6 +55,33 @@ def test_gemm_layouts(K, M, N, Kd):
     _check_status()
 
 
+@pytest.mark.parametrize("M,N,Kd", [(4096, 4608, 1024), (2304, 5120, 2048), (1152, 20000, 256)])
+def test_gemm_cta_pair_tiles_and_split_k_tail(K, M, N, Kd):
+    """Shapes with enough 256 x 256 tiles that the CTA-pair kernel (tcgen05.mma.cta_group::2) runs, ragged in M and N,
+    in all three layouts; the accumulating fp32 epilogue also with its last wave cut into k slices."""
+    dev = "cuda"
+    torch.manual_seed(3)
+    a = torch.randn(M, Kd, device=dev, dtype=torch.bfloat16)
+    b = torch.randn(N, Kd, device=dev, dtype=torch.bfloat16)
+    want = a.float() @ b.float().t()
+    c = torch.zeros(M, N, device=dev, dtype=torch.bfloat16)
+    K.gemm(a, b, c, M, N, Kd)
+    assert rel_err(c, want) < 5e-3
+    bt = b.t().contiguous()
+    c.zero_()
+    K.gemm(a, bt, c, M, N, Kd, b_mn=True)
+    assert rel_err(c, want) < 5e-3
+    at = a.t().contiguous()
+    cf = torch.zeros(M, N, device=dev, dtype=torch.float32)
+    K.gemm(at, bt, cf, M, N, Kd, a_mn=True, b_mn=True, epi=K.EPI_F32_ACC)
+    K.gemm(at, bt, cf, M, N, Kd, a_mn=True, b_mn=True, epi=K.EPI_F32_ACC, alpha=0.5)
+    assert rel_err(cf, 1.5 * want) < 1e-4
+    cf2 = torch.zeros(M, N, device=dev, dtype=torch.float32)
+    K.gemm(at, bt, cf2, M, N, Kd, a_mn=True, b_mn=True, epi=K.EPI_F32_ACC, alpha=1.5, no_split_k=True)
+    assert rel_err(cf2, 1.5 * want) < 1e-4
+    _check_status()
+
+
 def test_gemm_sharded_operands(K):
     dev = "cuda"
     torch.manual_seed(1)
