@@ -56,6 +56,62 @@ def reference_arm(args) -> int:
     return 0
 
 
+def comm_selfcheck(args, model_cfg, mesh, mesh_res, dev, seq, inst_local, k):
+    """Outside the timed region, on the job's own mesh: a 2-layer copy of the benchmarked architecture is built twice from
+    the same seed, once on the peer-memory ("fused") backend and once on NCCL, and trained for 2 optimizer steps of k
+    micro-batches on identical data.  Returns the largest relative differences over all ranks of the losses, the
+    accumulated gradient of step 1 and the fp32 master weights after step 2: evidence, in every benchmark record, that
+    the all-gather / reduce-scatter / all-reduce fused into our kernels give the numbers of the library collectives
+    (the sharded-vs-reference invariant of the reference's ``src/test/nn/transformer/model_test.py:79-134``)."""
+    import dataclasses
+
+    import torch
+    import torch.distributed as dist
+
+    from olmax_b200.ops import _lib
+    from olmax_b200.optim import AdamWConfig, ConstantSchedule
+    from olmax_b200.testing import rel_err
+
+    small = dataclasses.replace(model_cfg, num_layers=2)
+    inst = inst_local * mesh.tp.size * mesh.cp.size
+    results = {}
+    for backend in ("fused", "nccl"):
+        model = small.build(seed=3, mesh=mesh, device=dev, comm_backend=backend)
+        if backend == "fused" and model.store.symm is None and model.store.tp_symm is None:
+            return {"skipped": "peer-memory backend not active on this mesh"}
+        cache = model.get_buffer_cache(seq, dev)
+        optim = AdamWConfig(lr=ConstantSchedule(1e-3), no_decay_modules=["embedding.weight"]).build(model, k)
+        gen = torch.Generator().manual_seed(1234 + mesh.data_parallel_rank)
+        losses, first_grad = [], None
+        for step in range(2):
+            for _ in range(k):
+                ids = torch.randint(0, small.vocab_size, (inst, seq), generator=gen)
+                labels = torch.roll(ids, -1, 1)
+                if mesh.cp.size > 1:
+                    from olmax_b200.parallel.context import shard_sequence_for_cp
+                    ids = shard_sequence_for_cp(ids, mesh.cp.size, mesh.cp.rank)
+                    labels = shard_sequence_for_cp(labels, mesh.cp.size, mesh.cp.rank)
+                loss, _ = model(ids.to(dev), labels.to(dev), cache)
+                loss.backward()
+                optim.accumulate()
+                losses.append(loss.detach().float())
+            if step == 0:
+                first_grad = model.store.grad.detach().clone()
+            optim.step()
+        torch.cuda.synchronize()
+        _lib.check_status(dev)
+        results[backend] = (torch.stack(losses).cpu(), first_grad.cpu(), model.store.master.detach().clone().cpu())
+        del model, optim, cache
+        torch.cuda.empty_cache()
+    lf, gf, pf = results["fused"]
+    ln, gn, pn = results["nccl"]
+    t = torch.tensor([float(((lf - ln).abs() / ln.abs().clamp_min(1e-12)).max()), rel_err(gf, gn), rel_err(pf, pn)],
+                     dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return {"loss_rel": float(t[0]), "grad_rel": float(t[1]), "param_rel_after_2_steps": float(t[2]),
+            "layers": 2, "optimizer_steps": 2, "microbatches": k, "tolerance": 1e-2}
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons of this rank's GPU with nvidia-smi while the timed region runs."""
 
@@ -124,6 +180,8 @@ def main() -> int:
     ap.add_argument("--microbatches", type=int, default=2)
     ap.add_argument("--layers", type=int, default=None, help="debug only: truncate the model (makes the run INVALID as a benchmark)")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-selfcheck", action="store_true",
+                    help="multi-GPU runs: do not compare the fused backend against NCCL on a 2-layer model first")
     ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl"],
                     help="fused: collectives inside our kernels over peer memory; nccl: the NCCL baseline path")
     ap.add_argument("--ac", default="recipe", choices=["recipe", "none", "mlp", "full"],
@@ -181,6 +239,15 @@ def main() -> int:
     global_batch = inst_per_dp * dp * k
     tokens_per_step = global_batch * seq
 
+    selfcheck = None
+    if world > 1 and args.comm in ("auto", "fused") and not args.skip_selfcheck:
+        selfcheck = comm_selfcheck(args, model_cfg, mesh, mesh_res, dev, seq, inst_local, k)
+        bad = [n for n in ("loss_rel", "grad_rel", "param_rel_after_2_steps") if not (selfcheck.get(n, 0.0) <= 1e-2)]
+        if bad:
+            if rank == 0:
+                print(json.dumps({"error": "fused and NCCL backends disagree", "selfcheck": selfcheck}), flush=True)
+            return 2
+
     model = model_cfg.build(seed=1, mesh=mesh, device=dev, comm_backend=args.comm)
     cache = model.get_buffer_cache(seq, dev)
     lr = 1e-4
@@ -202,8 +269,11 @@ def main() -> int:
             dist.barrier()
             torch.cuda.synchronize()
 
+    loss_first_step = None
     for w in range(args.warmup):
-        trainer.train_batch(dev_batches[w % len(dev_batches)])
+        first = trainer.train_batch(dev_batches[w % len(dev_batches)])
+        if w == 0:
+            loss_first_step = float(first.item())
     sync_all()
     _lib.check_status(dev)
 
@@ -281,6 +351,8 @@ def main() -> int:
             "mfu_of_measured_sustained": round(per_gpu * flops_tok / (sustained * 1e12), 4),
             "tflops_per_gpu": round(per_gpu * flops_tok / 1e12, 1),
             "loss": final_loss,
+            "loss_first_step": loss_first_step,
+            "selfcheck": selfcheck,
             "gpu_launches": launches,
             "clocks": clocks,
             "peak_mem_gib": round(torch.cuda.max_memory_allocated(dev) / 2**30, 2),
