@@ -31,7 +31,7 @@ constexpr int T = 128;    // tile (queries and keys)
 constexpr int HD = 128;
 constexpr int BLK = 128 * 64 * 2;   // 16 KiB swizzled block [128 rows][64 elems]
 constexpr int TILE = 2 * BLK;       // 32 KiB
-constexpr int STAGES = 2;
+constexpr int STAGES = 2;   // the loops below index stages with (it & 1)
 constexpr int OFF_K = 0;
 constexpr int OFF_V = TILE;
 constexpr int OFF_Q = 2 * TILE;                    // STAGES tiles
@@ -136,8 +136,12 @@ __global__ void __launch_bounds__(THREADS, 1)
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  // The TMA, MMA and dQ-store warps run their loops with all 32 lanes so that the loop state stays warp-uniform; one
+  // elected lane issues.  A wait that gives up marks the warp `dead`: the loop then runs out without issuing anything.
   if (warp == 0) {
-    if (lane == 0 && n_iters > 0) {
+    const bool leader = elect_one();
+    bool dead = false;
+    if (leader && n_iters > 0) {
       tma_prefetch_desc(&tmQ);
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
@@ -147,14 +151,15 @@ __global__ void __launch_bounds__(THREADS, 1)
       tma_load_4d(smem + OFF_K + BLK, &tmK, kv_full, 64, hkv, kv0, b);
       tma_load_4d(smem + OFF_V, &tmV, kv_full, 0, hkv, kv0, b);
       tma_load_4d(smem + OFF_V + BLK, &tmV, kv_full, 64, hkv, kv0, b);
-      bool ok = true;
-      for (int it = 0; it < n_iters && ok; ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-        const int h = hkv * G + it / n_q;
-        const int q0 = (i_lo + it % n_q) * T;
-        ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag, p.status, 700);
-        if (!ok) break;
+    }
+    int hq = 0, iq = 0;   // query head within the group, query tile within [i_lo, i_hi]
+    for (int it = 0; it < n_iters; ++it) {
+      const int s = it & 1;
+      const uint32_t ph = (uint32_t)(it >> 1) & 1u;
+      const int h = hkv * G + hq;
+      const int q0 = (i_lo + iq) * T;
+      if (!dead) dead = !mbar_wait(&empty[s], ph ^ 1u, abort_flag, p.status, 700);
+      if (leader && !dead) {
         mbar_arrive_expect_tx(&full[s], 2 * TILE);
         uint8_t* sq = smem + OFF_Q + s * TILE;
         uint8_t* sdo = smem + OFF_DO + s * TILE;
@@ -163,98 +168,110 @@ __global__ void __launch_bounds__(THREADS, 1)
         tma_load_4d(sdo, &tmDO, &full[s], 0, h, q0, b);
         tma_load_4d(sdo + BLK, &tmDO, &full[s], 64, h, q0, b);
       }
+      if (++iq == n_q) {
+        iq = 0;
+        ++hq;
+      }
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0 && n_iters > 0) {
+    const bool leader = elect_one();
+    if (n_iters > 0) {
       constexpr uint32_t id_kk = make_idesc_bf16(T, T, 0, 0);    // both K-major
       constexpr uint32_t id_mm = make_idesc_bf16(T, HD, 1, 1);   // both MN-major
       constexpr uint32_t id_km = make_idesc_bf16(T, HD, 0, 1);   // A K-major, B MN-major
-      const uint32_t aK = smem_u32(smem + OFF_K), aV = smem_u32(smem + OFF_V), aP = smem_u32(smem + OFF_P);
-      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, 800);
+      // Shared-memory descriptors: the high word depends only on the operand's major-ness, the low word is the start
+      // address in 16-byte units.  A K-major [128][128] tile is two [128][64] blocks: k step kk sits at
+      // (kk / 4) * BLK + (kk % 4) * 32 bytes; in an MN-major tile k step kk sits at kk * 2048 bytes.
+      const uint64_t d_k = make_smem_desc(0, 0, 1024), d_mn = make_smem_desc(0, BLK, 1024);
+      const uint32_t hi_k = (uint32_t)(d_k >> 32), hi_mn = (uint32_t)(d_mn >> 32);
+      const uint32_t lo_flags_k = (uint32_t)d_k, lo_flags_mn = (uint32_t)d_mn;   // low-word bits above the address
+      auto lo = [](uint32_t addr) { return (addr & 0x3FFFFu) >> 4; };
+      const uint32_t aK = lo(smem_u32(smem + OFF_K)), aV = lo(smem_u32(smem + OFF_V)), aP = lo(smem_u32(smem + OFF_P));
+      const uint32_t aQ0 = lo(smem_u32(smem + OFF_Q)), aDO0 = lo(smem_u32(smem + OFF_DO));
+      constexpr uint32_t TILE16 = TILE >> 4;
+      bool dead = !mbar_wait(kv_full, 0, abort_flag, p.status, 800);
+      auto koff = [](int kk) { return ((uint32_t)(kk >> 2) * BLK + (uint32_t)(kk & 3) * 32) >> 4; };
       auto issue_s = [&](uint32_t aQ) {
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (uint32_t)(kk >> 2) * BLK + (uint32_t)(kk & 3) * 32;
-          umma_ss(tmem_base + C_S, make_smem_desc(aQ + off, 0, 1024), make_smem_desc(aK + off, 0, 1024), id_kk,
-                  kk != 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < HD / 16; ++kk)
+          umma_ss_lohi(tmem_base + C_S, lo_flags_k | (aQ + koff(kk)), hi_k, lo_flags_k | (aK + koff(kk)), hi_k, id_kk,
+                       kk != 0 ? 1u : 0u);
       };
       auto issue_dp = [&](uint32_t aDO) {
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (uint32_t)(kk >> 2) * BLK + (uint32_t)(kk & 3) * 32;
-          umma_ss(tmem_base + C_DP, make_smem_desc(aDO + off, 0, 1024), make_smem_desc(aV + off, 0, 1024), id_kk,
-                  kk != 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < HD / 16; ++kk)
+          umma_ss_lohi(tmem_base + C_DP, lo_flags_k | (aDO + koff(kk)), hi_k, lo_flags_k | (aV + koff(kk)), hi_k, id_kk,
+                       kk != 0 ? 1u : 0u);
       };
-      if (ok) ok = mbar_wait(&full[0], 0, abort_flag, p.status, 801);
-      if (ok) {
-        tc_fence_after_sync();
-        issue_s(smem_u32(smem + OFF_Q));
+      if (!dead) dead = !mbar_wait(&full[0], 0, abort_flag, p.status, 801);
+      tc_fence_after_sync();
+      if (leader && !dead) {
+        issue_s(aQ0);
         umma_commit(s_full);
-        issue_dp(smem_u32(smem + OFF_DO));
+        issue_dp(aDO0);
         umma_commit(dp_full);
       }
-      for (int it = 0; it < n_iters && ok; ++it) {
-        const int s = it % STAGES;
+      for (int it = 0; it < n_iters; ++it) {
+        const int s = it & 1;
         const uint32_t ph1 = (uint32_t)it & 1u;
-        const uint32_t aQ = smem_u32(smem + OFF_Q + s * TILE);
-        const uint32_t aDO = smem_u32(smem + OFF_DO + s * TILE);
+        const uint32_t aQ = aQ0 + (uint32_t)s * TILE16;
+        const uint32_t aDO = aDO0 + (uint32_t)s * TILE16;
         // dV += P^T dO
-        ok = mbar_wait(p_ready, ph1, abort_flag, p.status, 802);
-        if (!ok) break;
+        if (!dead) dead = !mbar_wait(p_ready, ph1, abort_flag, p.status, 802);
         tc_fence_after_sync();
+        if (leader && !dead) {
 #pragma unroll
-        for (int kk = 0; kk < T / 16; ++kk) {
-          umma_ss(tmem_base + C_DV, make_smem_desc(aP + (uint32_t)kk * 2048, BLK, 1024),
-                  make_smem_desc(aDO + (uint32_t)kk * 2048, BLK, 1024), id_mm, (it | kk) != 0 ? 1u : 0u);
+          for (int kk = 0; kk < T / 16; ++kk)
+            umma_ss_lohi(tmem_base + C_DV, lo_flags_mn | (aP + (uint32_t)kk * 128u), hi_mn,
+                         lo_flags_mn | (aDO + (uint32_t)kk * 128u), hi_mn, id_mm, (it | kk) != 0 ? 1u : 0u);
+          umma_commit(pv_done);
         }
-        umma_commit(pv_done);
         // dK += dS^T Q ; dQ_part = dS K
-        ok = mbar_wait(ds_ready, ph1, abort_flag, p.status, 803);
-        if (!ok) break;
+        if (!dead) dead = !mbar_wait(ds_ready, ph1, abort_flag, p.status, 803);
         tc_fence_after_sync();
+        if (leader && !dead) {
 #pragma unroll
-        for (int kk = 0; kk < T / 16; ++kk) {
-          umma_ss(tmem_base + C_DK, make_smem_desc(aP + (uint32_t)kk * 2048, BLK, 1024),
-                  make_smem_desc(aQ + (uint32_t)kk * 2048, BLK, 1024), id_mm, (it | kk) != 0 ? 1u : 0u);
-        }
+          for (int kk = 0; kk < T / 16; ++kk)
+            umma_ss_lohi(tmem_base + C_DK, lo_flags_mn | (aP + (uint32_t)kk * 128u), hi_mn,
+                         lo_flags_mn | (aQ + (uint32_t)kk * 128u), hi_mn, id_mm, (it | kk) != 0 ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < T / 16; ++kk) {
-          const uint32_t off = (uint32_t)(kk >> 2) * BLK + (uint32_t)(kk & 3) * 32;
-          umma_ss(tmem_base + C_S, make_smem_desc(aP + off, 0, 1024),
-                  make_smem_desc(aK + (uint32_t)kk * 2048, BLK, 1024), id_km, kk != 0 ? 1u : 0u);
+          for (int kk = 0; kk < T / 16; ++kk)
+            umma_ss_lohi(tmem_base + C_S, lo_flags_k | (aP + koff(kk)), hi_k, lo_flags_mn | (aK + (uint32_t)kk * 128u), hi_mn,
+                         id_km, kk != 0 ? 1u : 0u);
+          umma_commit(dq_full);   // also tells the compute warps that every MMA reading stage s has finished
         }
-        umma_commit(dq_full);   // also tells the compute warps that every MMA reading stage s has finished
         if (it + 1 < n_iters) {
-          const int s2 = (it + 1) % STAGES;
-          const uint32_t ph2 = (uint32_t)((it + 1) / STAGES) & 1u;
-          ok = mbar_wait(&full[s2], ph2, abort_flag, p.status, 804);
-          if (!ok) break;
+          const int s2 = (it + 1) & 1;
+          const uint32_t ph2 = (uint32_t)((it + 1) >> 1) & 1u;
+          if (!dead) dead = !mbar_wait(&full[s2], ph2, abort_flag, p.status, 804);
           tc_fence_after_sync();
-          issue_dp(smem_u32(smem + OFF_DO + s2 * TILE));
-          umma_commit(dp_full);
-          ok = mbar_wait(dq_read, ph1, abort_flag, p.status, 805);
-          if (!ok) break;
+          if (leader && !dead) {
+            issue_dp(aDO0 + (uint32_t)s2 * TILE16);
+            umma_commit(dp_full);
+          }
+          if (!dead) dead = !mbar_wait(dq_read, ph1, abort_flag, p.status, 805);
           tc_fence_after_sync();
-          issue_s(smem_u32(smem + OFF_Q + s2 * TILE));
-          umma_commit(s_full);
+          if (leader && !dead) {
+            issue_s(aQ0 + (uint32_t)s2 * TILE16);
+            umma_commit(s_full);
+          }
         }
       }
-      if (ok) umma_commit(all_done);
+      if (leader && !dead) umma_commit(all_done);
     }
     __syncwarp();
   } else if (warp == 10) {
     // ---------------- dQ store warp: fp32 partial tile (in the Q / dO stage) += into global memory ----------------
-    if (lane == 0 && n_iters > 0) {
-      bool ok = true;
-      for (int it = 0; it < n_iters && ok; ++it) {
-        const int s = it % STAGES;
-        const int h = hkv * G + it / n_q;
-        const int q0 = (i_lo + it % n_q) * T;
-        ok = mbar_wait(dq_staged, (uint32_t)it & 1u, abort_flag, p.status, 950);
-        if (!ok) break;
+    const bool leader = elect_one();
+    bool dead = false;
+    int hq = 0, iq = 0;
+    for (int it = 0; it < n_iters; ++it) {
+      const int s = it & 1;
+      const int h = hkv * G + hq;
+      const int q0 = (i_lo + iq) * T;
+      if (!dead) dead = !mbar_wait(dq_staged, (uint32_t)it & 1u, abort_flag, p.status, 950);
+      if (leader && !dead) {
         // columns [0, 64) sit in the Q stage, [64, 128) in the dO stage, 32 columns (128 bytes) per chunk
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
@@ -265,8 +282,12 @@ __global__ void __launch_bounds__(THREADS, 1)
         tma_store_wait_read<0>();      // the stage has been read: hand it back to the TMA producer
         mbar_arrive(&empty[s]);
       }
-      tma_store_wait<0>();
+      if (++iq == n_q) {
+        iq = 0;
+        ++hq;
+      }
     }
+    if (leader) tma_store_wait<0>();
     __syncwarp();
   } else {
     // ---------------- P / dS / dQ / dK / dV: 8 warps, thread <-> (row, 64-column half) ----------------
@@ -496,30 +517,44 @@ static int encode_dq_map(CUtensorMap* m, float* acc, int B, int S, int H) {
 
 using namespace ob;
 
-extern "C" int ob_flash_attn_bwd(const ObAttnArgs* a, cudaStream_t stream) {
-  if (a == nullptr) OB_FAIL(-1, "null args");
+// Everything both entry points share: argument checks (all of them before the first enqueue), tensor maps, the delta
+// pre-pass, clearing the dQ accumulator, the main kernel and the fp32 -> bf16 conversion of dQ.  `delta` ([B, H, S]) and
+// `dq_accum` ([B, S, H, 128], fp32) are the two work buffers, whoever owns them.
+static int launch_flash_bwd(const ObAttnArgs* a, float* delta, float* dq_accum, cudaStream_t stream) {
   if (a->D != 128) OB_FAIL(-2, "flash attention kernels are built for head_dim 128 (got %d)", a->D);
+  if (a->B <= 0 || a->S <= 0 || a->H <= 0 || a->Hkv <= 0) OB_FAIL(-4, "empty problem");
   if (a->H % a->Hkv != 0) OB_FAIL(-3, "H (%d) must be a multiple of Hkv (%d)", a->H, a->Hkv);
-  if (a->delta == nullptr || a->dq_accum == nullptr) OB_FAIL(-4, "backward needs the delta and dq_accum scratch buffers");
   int Sk = 0;
   if (int g = ob_attn_check_geometry(a, &Sk))
     OB_FAIL(-5, "unsupported attention geometry (rule %d): S %d Sk %d q_off %d causal %d window %d", g, a->S, Sk,
             a->q_off, a->causal, a->window);
-  CUtensorMap tq, tk, tv, tdo;
+  CUtensorMap tq, tk, tv, tdo, tdq;
   int rc;
   if ((rc = encode_bshd_map(&tq, a->q, a->B, a->S, a->H, a->q_sb, a->q_ss, a->q_sh, 128))) return rc;
   if ((rc = encode_bshd_map(&tk, a->k, a->B, Sk, a->Hkv, a->k_sb, a->k_ss, a->k_sh, 128))) return rc;
   if ((rc = encode_bshd_map(&tv, a->v, a->B, Sk, a->Hkv, a->v_sb, a->v_ss, a->v_sh, 128))) return rc;
   if ((rc = encode_bshd_map(&tdo, a->d_o, a->B, a->S, a->H, a->do_sb, a->do_ss, a->do_sh, 128))) return rc;
+  if ((rc = fa_bwd::encode_dq_map(&tdq, dq_accum, a->B, a->S, a->H))) return rc;
+  // the shared-memory opt-in is a per-device attribute of the function
+  static bool attr_set[64] = {};
+  int dev = 0;
+  OB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) OB_FAIL(-6, "device ordinal %d outside the supported range [0, 64)", dev);
+  if (!attr_set[dev]) {
+    OB_CUDA_OK(cudaFuncSetAttribute(fa_bwd::flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    fa_bwd::SMEM_BYTES));
+    attr_set[dev] = true;
+  }
 
   const long long rows = (long long)a->B * a->S * a->H;
   const int wpb = 8;  // warps per block
   const unsigned nblk = (unsigned)((rows + wpb - 1) / wpb);
   fa_bwd::attn_delta_kernel<<<nblk, wpb * 32, 0, stream>>>(
       reinterpret_cast<const bf16*>(a->o), a->o_sb, a->o_ss, a->o_sh, reinterpret_cast<const bf16*>(a->d_o), a->do_sb,
-      a->do_ss, a->do_sh, a->delta, a->B, a->S, a->H);
+      a->do_ss, a->do_sh, delta, a->B, a->S, a->H);
   OB_CUDA_OK(cudaGetLastError());
-  OB_CUDA_OK(cudaMemsetAsync(a->dq_accum, 0, (size_t)rows * 128 * sizeof(float), stream));
+  // the accumulator may hold a previous call's sums: clear the part this call uses
+  OB_CUDA_OK(cudaMemsetAsync(dq_accum, 0, (size_t)rows * 128 * sizeof(float), stream));
 
   fa_bwd::Params p;
   p.B = a->B; p.S = a->S; p.H = a->H; p.Hkv = a->Hkv;
@@ -532,26 +567,24 @@ extern "C" int ob_flash_attn_bwd(const ObAttnArgs* a, cudaStream_t stream) {
   p.scale_over_cap = a->softcap > 0.f ? a->scale / a->softcap : 0.f;
   p.cap_log2 = a->softcap * LOG2E;
   p.lse = a->lse;
-  p.delta = a->delta;
-  p.dq_accum = a->dq_accum;
+  p.delta = delta;
+  p.dq_accum = dq_accum;
   p.dk = reinterpret_cast<bf16*>(a->dk); p.dk_sb = a->dk_sb; p.dk_ss = a->dk_ss; p.dk_sh = a->dk_sh;
   p.dv = reinterpret_cast<bf16*>(a->dv); p.dv_sb = a->dv_sb; p.dv_ss = a->dv_ss; p.dv_sh = a->dv_sh;
   p.status = a->status;
-  static bool attr_set = false;
-  if (!attr_set) {
-    OB_CUDA_OK(cudaFuncSetAttribute(fa_bwd::flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    fa_bwd::SMEM_BYTES));
-    attr_set = true;
-  }
   dim3 grid((Sk + 127) / 128, a->Hkv, a->B);
-  CUtensorMap tdq;
-  if ((rc = fa_bwd::encode_dq_map(&tdq, a->dq_accum, a->B, a->S, a->H))) return rc;
   fa_bwd::flash_bwd_kernel<<<grid, fa_bwd::THREADS, fa_bwd::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdq, p);
   OB_CUDA_OK(cudaGetLastError());
-  fa_bwd::attn_dq_convert_kernel<<<nblk, wpb * 32, 0, stream>>>(a->dq_accum, reinterpret_cast<bf16*>(a->dq), a->dq_sb,
+  fa_bwd::attn_dq_convert_kernel<<<nblk, wpb * 32, 0, stream>>>(dq_accum, reinterpret_cast<bf16*>(a->dq), a->dq_sb,
                                                                a->dq_ss, a->dq_sh, a->B, a->S, a->H);
   OB_CUDA_OK(cudaGetLastError());
   return 0;
+}
+
+extern "C" int ob_flash_attn_bwd(const ObAttnArgs* a, cudaStream_t stream) {
+  if (a == nullptr) OB_FAIL(-1, "null args");
+  if (a->delta == nullptr || a->dq_accum == nullptr) OB_FAIL(-4, "backward needs the delta and dq_accum scratch buffers");
+  return launch_flash_bwd(a, a->delta, a->dq_accum, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -593,9 +626,7 @@ static int scratch_for_current_device(float** out) {
 extern "C" int ob_flash_attn_bwd_static(const ObAttnArgs* a, cudaStream_t stream) {
   using namespace ob::fa_bwd_static;
   if (a == nullptr) OB_FAIL(-1, "null args");
-  if (a->D != 128) OB_FAIL(-2, "flash attention kernels are built for head_dim 128 (got %d)", a->D);
   if (a->B <= 0 || a->S <= 0 || a->H <= 0 || a->Hkv <= 0) OB_FAIL(-4, "empty problem");
-  if (a->H % a->Hkv != 0) OB_FAIL(-3, "H (%d) must be a multiple of Hkv (%d)", a->H, a->Hkv);
   const long long rows = (long long)a->B * a->S * a->H;
   if (rows > MAX_ROWS)
     OB_FAIL(-20, "B*S*H = %lld exceeds the %lld rows the built-in work area holds; use ob_flash_attn_bwd with "
@@ -603,57 +634,6 @@ extern "C" int ob_flash_attn_bwd_static(const ObAttnArgs* a, cudaStream_t stream
   float* scratch = nullptr;
   int rc = scratch_for_current_device(&scratch);
   if (rc) return rc;
-  float* dq_accum = scratch;                     // [rows, 128]
-  float* delta = scratch + MAX_ROWS * 128;       // [rows]
-  int Sk = 0;
-  if (int g = ob_attn_check_geometry(a, &Sk))
-    OB_FAIL(-5, "unsupported attention geometry (rule %d): S %d Sk %d q_off %d causal %d window %d", g, a->S, Sk,
-            a->q_off, a->causal, a->window);
-
-  CUtensorMap tq, tk, tv, tdo;
-  if ((rc = encode_bshd_map(&tq, a->q, a->B, a->S, a->H, a->q_sb, a->q_ss, a->q_sh, 128))) return rc;
-  if ((rc = encode_bshd_map(&tk, a->k, a->B, Sk, a->Hkv, a->k_sb, a->k_ss, a->k_sh, 128))) return rc;
-  if ((rc = encode_bshd_map(&tv, a->v, a->B, Sk, a->Hkv, a->v_sb, a->v_ss, a->v_sh, 128))) return rc;
-  if ((rc = encode_bshd_map(&tdo, a->d_o, a->B, a->S, a->H, a->do_sb, a->do_ss, a->do_sh, 128))) return rc;
-
-  const int wpb = 8;
-  const unsigned nblk = (unsigned)((rows + wpb - 1) / wpb);
-  fa_bwd::attn_delta_kernel<<<nblk, wpb * 32, 0, stream>>>(
-      reinterpret_cast<const bf16*>(a->o), a->o_sb, a->o_ss, a->o_sh, reinterpret_cast<const bf16*>(a->d_o), a->do_sb,
-      a->do_ss, a->do_sh, delta, a->B, a->S, a->H);
-  OB_CUDA_OK(cudaGetLastError());
-  // the accumulator still holds the previous call's sums: clear the part this call uses
-  OB_CUDA_OK(cudaMemsetAsync(dq_accum, 0, (size_t)rows * 128 * sizeof(float), stream));
-
-  fa_bwd::Params p;
-  p.B = a->B; p.S = a->S; p.H = a->H; p.Hkv = a->Hkv;
-  p.Sk = Sk; p.q_off = a->q_off;
-  p.causal = a->causal; p.window = a->window;
-  const float LOG2E = 1.4426950408889634f;
-  p.scale = a->scale;
-  p.scale_log2 = a->scale * LOG2E;
-  p.softcap = a->softcap;
-  p.scale_over_cap = a->softcap > 0.f ? a->scale / a->softcap : 0.f;
-  p.cap_log2 = a->softcap * LOG2E;
-  p.lse = a->lse;
-  p.delta = delta;
-  p.dq_accum = dq_accum;
-  p.dk = reinterpret_cast<bf16*>(a->dk); p.dk_sb = a->dk_sb; p.dk_ss = a->dk_ss; p.dk_sh = a->dk_sh;
-  p.dv = reinterpret_cast<bf16*>(a->dv); p.dv_sb = a->dv_sb; p.dv_ss = a->dv_ss; p.dv_sh = a->dv_sh;
-  p.status = a->status;
-  static bool attr_set = false;
-  if (!attr_set) {
-    OB_CUDA_OK(cudaFuncSetAttribute(fa_bwd::flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    fa_bwd::SMEM_BYTES));
-    attr_set = true;
-  }
-  dim3 grid((Sk + 127) / 128, a->Hkv, a->B);
-  CUtensorMap tdq;
-  if ((rc = fa_bwd::encode_dq_map(&tdq, dq_accum, a->B, a->S, a->H))) return rc;
-  fa_bwd::flash_bwd_kernel<<<grid, fa_bwd::THREADS, fa_bwd::SMEM_BYTES, stream>>>(tq, tk, tv, tdo, tdq, p);
-  OB_CUDA_OK(cudaGetLastError());
-  fa_bwd::attn_dq_convert_kernel<<<nblk, wpb * 32, 0, stream>>>(dq_accum, reinterpret_cast<bf16*>(a->dq), a->dq_sb,
-                                                               a->dq_ss, a->dq_sh, a->B, a->S, a->H);
-  OB_CUDA_OK(cudaGetLastError());
-  return 0;
+  // dQ accumulator [rows, 128] first, delta [rows] after the accumulator's full-size region
+  return launch_flash_bwd(a, scratch + MAX_ROWS * 128, scratch, stream);
 }

@@ -118,25 +118,30 @@ __global__ void __launch_bounds__(THREADS, 2)
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  // The TMA and MMA warps run their loops with all 32 lanes so that the loop state stays warp-uniform; one elected
+  // lane issues.  A wait that gives up marks the warp `dead`: the loop then runs out without issuing anything.
   if (warp == 0) {
-    if (lane == 0) {
+    const bool leader = elect_one();
+    bool dead = false;
+    if (leader) {
       tma_prefetch_desc(&tmQ);
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
       mbar_arrive_expect_tx(q_full, TILE_BYTES);
       tma_load_4d(sQ, &tmQ, q_full, 0, h, q0, b);
       tma_load_4d(sQ + BLK, &tmQ, q_full, 64, h, q0, b);
-      bool ok = true;
-      for (int j = 0; j < n_iters && ok; ++j) {
-        const int kv0 = (kv_tile_lo + j) * TK;
-        const uint32_t ph = (uint32_t)j & 1u;
-        ok = mbar_wait(k_empty, ph ^ 1u, abort_flag, p.status, 400);
-        if (!ok) break;
+    }
+    for (int j = 0; j < n_iters; ++j) {
+      const int kv0 = (kv_tile_lo + j) * TK;
+      const uint32_t ph = (uint32_t)j & 1u;
+      if (!dead) dead = !mbar_wait(k_empty, ph ^ 1u, abort_flag, p.status, 400);
+      if (leader && !dead) {
         mbar_arrive_expect_tx(k_full, TILE_BYTES);
         tma_load_4d(sK, &tmK, k_full, 0, hkv, kv0, b);
         tma_load_4d(sK + BLK, &tmK, k_full, 64, hkv, kv0, b);
-        ok = mbar_wait(v_empty, ph ^ 1u, abort_flag, p.status, 401);
-        if (!ok) break;
+      }
+      if (!dead) dead = !mbar_wait(v_empty, ph ^ 1u, abort_flag, p.status, 401);
+      if (leader && !dead) {
         mbar_arrive_expect_tx(v_full, TILE_BYTES);
         tma_load_4d(sV, &tmV, v_full, 0, hkv, kv0, b);
         tma_load_4d(sV + BLK, &tmV, v_full, 64, hkv, kv0, b);
@@ -144,36 +149,39 @@ __global__ void __launch_bounds__(THREADS, 2)
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(TQ, TK, 0, 0);
-      constexpr uint32_t idesc_o = make_idesc_bf16(TQ, HD, 0, 1);
-      const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 500);
-      for (int j = 0; j < n_iters && ok; ++j) {
-        const uint32_t ph = (uint32_t)j & 1u;
-        ok = mbar_wait(k_full, ph, abort_flag, p.status, 501);
-        if (!ok) break;
-        tc_fence_after_sync();
+    const bool leader = elect_one();
+    constexpr uint32_t idesc_s = make_idesc_bf16(TQ, TK, 0, 0);
+    constexpr uint32_t idesc_o = make_idesc_bf16(TQ, HD, 0, 1);
+    // shared-memory descriptors: constant high words, low words (start address in 16-byte units) advanced per k step
+    const uint64_t dQ = make_smem_desc(smem_u32(sQ), 0, 1024), dK = make_smem_desc(smem_u32(sK), 0, 1024);
+    const uint64_t dV = make_smem_desc(smem_u32(sV), BLK, 1024);
+    const uint32_t q_lo = (uint32_t)dQ, k_lo = (uint32_t)dK, v_lo = (uint32_t)dV;
+    const uint32_t kk_hi = (uint32_t)(dQ >> 32), v_hi = (uint32_t)(dV >> 32);
+    bool dead = !mbar_wait(q_full, 0, abort_flag, p.status, 500);
+    for (int j = 0; j < n_iters; ++j) {
+      const uint32_t ph = (uint32_t)j & 1u;
+      if (!dead) dead = !mbar_wait(k_full, ph, abort_flag, p.status, 501);
+      tc_fence_after_sync();
+      if (leader && !dead) {
         // S = Q K^T.  In-order execution of this thread's MMAs keeps it behind the previous P V, which read P
         // from the same columns.
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (uint32_t)(kk >> 2) * BLK + (uint32_t)(kk & 3) * 32;
-          umma_ss(tmem_base + S_COL, make_smem_desc(aQ + off, 0, 1024), make_smem_desc(aK + off, 0, 1024), idesc_s,
-                  kk != 0 ? 1u : 0u);
+          const uint32_t off = ((uint32_t)(kk >> 2) * BLK + (uint32_t)(kk & 3) * 32) >> 4;
+          umma_ss_lohi(tmem_base + S_COL, q_lo + off, kk_hi, k_lo + off, kk_hi, idesc_s, kk != 0 ? 1u : 0u);
         }
         umma_commit(k_empty);
         umma_commit(s_full);
-        ok = mbar_wait(p_full, ph, abort_flag, p.status, 502);
-        if (!ok) break;
-        ok = mbar_wait(v_full, ph, abort_flag, p.status, 503);
-        if (!ok) break;
-        tc_fence_after_sync();
+      }
+      if (!dead) dead = !mbar_wait(p_full, ph, abort_flag, p.status, 502);
+      if (!dead) dead = !mbar_wait(v_full, ph, abort_flag, p.status, 503);
+      tc_fence_after_sync();
+      if (leader && !dead) {
         // O += P V: A = P from TMEM (128 x 16 bf16 per step = 8 columns), B = V as an MN-major operand
 #pragma unroll
         for (int kk = 0; kk < TK / 16; ++kk) {
-          umma_ts(tmem_base + O_COL, tmem_base + S_COL + (uint32_t)kk * 8,
-                  make_smem_desc(aV + (uint32_t)kk * 2048, BLK, 1024), idesc_o, (j | kk) != 0 ? 1u : 0u);
+          umma_ts_lohi(tmem_base + O_COL, tmem_base + S_COL + (uint32_t)kk * 8, v_lo + (uint32_t)kk * 128u, v_hi, idesc_o,
+                       (j | kk) != 0 ? 1u : 0u);
         }
         umma_commit(v_empty);
         umma_commit(o_done);
@@ -356,11 +364,15 @@ extern "C" int ob_flash_attn_fwd(const ObAttnArgs* a, cudaStream_t stream) {
   p.o_sb = a->o_sb; p.o_ss = a->o_ss; p.o_sh = a->o_sh;
   p.lse = a->lse;
   p.status = a->status;
-  static bool attr_set = false;
-  if (!attr_set) {
+  // the shared-memory opt-in is a per-device attribute of the function
+  static bool attr_set[64] = {};
+  int dev = 0;
+  OB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) OB_FAIL(-6, "device ordinal %d outside the supported range [0, 64)", dev);
+  if (!attr_set[dev]) {
     OB_CUDA_OK(cudaFuncSetAttribute(fa_fwd::flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     fa_fwd::SMEM_BYTES));
-    attr_set = true;
+    attr_set[dev] = true;
   }
   dim3 grid((a->S + 127) / 128, a->H, a->B);
   fa_fwd::flash_fwd_kernel<<<grid, fa_fwd::THREADS, fa_fwd::SMEM_BYTES, stream>>>(tq, tk, tv, p);

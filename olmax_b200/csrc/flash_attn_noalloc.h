@@ -16,8 +16,9 @@
 //   * B * S * H must not exceed OB_FLASH_BWD_STATIC_MAX_ROWS (32768, e.g. batch 1 x 4096 tokens x 8 heads); larger
 //     problems are rejected with an error message and must use ob_flash_attn_bwd().  The array occupies
 //     32768 * 129 * 4 bytes = 16.1 MiB on every GPU that loads the library, for the life of the process.
-//   * The first call on a device looks up the array's device address (with that device current) and caches it.  Make
-//     that first call during start-up, outside any stream capture.
+//   * The first call on a device looks up the array's device address (with that device current) and caches it, and
+//     opts the kernel in to its shared-memory size on that device.  Make that first call during start-up, outside any
+//     stream capture, and from one host thread per device (the per-device cache is written without a lock).
 //   * All calls on a device share the one array, which keeps whatever the previous call left in it.  The function
 //     clears the part it accumulates into before use, so back-to-back calls on ONE stream are safe; calls that can
 //     overlap on the GPU (different streams, different host threads) would race on it and must be serialised by the
