@@ -34,9 +34,9 @@ class RuntimeConfig:
     reshard_after_forward: bool = True
     """Free gathered weights after the forward use and gather again for backward (the entrypoint passes it to
     ``TransformerConfig.build``)."""
-    peer_barrier: str = "nccl"
-    """How the peer-memory backend separates its phases: ``nccl`` (a one-element all-reduce) or ``flags`` (the bounded
-    flag-word barrier kernel); ``OLMAX_B200_BARRIER``."""
+    peer_barrier: str = "flags"
+    """How the peer-memory backend separates its phases: ``flags`` (the bounded flag-word barrier kernel, default) or
+    ``nccl`` (a one-element all-reduce); ``OLMAX_B200_BARRIER``."""
     peer_wait_timeout_ms: int = 600_000
     """Upper bound of the flag barrier's wait for another GPU (``OLMAX_B200_BARRIER_TIMEOUT_S``); a wait that runs out
     raises on the host instead of hanging the GPU.  The waits inside the GEMMs have a fixed iteration limit."""

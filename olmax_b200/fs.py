@@ -10,6 +10,7 @@ capped at 3 s), like the reference.
 
 from __future__ import annotations
 
+import abc
 import concurrent.futures
 import functools
 import io
@@ -101,13 +102,26 @@ def retriable(max_attempts: int = 3, retriable_errors: Tuple[type, ...] = (OSErr
 # ----------------------------------------------------------------------------------------------------------------------
 # remote back-ends (lazy)
 # ----------------------------------------------------------------------------------------------------------------------
-class _Backend:
-    def size(self, bucket: str, key: str) -> int: raise NotImplementedError
-    def read_range(self, bucket: str, key: str, start: int, n: int) -> bytes: raise NotImplementedError
-    def upload(self, src: Path, bucket: str, key: str, overwrite: bool) -> None: raise NotImplementedError
-    def exists(self, bucket: str, key: str) -> bool: raise NotImplementedError
-    def remove(self, bucket: str, key: str) -> None: raise NotImplementedError
-    def list(self, bucket: str, prefix: str, recursive: bool) -> List[str]: raise NotImplementedError
+class _Backend(abc.ABC):
+    """What a remote store has to offer; ``bucket`` / ``key`` are the host and path parts of the URL."""
+
+    @abc.abstractmethod
+    def size(self, bucket: str, key: str) -> int: ...
+
+    @abc.abstractmethod
+    def read_range(self, bucket: str, key: str, start: int, n: int) -> bytes: ...
+
+    @abc.abstractmethod
+    def exists(self, bucket: str, key: str) -> bool: ...
+
+    def upload(self, src: Path, bucket: str, key: str, overwrite: bool) -> None:
+        raise OLMaxUploadError(f"{type(self).__name__} is read-only")
+
+    def remove(self, bucket: str, key: str) -> None:
+        raise OLMaxUploadError(f"{type(self).__name__} is read-only")
+
+    def list(self, bucket: str, prefix: str, recursive: bool) -> List[str]:
+        raise OLMaxNetworkError(f"{type(self).__name__} cannot list a directory")
 
 
 class _S3Backend(_Backend):

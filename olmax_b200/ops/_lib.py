@@ -146,12 +146,22 @@ _STATUS: dict = {}
 
 def status_buffer(device: torch.device) -> torch.Tensor:
     """Per-device int32[4] that kernels write when a bounded wait runs out (all zero = healthy)."""
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    key = (device.type, device.index if (device.index is not None or device.type != "cuda") else torch.cuda.current_device())
     buf = _STATUS.get(key)
     if buf is None:
         buf = torch.zeros(4, dtype=torch.int32, device=device)
         _STATUS[key] = buf
     return buf
+
+
+_STATUS_NAMES = {1: "mbarrier wait timed out", 2: "peer flag wait timed out", 3: "bad argument"}
+
+
+def raise_for_status(vals) -> None:
+    """Raise :class:`KernelError` when ``vals`` (the four status words: code, site, block, extra) report a failure."""
+    if int(vals[0]) != 0:
+        raise KernelError(f"kernel reported '{_STATUS_NAMES.get(int(vals[0]), int(vals[0]))}' at site {int(vals[1])}, "
+                          f"block {int(vals[2])}, extra {int(vals[3])}")
 
 
 def check_status(device: Optional[torch.device] = None) -> None:
@@ -162,10 +172,29 @@ def check_status(device: Optional[torch.device] = None) -> None:
     vals = buf.tolist()
     if vals[0] != 0:
         buf.zero_()
-        names = {1: "mbarrier wait timed out", 2: "peer flag wait timed out", 3: "bad argument"}
-        raise KernelError(
-            f"kernel reported '{names.get(vals[0], vals[0])}' at site {vals[1]}, block {vals[2]}, extra {vals[3]}"
-        )
+        raise_for_status(vals)
+
+
+def snapshot_status(device: torch.device):
+    """Non-blocking copy of the status words, to be looked at later with :func:`resolve_status`: on a GPU the copy goes
+    to pinned host memory behind everything already enqueued on the current stream, so reading it one step later costs
+    no synchronisation.  (On a CPU device the buffer only exists for tests and is cloned.)"""
+    buf = status_buffer(device)
+    if not buf.is_cuda:
+        return (buf.clone(), None)
+    host = torch.empty(4, dtype=torch.int32, pin_memory=True)
+    host.copy_(buf, non_blocking=True)
+    ev = torch.cuda.Event()
+    ev.record()
+    return (host, ev)
+
+
+def resolve_status(snapshot) -> None:
+    """Wait for a :func:`snapshot_status` copy and raise :class:`KernelError` if it shows a failure."""
+    host, ev = snapshot
+    if ev is not None:
+        ev.synchronize()
+    raise_for_status(host.tolist())
 
 
 class ObAttnArgs(ctypes.Structure):

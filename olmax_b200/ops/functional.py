@@ -43,9 +43,16 @@ def _b_operand(handle):
     return first, {"N_s": handle.rows_local, "b_shard_stride": stride}
 
 
-def _ag_kwargs(handle, second=None) -> dict:
+def _ag_kwargs(handle, second=None, extra: Optional[dict] = None) -> dict:
     """GEMM arguments that fuse the FSDP all-gather of ``handle`` (and ``second``, the up-projection of a gated
-    MLP) into the launch, when the peer-memory backend still has to fetch their remote shards."""
+    MLP) into the launch, when the peer-memory backend still has to fetch their remote shards.  A launch fuses one
+    all-gather: when ``extra`` already carries the tensor-parallel gather of the activation rows, the weight's remote
+    shards are fetched by the stand-alone plain-load kernel first (``ParamHandle.full``)."""
+    if extra and "ag_src" in extra:
+        handle.full()
+        if second is not None:
+            second.full()
+        return {}
     ag = handle.take_ag()
     if ag is None:
         return {}
@@ -65,10 +72,9 @@ def _gemm_fwd(x2: torch.Tensor, handle, out: Optional[torch.Tensor] = None, epi:
     M, Kd = x2.shape
     N = handle.tp_shape[0]
     first, kw = _b_operand(handle)
-    kw.update(_ag_kwargs(handle))
+    kw.update(_ag_kwargs(handle, extra=extra))
     kw["prefetch"] = handle.store.prefetch_slice(N * Kd)
     if extra:
-        assert "ag_src" not in kw or "ag_src" not in extra, "one fused all-gather per GEMM"
         kw.update(extra)
     if out is None:
         out = torch.empty((M, N), dtype=torch.float32 if epi == K.EPI_F32 else torch.bfloat16, device=x2.device)
@@ -86,10 +92,9 @@ def _gemm_dgrad(dy2: torch.Tensor, handle, out: Optional[torch.Tensor] = None, a
     first, stride = handle.pieces()
     R = handle.shard_count
     kw = {} if R == 1 else {"Kc_s": handle.rows_local, "b_shard_stride": stride}
-    kw.update(_ag_kwargs(handle))
+    kw.update(_ag_kwargs(handle, extra=extra))
     kw["prefetch"] = handle.store.prefetch_slice(N * Kd)
     if extra:
-        assert "ag_src" not in kw or "ag_src" not in extra, "one fused all-gather per GEMM"
         kw.update(extra)
     if out is None:
         out = torch.empty((M, Kd), dtype=torch.bfloat16, device=dy2.device)
@@ -183,7 +188,7 @@ class _GatedMLPFn(torch.autograd.Function):
         h = gate.tp_shape[0]
         gfirst, kw = _b_operand(gate)
         ufirst, _ = up.pieces()
-        kw.update(_ag_kwargs(gate, up))
+        kw.update(_ag_kwargs(gate, up, extra=ag_kw))
         kw["prefetch"] = gate.store.prefetch_slice(2 * h * d)
         if ag_kw:
             kw.update(ag_kw)

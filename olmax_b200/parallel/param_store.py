@@ -378,7 +378,7 @@ class ParamStore:
         self.master = torch.zeros(off, dtype=self.param_dtype, device=dev)
         use_symm = False
         if (self.comm_backend in ("auto", "fused") and self.compute_dtype != self.param_dtype
-                and (self.mesh.shard.size > 1 or self.mesh.replicate.size > 1) and self.mesh.tp.size == 1):
+                and (self.mesh.shard.size > 1 or self.mesh.replicate.size > 1)):
             from .symm import SymmContext, symm_available
 
             use_symm = symm_available(dev)

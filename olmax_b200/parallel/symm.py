@@ -54,10 +54,11 @@ def symm_available(device: torch.device) -> bool:
 
 class PeerBarrier:
     """
-    Stream-ordered barrier over the GPUs ``ranks`` (global ranks).  Default: a one-element NCCL all-reduce on ``pg``.
-    ``OLMAX_B200_BARRIER=flags``: peer-mapped flag words (``ob_peer_barrier``), a single small kernel per member
-    instead of a collective (measured equal in step time: the cost of a barrier is the skew between ranks, not its
-    latency).  Every wait of the flag barrier is bounded
+    Stream-ordered barrier over the GPUs ``ranks`` (global ranks).  Default: peer-mapped flag words
+    (``ob_peer_barrier``), one small kernel per member that publishes an epoch in every member's flag array and waits
+    for all of them, so the peer-memory path issues no library collective between its phases.
+    ``OLMAX_B200_BARRIER=nccl``: a one-element NCCL all-reduce on ``pg`` instead (measured equal in step time: the cost
+    of a barrier is the skew between ranks, not its latency).  Every wait of the flag barrier is bounded
     (``OLMAX_B200_BARRIER_TIMEOUT_S``, default 600 s, the order of NCCL's own watchdog: ranks may legitimately be far
     apart, e.g. while one of them writes a checkpoint): a member that never arrives makes the others record an error
     that ``ops._lib.check_status`` raises, the GPUs stay usable.  Construction is collective over the whole job.
@@ -67,7 +68,7 @@ class PeerBarrier:
         import torch.distributed._symmetric_memory as symm_mem
 
         self.n, self.me, self.pg = len(ranks), my_index, pg
-        self.use_flags = os.environ.get("OLMAX_B200_BARRIER", "nccl") == "flags" and self.n <= 64
+        self.use_flags = os.environ.get("OLMAX_B200_BARRIER", "flags") == "flags" and self.n <= 64
         self.timeout_s = float(os.environ.get("OLMAX_B200_BARRIER_TIMEOUT_S", "600"))
         self.epoch = 0
         self._token = torch.zeros(1, dtype=torch.float32, device=device)

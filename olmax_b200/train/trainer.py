@@ -99,6 +99,7 @@ class Trainer:
         self._step_this_run = 0
         self._epoch = 1
         self._metrics: "OrderedDict[int, Dict[str, Any]]" = OrderedDict()
+        self._kernel_status: Dict[int, Any] = {}   # step -> pending copy of the kernels' status words
         self._canceled = False
         self._canceled_synced = False
         self._cancel_reason: Optional[str] = None
@@ -209,7 +210,30 @@ class Trainer:
             return float(value.item())
         return float(value)
 
+    def _record_kernel_status(self) -> None:
+        """Queue a copy of the kernel library's status words behind this step's work.  A kernel whose bounded wait ran
+        out (operands that never arrived from a peer, a barrier a peer never reached) tears down and returns, so the
+        step itself completes; the words are the only trace, and a step that produced them has computed garbage."""
+        from ..ops import _lib
+
+        self._kernel_status[self._step] = _lib.snapshot_status(self._model.store.device)
+
+    def _check_kernel_status(self, exclude_current: bool = True) -> None:
+        """Raise :class:`~olmax_b200.ops._lib.KernelError` for the oldest recorded step whose status words show a
+        failure: one step late (no synchronisation), and always before a checkpoint of a later step is written."""
+        from ..ops import _lib
+
+        for step in sorted(self._kernel_status):
+            if exclude_current and step == self._step:
+                continue
+            snap = self._kernel_status.pop(step)
+            try:
+                _lib.resolve_status(snap)
+            except _lib.KernelError as e:
+                raise _lib.KernelError(f"step {step}: {e}") from None
+
     def _log_metrics(self, exclude_current: bool = True) -> None:
+        self._check_kernel_status(exclude_current)
         for step in list(self._metrics):
             if exclude_current and step == self._step:
                 continue
@@ -380,6 +404,7 @@ class Trainer:
             with _nvtx("train_batch"):
                 loss = self.train_batch(batch)
             self.record_metric(TrainMetrics.loss, loss)
+            self._record_kernel_status()
             self.record_metric(TrainMetrics.lr, self._optimizer.last_lr)
             if self._optimizer.grad_norm is not None:
                 self.record_metric(TrainMetrics.g_norm, self._optimizer.grad_norm)
@@ -477,6 +502,8 @@ class Trainer:
         state = self._get_state()
         if torch.cuda.is_available():
             torch.cuda.synchronize()
+        # nothing is written from a state that a failed kernel may have corrupted (this step's words included)
+        self._check_kernel_status(exclude_current=False)
         if block:
             self.checkpointer.save(path, state, overwrite=self.save_overwrite)
             for cb in self._iter_callbacks():

@@ -188,6 +188,28 @@ def test_nan_loss_is_reported(tmp_path):
         _trainer(tmp_path, 3).fit(model, _loader())
 
 
+def test_kernel_status_word_stops_training_before_a_checkpoint_is_written(tmp_path):
+    """A kernel whose bounded wait ran out only leaves its status words behind.  Injected on the host: the words are
+    set after step 2; fit() must raise at the next step and must not write the checkpoint due at step 3."""
+    from olmax_b200.ops import _lib
+
+    @dataclass
+    class GiveUp(Callback):
+        def pre_step(self):
+            if self.step == 2:
+                _lib.status_buffer(torch.device("cpu")).copy_(torch.tensor([2, 110, 7, 3005], dtype=torch.int32))
+
+    trainer = _trainer(tmp_path, 6, callbacks=OrderedDict(g=GiveUp()), checkpoint_interval=3)
+    try:
+        with pytest.raises(_lib.KernelError, match="step 2: kernel reported 'peer flag wait timed out' at site 110"):
+            trainer.fit(_model(), _loader())
+    finally:
+        _lib.status_buffer(torch.device("cpu")).zero_()
+    assert trainer.step == 3
+    saved = sorted(p.parent.name for p in tmp_path.rglob("_CHECKPOINT_METADATA"))
+    assert saved == ["step0"], saved   # the initial checkpoint only: nothing from a step at or after the failure
+
+
 def test_sigterm_cancels_gracefully_and_checkpoints(tmp_path):
     @dataclass
     class Killer(Callback):

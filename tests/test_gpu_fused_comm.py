@@ -265,6 +265,8 @@ def _tp_worker(mesh_kind, backend="nccl"):
     model = cfg.build(seed=5, mesh_resource=res, device=dev, comm_backend=backend)
     mesh = model.mesh
     assert (model.store.tp_symm is not None) == (backend == "fused" and mesh.tp.size > 1)
+    # the FSDP axis of a mesh that also has a TP axis runs on the peer-memory backend too
+    assert (model.store.symm_ag is not None) == (backend == "fused" and mesh.shard.size > 1)
     optim = AdamWConfig(lr=ConstantSchedule(1e-3)).build(model, 1)
     gen = torch.Generator().manual_seed(7)
     cache = model.get_buffer_cache(256, dev)
