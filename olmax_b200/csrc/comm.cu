@@ -124,13 +124,20 @@ __global__ void __launch_bounds__(AR_THREADS)
 // earlier kernels stored into peer memory is visible to a GPU that sees the flag), then waits until all n words of its
 // own array show `epoch` -- with a time limit, after which it records ERR_PEER_TIMEOUT and returns, so a missing peer
 // costs `timeout_ns` and an exception on the host, never a hung GPU.
+//
+// The two halves can also be launched on their own (`phases`: 1 = publish, 2 = wait, 3 = both): a member publishes when
+// its stores are done and waits later, right before it needs the others' stores, so that the skew between the GPUs is
+// absorbed by the work in between instead of being paid at every barrier.
 __global__ void peer_barrier_kernel(unsigned* const* __restrict__ flags, int me, int n, unsigned epoch,
-                                    long long timeout_ns, int* status) {
+                                    long long timeout_ns, int* status, int phases) {
   const int t = (int)threadIdx.x;
   if (t >= n) return;
-  __threadfence_system();
-  unsigned* remote = flags[t] + me;
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  if (phases & 1) {
+    __threadfence_system();
+    unsigned* remote = flags[t] + me;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  }
+  if (!(phases & 2)) return;
   const unsigned* own = flags[me] + t;
   long long t0;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
@@ -200,7 +207,25 @@ extern "C" int ob_peer_barrier(unsigned* const* flags, int me, int n, unsigned e
   if (n <= 1) return 0;
   if (n > 64 || me < 0 || me >= n) OB_FAIL(-7, "barrier: rank %d / group of %d not supported (max 64)", me, n);
   if (timeout_ns <= 0) timeout_ns = 30LL * 1000 * 1000 * 1000;
-  peer_barrier_kernel<<<1, 64, 0, stream>>>(flags, me, n, epoch, timeout_ns, status);
+  peer_barrier_kernel<<<1, 64, 0, stream>>>(flags, me, n, epoch, timeout_ns, status, 3);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_peer_signal(unsigned* const* flags, int me, int n, unsigned epoch, cudaStream_t stream) {
+  if (n <= 1) return 0;
+  if (n > 64 || me < 0 || me >= n) OB_FAIL(-7, "barrier: rank %d / group of %d not supported (max 64)", me, n);
+  peer_barrier_kernel<<<1, 64, 0, stream>>>(flags, me, n, epoch, 0, nullptr, 1);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_peer_wait(unsigned* const* flags, int me, int n, unsigned epoch, long long timeout_ns, int* status,
+                            cudaStream_t stream) {
+  if (n <= 1) return 0;
+  if (n > 64 || me < 0 || me >= n) OB_FAIL(-7, "barrier: rank %d / group of %d not supported (max 64)", me, n);
+  if (timeout_ns <= 0) timeout_ns = 30LL * 1000 * 1000 * 1000;
+  peer_barrier_kernel<<<1, 64, 0, stream>>>(flags, me, n, epoch, timeout_ns, status, 2);
   OB_CUDA_OK(cudaGetLastError());
   return 0;
 }

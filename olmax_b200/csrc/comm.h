@@ -23,6 +23,12 @@ int ob_reduce_slots_f32(const float* stage, float* acc, long long n, int R, long
 // all others within timeout_ns (<= 0: 30 s) writes ERR_PEER_TIMEOUT (site 500) to status and returns.
 int ob_peer_barrier(unsigned* const* flags, int me, int n, unsigned epoch, long long timeout_ns, int* status,
                     cudaStream_t stream);
+// The two halves of the barrier as separate launches, for members that publish an epoch when their stores are done
+// and wait for the others' epoch only later (the same epoch sequence as ob_peer_barrier: every publish, whether from
+// ob_peer_barrier or ob_peer_signal, takes the next number; a wait passes once every member's word is >= its epoch).
+int ob_peer_signal(unsigned* const* flags, int me, int n, unsigned epoch, cudaStream_t stream);
+int ob_peer_wait(unsigned* const* flags, int me, int n, unsigned epoch, long long timeout_ns, int* status,
+                 cudaStream_t stream);
 // dst = src (bytes, 16-byte multiples); either side may be peer memory.  blocks <= 0: 4 per SM; unroll 4 / 8 / 16 = 16-byte
 // loads in flight per thread (matters when src is remote).
 int ob_copy_bytes(void* dst, const void* src, long long bytes, int blocks, int unroll, cudaStream_t stream);

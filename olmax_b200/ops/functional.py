@@ -756,6 +756,10 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
                         _gemm_wgrad(dl, xc, handle)
             if single_wgrad:
                 _gemm_wgrad(dlogits, x2, handle)
+                # This weight gradient is staged during the FORWARD pass.  Its unit (the head, or the embedding for a
+                # tied head) is folded now rather than in backward order, so that no layer's weight gradients can land
+                # in the same staging buffer before it has been folded.
+                handle.store.reduce_unit_now(handle.unit)
             loss = stats[0] * inv[0]
             zl = stats[1] * inv[0] * z_loss
             ctx.save_for_backward(dx if need_grad else torch.empty(0))

@@ -26,7 +26,7 @@ __all__ = [
     "gemm", "flash_attn_fwd", "flash_attn_bwd", "rmsnorm_fwd", "rmsnorm_bwd", "rope", "glu_fwd", "glu_bwd",
     "embed_gather", "embed_scatter", "ce_fwd_bwd", "count_valid", "adamw", "sumsq", "clip_coef", "cast_f32_bf16",
     "layernorm_fwd", "layernorm_bwd", "gather_shards", "scatter_add_shards", "allreduce_p2p", "allreduce_multimem",
-    "peer_barrier", "copy_bytes", "push_copy", "fold_slots_bf16", "reduce_slots",
+    "peer_barrier", "peer_signal", "peer_wait", "copy_bytes", "push_copy", "fold_slots_bf16", "reduce_slots",
     "launch_count", "reset_launch_count", "pointer_table",
     "timing_enabled", "set_timing", "timed_region", "timing_report", "format_timing",
 ]
@@ -71,6 +71,8 @@ register_signature("ob_sumsq", [_vp, _ll, _vp, _vp])
 register_signature("ob_clip_coef", [_vp, _f, _f, _vp, _vp])
 register_signature("ob_cast_f32_bf16", [_vp, _vp, _ll, _vp])
 register_signature("ob_peer_barrier", [_vp, _i, _i, ctypes.c_uint, _ll, _vp, _vp])
+register_signature("ob_peer_signal", [_vp, _i, _i, ctypes.c_uint, _vp])
+register_signature("ob_peer_wait", [_vp, _i, _i, ctypes.c_uint, _ll, _vp, _vp])
 register_signature("ob_copy_bytes", [_vp, _vp, _ll, _i, _i, _vp])
 register_signature("ob_push_copy", [_vp, _vp, _ll, _i, _i, _i, _vp])
 register_signature("ob_fold_slots_bf16", [_vp, _vp, _ll, _i, _ll, _i, _i, _vp])
@@ -378,6 +380,20 @@ def peer_barrier(table, me: int, n: int, epoch: int, timeout_s: float = 0.0) -> 
     _count()
 
 
+def peer_signal(table, me: int, n: int, epoch: int) -> None:
+    """First half of :func:`peer_barrier`: publish ``epoch`` to every member (after a system-scope fence)."""
+    check(lib().ob_peer_signal(table.data_ptr(), me, n, epoch & 0xFFFFFFFF, stream_ptr(table.device)), "peer_signal")
+    _count()
+
+
+def peer_wait(table, me: int, n: int, epoch: int, timeout_s: float = 0.0) -> None:
+    """Second half of :func:`peer_barrier`: wait (bounded) until every member has published ``epoch`` or a later one."""
+    dev = table.device
+    check(lib().ob_peer_wait(table.data_ptr(), me, n, epoch & 0xFFFFFFFF, int(timeout_s * 1e9),
+                             status_buffer(dev).data_ptr(), stream_ptr(dev)), "peer_wait")
+    _count()
+
+
 def copy_bytes(dst_ptr: int, src_ptr: int, nbytes: int, device, blocks: int = 0, unroll: int = 8) -> None:
     """Raw copy between two addresses (either may be peer memory) with our copy kernel."""
     check(lib().ob_copy_bytes(dst_ptr, src_ptr, nbytes, blocks, unroll, stream_ptr(device)), "copy_bytes")
@@ -496,5 +512,5 @@ def format_timing(report: dict, top: int = 40) -> str:
 for _name in ("gemm", "flash_attn_fwd", "flash_attn_bwd", "rmsnorm_fwd", "rmsnorm_bwd", "layernorm_fwd", "layernorm_bwd",
               "rope", "glu_fwd", "glu_bwd", "embed_gather", "embed_scatter", "ce_fwd_bwd", "count_valid", "adamw", "sumsq",
               "clip_coef", "cast_f32_bf16", "gather_shards", "scatter_add_shards", "allreduce_p2p", "allreduce_multimem",
-              "copy_bytes", "push_copy", "fold_slots_bf16", "reduce_slots", "peer_barrier"):
+              "copy_bytes", "push_copy", "fold_slots_bf16", "reduce_slots", "peer_barrier", "peer_signal", "peer_wait"):
     globals()[_name] = _timed(_name, globals()[_name])

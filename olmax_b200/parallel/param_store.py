@@ -253,8 +253,7 @@ class FSDPUnit:
             # peer-memory backend: every rank's weight-gradient GEMMs have stored their contributions into the owners'
             # staging slots; after a barrier each owner folds its slots into its accumulator
             names, self._staged = self._staged, set()
-            st.sync_peers()
-            st.symm.fold_stage(self, names)
+            st.symm.rs_unit_done(self, names)
             st.stats["reduce_scatter_bytes"] += (st.mesh.shard.size - 1) * self.numel_local * 4
         if self._full_grad is None:
             return
@@ -548,6 +547,13 @@ class ParamStore:
         return (self.symm_ag.unit_pointer_table(u), buf.data_ptr(), buf.stride(0) * es, off, nbytes,
                 self.mesh.shard.size, self.mesh.shard.rank)
 
+    def reduce_unit_now(self, unit: FSDPUnit) -> None:
+        """Reduce-scatter ``unit``'s weight gradients and fold them into the accumulator without deferring the fold
+        (used for gradients produced outside the backward order of the units)."""
+        unit.reduce_grads()
+        if self.symm_rs is not None:
+            self.symm_rs.rs_flush()
+
     def invalidate_gathered(self) -> None:
         for u in self.units:
             u.release()
@@ -559,6 +565,8 @@ class ParamStore:
         for u in self.units:
             if u._full_grad is not None or u._staged:
                 u.reduce_grads()
+        if self.symm_rs is not None:
+            self.symm_rs.rs_flush()
         if self.reshard_after_forward and self.mesh.shard.size > 1:
             for u in self.units:
                 u.release()

@@ -89,8 +89,26 @@ class PeerBarrier:
         self.epoch += 1
         K.peer_barrier(self._table, self.me, self.n, self.epoch, self.timeout_s)
 
+    # Split-phase use: ``token = arrive()`` when this rank's stores are done, ``wait(token)`` right before the others'
+    # stores are needed; the skew between the ranks is then absorbed by whatever runs in between.
+    def arrive(self):
+        if self.n <= 1:
+            return None
+        if not self.use_flags:
+            dist.all_reduce(self._token, group=self.pg)   # a collective cannot be split: the whole barrier happens here
+            return None
+        self.epoch += 1
+        K.peer_signal(self._table, self.me, self.n, self.epoch)
+        return self.epoch
+
+    def wait(self, token) -> None:
+        if token is not None:
+            K.peer_wait(self._table, self.me, self.n, token, self.timeout_s)
+
 
 class SymmContext:
+    N_STAGE = 3   # reduce-scatter staging buffers in rotation
+
     def __init__(self, store, numel: int):
         import torch.distributed._symmetric_memory as symm_mem
 
@@ -117,17 +135,22 @@ class SymmContext:
         use_mc = os.environ.get("OLMAX_B200_MULTIMEM", "1") == "1"
         self.multicast_ptr = mc if (use_mc and mesh.replicate.size == mesh.world_size) else 0
         # Reduce-scatter staging: every weight-gradient GEMM STORES (plain stores, no atomics) the row block owned by
-        # GPU r into slot `me` of r's staging buffer; after a barrier r folds its R slots into its accumulator.  Two
-        # buffers alternate between consecutive FSDP units.
+        # GPU r into slot `me` of r's staging buffer; r folds its R slots into its accumulator once every member has
+        # published that its stores of that unit are done.  The fold of unit u is deferred to the moment unit u-1 (the
+        # next one in backward order) has been computed: [wgrads(u-1)] -> wait(u) -> fold(u) -> publish(u-1), so the
+        # wait finds the others' epoch already there unless they lag by more than a whole unit.  Three buffers rotate
+        # (index % 3): a buffer is written again for unit u-3 only after this rank has passed wait(u-1), and a member
+        # publishes (u-1) only after its fold(u), the previous user of that buffer.
         self.stage_slot = max((u.numel_local for u in store.units), default=0)
         self.rs_stage = None
         self.stage_ptrs: List[int] = []
         if self.R > 1 and os.environ.get("OLMAX_B200_FUSED_RS", "1") == "1":
-            self.rs_stage = symm_mem.empty(2 * self.R * self.stage_slot, dtype=torch.float32, device=dev)
+            self.rs_stage = symm_mem.empty(self.N_STAGE * self.R * self.stage_slot, dtype=torch.float32, device=dev)
             self._h_stage = symm_mem.rendezvous(self.rs_stage, world)
             all_stage = [int(p) for p in self._h_stage.buffer_ptrs]
             self.stage_ptrs = [all_stage[r] for r in mesh.shard.ranks]
         self.flags = torch.zeros(max(1, self.R) * 4096, dtype=torch.int32, device=dev)
+        self._rs_pending = None   # (unit, names, barrier token) of the unit whose fold is still to come
         self._tables: Dict[tuple, torch.Tensor] = {}
         self._token = torch.zeros(1, dtype=torch.float32, device=dev)
         self._sync_group = world if mesh.replicate.size > 1 else mesh.shard.pg
@@ -155,7 +178,7 @@ class SymmContext:
     def stage_pointer_table(self, handle) -> torch.Tensor:
         """Device array: for every owner GPU r, the address inside r's staging buffer where THIS rank's contribution
         to the row shard r of ``handle``'s gradient goes (buffer chosen by the parity of the unit index)."""
-        buf = handle.unit.index & 1
+        buf = handle.unit.index % self.N_STAGE
         key = ("stage", handle.name, buf)
         t = self._tables.get(key)
         if t is None:
@@ -167,7 +190,7 @@ class SymmContext:
     def fold_stage(self, unit, names) -> None:
         """accumulator += grad_scale * sum over the R slots of the unit's staging buffer, for the parameters in
         ``names`` (those whose weight gradient was stored this pass; other regions of the slots hold stale data)."""
-        buf = unit.index & 1
+        buf = unit.index % self.N_STAGE
         base = buf * self.R * self.stage_slot
         for h in unit.params:
             if h.name not in names:
@@ -176,6 +199,24 @@ class SymmContext:
             stage = self.rs_stage[base + m.unit_offset:]
             acc = self.grad[m.offset : m.offset + m.numel_local]
             K.reduce_slots(stage, acc, m.numel_local, self.R, self.stage_slot, self.store.grad_scale)
+
+    def rs_unit_done(self, unit, names) -> None:
+        """This rank has launched every weight-gradient GEMM of ``unit`` (their epilogues store into the owners'
+        staging slots).  Folds the PREVIOUS unit's slots (waiting, normally without delay, for the members' epoch of
+        that unit) and then publishes this unit's epoch; this unit is folded at the next call or by :meth:`rs_flush`."""
+        self._fold_pending()
+        self._rs_pending = (unit, names, self._barrier.arrive())
+
+    def _fold_pending(self) -> None:
+        if self._rs_pending is not None:
+            unit, names, token = self._rs_pending
+            self._rs_pending = None
+            self._barrier.wait(token)
+            self.fold_stage(unit, names)
+
+    def rs_flush(self) -> None:
+        """Fold whatever is still staged (end of a backward pass)."""
+        self._fold_pending()
 
     def shadow_pointer_table(self, handle) -> torch.Tensor:
         return self._table("shadow", handle, self.shadow_ptrs, self.shadow.element_size())

@@ -321,6 +321,21 @@ def test_fused_tensor_parallel_matches_nccl_tensor_parallel(world):
             assert rel_err(pf[name], pn[name]) < 1e-2, name
 
 
+def test_fused_fsdp_with_tied_embeddings_matches_nccl():
+    """A tied LM head stages its weight gradient under the embedding unit during the forward pass; the peer-memory
+    reduce-scatter has to fold it before any layer's gradients reuse that staging buffer."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    fused = run_distributed_test(_tp_worker, world_size=2, backend="nccl", func_args=("fsdp", "fused"), timeout=300)
+    nccl = run_distributed_test(_tp_worker, world_size=2, backend="nccl", func_args=("fsdp", "nccl"), timeout=300)
+    for r in range(2):
+        lf, pf = fused[r]
+        ln, pn = nccl[r]
+        assert all(abs(a - b) < 2e-2 * abs(b) for a, b in zip(lf, ln)), (lf, ln)
+        for name in pn:
+            assert rel_err(pf[name], pn[name]) < 1e-2, name
+
+
 @pytest.mark.parametrize("strategy", ["all_gather", "ring"])
 def test_context_parallel_matches_fsdp_on_two_gpus(strategy):
     """Sequences split over 2 GPUs (dual-chunk-swap order; K/V all-gathered or travelling around the ring; the
