@@ -11,6 +11,8 @@ device with CUDA events (max over ranks) with the step's inputs already resident
 metric through the public ``Trainer.train_batch`` call, where every step copies its token ids and labels from pinned
 host memory and reads the loss back to the host.  ``--impl reference`` would run the reference's own code from
 ``baseline/_ref``; it needs JAX, which this image does not have, so it prints the ``unavailable`` line.
+``--impl torchlib`` runs the same model and step built from PyTorch's library kernels and NCCL (``baseline/torchlib.py``),
+a same-box comparison that is not the reference.
 """
 
 from __future__ import annotations
@@ -168,7 +170,9 @@ def main() -> int:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torchlib"],
+                    help="ours: this repository; reference: the unmodified reference from baseline/_ref; torchlib: the same "
+                         "model and step from PyTorch's own library kernels and NCCL (baseline/torchlib.py)")
     ap.add_argument("--recipe", default="olmo2_7B_bench")
     ap.add_argument("--mesh", default="FSDP", choices=["FSDP", "HSDP", "DDP", "FSDP_with_TP", "FSDP_with_CP", "HSDP_with_CP"])
     ap.add_argument("--shard-degree", type=int, default=None)
@@ -189,6 +193,13 @@ def main() -> int:
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.impl == "torchlib":
+        import importlib.util
+
+        spec = importlib.util.spec_from_file_location("olmax_b200_torchlib_arm", ROOT / "baseline" / "torchlib.py")
+        arm = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(arm)
+        return arm.run(args, ClockSampler, PUBLISHED_TPS_PER_GPU.get(args.recipe))
 
     import torch
     import torch.distributed as dist
