@@ -1,3 +1,4 @@
+from . import ocdbt, orbax_layout
 from .utils import (
     AsyncSaveHandle,
     get_metadata,

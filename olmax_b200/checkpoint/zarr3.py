@@ -105,7 +105,7 @@ def write_metadata(array_dir: Path, shape: Sequence[int], chunk_shape: Sequence[
         "node_type": "array",
         "shape": [int(s) for s in shape],
         "data_type": TORCH_TO_ZARR[dtype],
-        "chunk_grid": {"name": "regular", "configuration": {"chunk_shape": [int(s) for s in chunk_shape] or [1]}},
+        "chunk_grid": {"name": "regular", "configuration": {"chunk_shape": [int(s) for s in chunk_shape]}},
         "chunk_key_encoding": {"name": "default", "configuration": {"separator": "/"}},
         "fill_value": 0,
         "codecs": [{"name": "bytes", "configuration": {"endian": "little"}}, {"name": "crc32c"}],

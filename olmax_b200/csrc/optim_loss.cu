@@ -42,7 +42,10 @@ __global__ void __launch_bounds__(CE_THREADS)
   const long long row = blockIdx.x;
   const float* lrow = logits + row * ld;
   const long long label = labels[row];
-  const bool valid = label != (long long)ignore_index && label >= 0 && label < V;
+  // `counted` rows enter the mean and the z-loss; only rows whose label is a real class have a cross-entropy term (the
+  // one-hot of an out-of-range class is all zero: `olmax/nn/functional.py:94-121` of the reference)
+  const bool counted = label != (long long)ignore_index;
+  const bool in_range = counted && label >= 0 && label < V;
   const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
   const int nvec = V / 4;
   MaxSum acc{-INFINITY, 0.f};
@@ -82,18 +85,19 @@ __global__ void __launch_bounds__(CE_THREADS)
   const float lse = total.m + __logf(total.s);
   if (threadIdx.x == 0) {
     if (lse_out != nullptr) lse_out[row] = lse;
-    if (valid) {
+    if (in_range) {
       float tl = lrow[label];
       if (softcap > 0.f) tl = softcap * tanh_fast(tl * inv_cap);
       atomicAdd(&stats[0], lse - tl);
-      atomicAdd(&stats[1], lse * lse);
     }
+    if (counted) atomicAdd(&stats[1], lse * lse);
   }
   if (dlogits == nullptr) return;
   bf16* drow = dlogits + row * ld_d;
   // d/dz of [ (lse - z_label) + z_loss * lse^2 ] / count  = softmax * (1 + 2 z_loss lse) - onehot, all / count
-  const float gs = valid ? grad_scale * (*inv_count) : 0.f;
-  const float sm_scale = gs * (1.f + 2.f * z_loss * lse);
+  const float gs = in_range ? grad_scale * (*inv_count) : 0.f;
+  const float gz = counted ? grad_scale * (*inv_count) * 2.f * z_loss * lse : 0.f;
+  const float sm_scale = gs + gz;
   const int nvec8 = V / 8;
   for (int i = threadIdx.x; i < nvec8; i += CE_THREADS) {
     const float4 a = *reinterpret_cast<const float4*>(lrow + i * 8);

@@ -422,6 +422,7 @@ class Trainer:
                 gc.collect()
             for cb in self._iter_callbacks():
                 cb.post_step()
+            self._poll_checkpoint()
             now = time.perf_counter()
             self._record_throughput(now - last_time, batch)
             last_time = now
@@ -469,6 +470,13 @@ class Trainer:
             if wait:
                 self._log_metrics(exclude_current=False)
                 self._maybe_wait_for_checkpoint()
+            elif self._save_handle is not None and dist_utils.get_world_size() == 1:
+                # error path of a single-process run: a save that was in flight is still completed and finalized
+                # (with several ranks the finalization needs barriers the failing job can no longer promise)
+                try:
+                    self._maybe_wait_for_checkpoint()
+                except Exception:  # pragma: no cover
+                    log.exception("finalizing the in-flight checkpoint failed")
         finally:
             for cb in self._iter_callbacks():
                 try:
@@ -479,6 +487,18 @@ class Trainer:
             dist_utils.barrier("shutdown")
 
     # ------------------------------------------------------------------ checkpoints
+    def _poll_checkpoint(self) -> None:
+        """Finalize an asynchronous save as soon as every rank's writer thread has finished (agreed over the host
+        control group, one small gather per step while a save is in flight) instead of at the next save: the
+        checkpoint becomes visible to ``_find_latest_checkpoint`` within a step of being written."""
+        if self._save_handle is None:
+            return
+        done = bool(self._save_handle.done())
+        if dist_utils.get_world_size() > 1:
+            done = all(dist_utils.allgather_value(done))
+        if done:
+            self._maybe_wait_for_checkpoint()
+
     def _maybe_wait_for_checkpoint(self) -> None:
         if self._save_handle is not None:
             handle, self._save_handle = self._save_handle, None

@@ -362,6 +362,8 @@ def test_cross_entropy_kernel(K, softcap, z):
     logits = (torch.randn(rows, V, device=dev) * 3).contiguous()
     labels = torch.randint(0, V, (rows,), device=dev)
     labels[::7] = -100
+    labels[3::11] = V   # out of range but not ignored (the sequential synthetic data produces these): counted in the mean
+                        # and in the z-loss, no cross-entropy term
     lf = logits.clone().requires_grad_(True)
     loss, zl = ref.fused_cross_entropy(lf, labels, z_loss_multiplier=z, logit_softcap=softcap)
     (gl,) = torch.autograd.grad(loss + zl, lf)
@@ -373,6 +375,7 @@ def test_cross_entropy_kernel(K, softcap, z):
     K.ce_fwd_bwd(logits, labels, dl, stats, inv, V=V, softcap=softcap, z_loss=z)
     got = stats[0] * inv[0]
     assert abs(got.item() - loss.item()) < 2e-3 * max(1.0, abs(loss.item()))
+    assert abs((stats[1] * inv[0] * z).item() - zl.item()) < 2e-3 * max(1e-6, abs(zl.item()))
     assert rel_err(dl, gl) < 8e-3
     _check_status()
 

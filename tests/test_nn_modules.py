@@ -279,3 +279,21 @@ def test_gated_mlp_selective_recomputation_keeps_only_its_input():
         assert torch.allclose(a, b, atol=1e-6)
     with torch.no_grad():      # nothing to recompute without a backward pass
         assert F.gated_mlp(x, *w, "silu", recompute=True).shape == (7, 16)
+
+
+def test_cross_entropy_counts_out_of_range_labels_in_mean_and_z_loss():
+    """A label outside [0, V) that is not ``ignore_index`` (the sequential synthetic data yields label == V) has no
+    cross-entropy term but stays in the mean and in the z-loss, as in the reference's ``fused_cross_entropy_loss``
+    (``src/olmax/nn/functional.py:94-121``: the one-hot vanishes, ``log_normalizer * where`` does not)."""
+    from olmax_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    logits = torch.randn(6, 10)
+    labels = torch.tensor([1, 10, -100, 3, 10, 9])
+    loss, z = ref.fused_cross_entropy(logits, labels, z_loss_multiplier=0.1)
+    lse = torch.logsumexp(logits, -1)
+    has_ce = torch.tensor([1.0, 0, 0, 1, 0, 1])
+    counted = torch.tensor([1.0, 1, 0, 1, 1, 1])
+    want_loss = ((lse - logits[torch.arange(6), labels.clamp(0, 9)]) * has_ce).sum() / counted.sum()
+    want_z = 0.1 * (lse.pow(2) * counted).sum() / counted.sum()
+    assert torch.allclose(loss, want_loss) and torch.allclose(z, want_z)
