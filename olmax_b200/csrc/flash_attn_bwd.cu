@@ -79,13 +79,13 @@ __global__ void __launch_bounds__(THREADS, 1)
   uint64_t* empty = bars + 3;      // [STAGES]
   uint64_t* s_full = bars + 5;
   uint64_t* dp_full = bars + 6;
-  uint64_t* p_ready = bars + 7;    // 128 arrivals
+  uint64_t* p_ready = bars + 7;    // 8 arrivals (one per compute warp)
   uint64_t* pv_done = bars + 8;
-  uint64_t* ds_ready = bars + 9;   // 128 arrivals
+  uint64_t* ds_ready = bars + 9;   // 8 arrivals
   uint64_t* dq_full = bars + 10;
-  uint64_t* dq_read = bars + 11;   // 128 arrivals
+  uint64_t* dq_read = bars + 11;   // 8 arrivals
   uint64_t* all_done = bars + 12;
-  uint64_t* dq_staged = bars + 13; // 256 arrivals: the fp32 dQ partial tile is in shared memory
+  uint64_t* dq_staged = bars + 13; // 8 arrivals: the fp32 dQ partial tile is in shared memory
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -116,13 +116,13 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(p_ready, 256);
+    mbar_init(p_ready, 8);     // one arrival per compute warp (lane 0, after the warp has synchronised)
     mbar_init(pv_done, 1);
-    mbar_init(ds_ready, 256);
+    mbar_init(ds_ready, 8);
     mbar_init(dq_full, 1);
-    mbar_init(dq_read, 256);
+    mbar_init(dq_read, 8);
     mbar_init(all_done, 1);
-    mbar_init(dq_staged, 256);
+    mbar_init(dq_staged, 8);
     *abort_flag = 0;
     mbar_fence_init();
     fence_proxy_async();
@@ -303,15 +303,34 @@ __global__ void __launch_bounds__(THREADS, 1)
     const float LOG2E = 1.4426950408889634f;
     const bool capped = p.softcap > 0.f;
     bool ok = true;
+    // Row statistics (log-sum-exp, delta) of the NEXT iteration's query row are fetched one iteration ahead: the loads
+    // (global memory, hundreds of cycles) then complete under the current iteration's work instead of stalling the
+    // exponentials right after S arrives.
+    int hq = 0, iq = 0;          // query head within the group / query tile within [i_lo, i_hi] of iteration `it`
+    float lse2_next = INFINITY, dl_next = 0.f;
+    auto fetch_stats = [&](int hq_, int iq_) {
+      const int q_idx_ = (i_lo + iq_) * T + row;
+      if (q_idx_ < p.S) {
+        const long long idx = ((long long)b * p.H + (hkv * G + hq_)) * p.S + q_idx_;
+        lse2_next = p.lse[idx] * LOG2E;
+        dl_next = p.delta[idx];
+      } else {
+        lse2_next = INFINITY;
+        dl_next = 0.f;
+      }
+    };
+    if (n_iters > 0) fetch_stats(0, 0);
     for (int it = 0; it < n_iters && ok; ++it) {
       const uint32_t ph1 = (uint32_t)it & 1u;
-      const int h = hkv * G + it / n_q;
-      const int q0 = (i_lo + it % n_q) * T;
+      const int q0 = (i_lo + iq) * T;
       const int q_idx = q0 + row;
-      const bool q_ok = q_idx < p.S;
-      const long long stat_idx = ((long long)b * p.H + h) * p.S + q_idx;
-      const float lse2 = q_ok ? p.lse[stat_idx] * LOG2E : INFINITY;
-      const float dl = q_ok ? p.delta[stat_idx] : 0.f;
+      const float lse2 = lse2_next;
+      const float dl = dl_next;
+      if (++iq == n_q) {
+        iq = 0;
+        ++hq;
+      }
+      if (it + 1 < n_iters) fetch_stats(hq, iq);
       const int qp0 = p.q_off + q0, q_pos = p.q_off + q_idx;   // positions on the key axis
       const bool need_mask = (kv0 + T > p.Sk) || (p.causal && kv0 + T - 1 > qp0) ||
                              (p.window >= 0 && kv0 < qp0 + T - 1 - p.window);
@@ -352,7 +371,8 @@ __global__ void __launch_bounds__(THREADS, 1)
       for (int ch = 0; ch < 8; ++ch)
         *reinterpret_cast<uint4*>(sP + ((ch ^ sw) << 4)) = make_uint4(pp[ch * 4], pp[ch * 4 + 1], pp[ch * 4 + 2], pp[ch * 4 + 3]);
       fence_proxy_async();
-      mbar_arrive(p_ready);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_ready);
 
       ok = mbar_wait(dp_full, ph1, abort_flag, p.status, 901);
       if (!ok) break;
@@ -390,7 +410,8 @@ __global__ void __launch_bounds__(THREADS, 1)
       for (int ch = 0; ch < 8; ++ch)
         *reinterpret_cast<uint4*>(sP + ((ch ^ sw) << 4)) = make_uint4(ds[ch * 4], ds[ch * 4 + 1], ds[ch * 4 + 2], ds[ch * 4 + 3]);
       fence_proxy_async();
-      mbar_arrive(ds_ready);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_ready);
 
       ok = mbar_wait(dq_full, ph1, abort_flag, p.status, 903);
       if (!ok) break;
@@ -403,9 +424,10 @@ __global__ void __launch_bounds__(THREADS, 1)
         tmem_ld32(t_lane + C_S + (uint32_t)(col0 + 32), r1);
         tmem_ld_wait();
         tc_fence_before_sync();
-        mbar_arrive(dq_read);   // the S / dQ columns may be overwritten by the next S = Q K^T
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dq_read);   // the S / dQ columns may be overwritten by the next S = Q K^T
         // columns [0, 64) go to this iteration's Q stage, [64, 128) to its dO stage (both idle since dq_full)
-        uint8_t* c0p = (half == 0 ? smem + OFF_Q : smem + OFF_DO) + (it % STAGES) * TILE;
+        uint8_t* c0p = (half == 0 ? smem + OFF_Q : smem + OFF_DO) + (it & 1) * TILE;
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
           uint8_t* crow = c0p + cc * 16384 + row * 128;
@@ -415,7 +437,8 @@ __global__ void __launch_bounds__(THREADS, 1)
             *reinterpret_cast<uint4*>(crow + ((j ^ sw) << 4)) = make_uint4(r[j * 4], r[j * 4 + 1], r[j * 4 + 2], r[j * 4 + 3]);
         }
         fence_proxy_async();
-        mbar_arrive(dq_staged);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dq_staged);
       }
     }
     // dK, dV out (thread <-> key row, 64-column half)

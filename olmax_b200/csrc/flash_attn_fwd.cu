@@ -103,7 +103,7 @@ __global__ void __launch_bounds__(THREADS, 2)
     mbar_init(v_full, 1);
     mbar_init(v_empty, 1);
     mbar_init(s_full, 1);
-    mbar_init(p_full, 256);
+    mbar_init(p_full, 8);      // one arrival per softmax warp (lane 0, after the warp has synchronised)
     mbar_init(o_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -280,7 +280,8 @@ __global__ void __launch_bounds__(THREADS, 2)
       l_run += lsum;
       tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(p_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
     }
     // epilogue: wait for the last P V, combine the halves' sums, normalise, store
     if (ok) ok = mbar_wait(o_done, (uint32_t)(n_iters - 1) & 1u, abort_flag, p.status, 601);
