@@ -346,24 +346,34 @@ __global__ void __launch_bounds__(THREADS, 1)
         tmem_ld32(t_lane + C_S + (uint32_t)col0, r0);
         tmem_ld32(t_lane + C_S + (uint32_t)(col0 + 32), r1);
         tmem_ld_wait();
+        // P = exp2(s * scale * log2e - lse2), in place over the loaded scores.  The soft-cap and mask cases are
+        // handled by loops of their own: a branch inside the hot loop would cut it into one basic block per element
+        // pair and expose the FFMA -> EX2 -> pack latency of every pair instead of overlapping the pairs.
+        if (capped) {
 #pragma unroll
-        for (int i = 0; i < 64; i += 2) {
-          float s0 = __uint_as_float(i < 32 ? r0[i] : r1[i - 32]);
-          float s1 = __uint_as_float(i < 32 ? r0[i + 1] : r1[i - 31]);
-          float e0, e1;
-          if (capped) {
-            e0 = fast_exp2(p.cap_log2 * fast_tanh(s0 * p.scale_over_cap) - lse2);
-            e1 = fast_exp2(p.cap_log2 * fast_tanh(s1 * p.scale_over_cap) - lse2);
-          } else {
-            e0 = fast_exp2(fmaf(s0, p.scale_log2, -lse2));
-            e1 = fast_exp2(fmaf(s1, p.scale_log2, -lse2));
+          for (int i = 0; i < 32; ++i) {
+            r0[i] = __float_as_uint(fast_exp2(p.cap_log2 * fast_tanh(__uint_as_float(r0[i]) * p.scale_over_cap) - lse2));
+            r1[i] = __float_as_uint(fast_exp2(p.cap_log2 * fast_tanh(__uint_as_float(r1[i]) * p.scale_over_cap) - lse2));
           }
-          if (need_mask) {
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            r0[i] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(r0[i]), p.scale_log2, -lse2)));
+            r1[i] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(r1[i]), p.scale_log2, -lse2)));
+          }
+        }
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
             const int kv = kv0 + col0 + i;
-            if (kv > kv_hi || kv < kv_lo) e0 = 0.f;
-            if (kv + 1 > kv_hi || kv + 1 < kv_lo) e1 = 0.f;
+            if (kv > kv_hi || kv < kv_lo) r0[i] = 0u;
+            if (kv + 32 > kv_hi || kv + 32 < kv_lo) r1[i] = 0u;
           }
-          pp[i >> 1] = pack_bf16x2(e0, e1);
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          pp[i >> 1] = pack_bf16x2(__uint_as_float(r0[i]), __uint_as_float(r0[i + 1]));
+          pp[16 + (i >> 1)] = pack_bf16x2(__uint_as_float(r1[i]), __uint_as_float(r1[i + 1]));
         }
       }
       // eight 16-byte chunks of this row; the chunk index is XOR-swizzled by row % 8 (128-byte swizzle)
