@@ -307,25 +307,23 @@ __global__ void __launch_bounds__(THREADS, 1)
     // (global memory, hundreds of cycles) then complete under the current iteration's work instead of stalling the
     // exponentials right after S arrives.
     int hq = 0, iq = 0;          // query head within the group / query tile within [i_lo, i_hi] of iteration `it`
-    float lse2_next = INFINITY, dl_next = 0.f;
+    // (only the loads are issued ahead; nothing computes on the loaded values until the next iteration, so that no
+    // instruction of this iteration waits for them)
+    float lse_next = INFINITY, dl_next = 0.f;
     auto fetch_stats = [&](int hq_, int iq_) {
-      const int q_idx_ = (i_lo + iq_) * T + row;
-      if (q_idx_ < p.S) {
-        const long long idx = ((long long)b * p.H + (hkv * G + hq_)) * p.S + q_idx_;
-        lse2_next = p.lse[idx] * LOG2E;
-        dl_next = p.delta[idx];
-      } else {
-        lse2_next = INFINITY;
-        dl_next = 0.f;
-      }
+      const int q_idx_ = min((i_lo + iq_) * T + row, p.S - 1);   // clamped: rows beyond S are masked by q_ok below
+      const long long idx = ((long long)b * p.H + (hkv * G + hq_)) * p.S + q_idx_;
+      lse_next = __ldg(p.lse + idx);
+      dl_next = __ldg(p.delta + idx);
     };
     if (n_iters > 0) fetch_stats(0, 0);
     for (int it = 0; it < n_iters && ok; ++it) {
       const uint32_t ph1 = (uint32_t)it & 1u;
       const int q0 = (i_lo + iq) * T;
       const int q_idx = q0 + row;
-      const float lse2 = lse2_next;
-      const float dl = dl_next;
+      const bool q_ok = q_idx < p.S;
+      const float lse2 = q_ok ? lse_next * LOG2E : INFINITY;
+      const float dl = q_ok ? dl_next : 0.f;
       if (++iq == n_q) {
         iq = 0;
         ++hq;
