@@ -234,9 +234,11 @@ __global__ void __launch_bounds__(THREADS, 2)
           if (kv + 32 > kv_hi || kv + 32 < kv_lo) r1[i] = __float_as_uint(-INFINITY);
         }
       }
-      float mx = -INFINITY;
+      // four independent chains: a single running maximum (or sum, below) would serialise 32 dependent operations
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(r0[i]), __uint_as_float(r1[i])));
+      for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], fmaxf(__uint_as_float(r0[i]), __uint_as_float(r1[i])));
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float sc = capped ? 1.0f : p.scale_log2;   // soft-capped scores are already in the log2 domain
       mx *= sc;                                        // sc > 0: max commutes with the scaling
       xch[half * 128 + row] = mx;
@@ -264,7 +266,7 @@ __global__ void __launch_bounds__(THREADS, 2)
       }
       const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
       // P = exp2(s - m) as bf16 pairs, written over the S columns (both halves hold their scores in registers by now)
-      float lsum = 0.f;
+      float lsum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
         uint32_t pk[16];
@@ -272,12 +274,12 @@ __global__ void __launch_bounds__(THREADS, 2)
         for (int i = 0; i < 32; i += 2) {
           const float s0 = __uint_as_float(hh ? r1[i] : r0[i]), s1 = __uint_as_float(hh ? r1[i + 1] : r0[i + 1]);
           const float e0 = fast_exp2(fmaf(s0, sc, neg_m)), e1 = fast_exp2(fmaf(s1, sc, neg_m));
-          lsum += e0 + e1;
+          lsum4[(i >> 1) & 3] += e0 + e1;
           pk[i >> 1] = pack_bf16x2(e0, e1);
         }
         tmem_st16(t_lane + S_COL + (uint32_t)(half * 32 + hh * 16), pk);
       }
-      l_run += lsum;
+      l_run += (lsum4[0] + lsum4[1]) + (lsum4[2] + lsum4[3]);
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
