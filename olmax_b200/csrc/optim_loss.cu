@@ -136,6 +136,101 @@ __global__ void __launch_bounds__(CE_THREADS)
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Vocabulary-parallel cross entropy: every member of a group holds the logits of ITS slice of the vocabulary
+// ([rows, V_local], global class = vocab_offset + column) for the same rows.
+//   stats kernel: per row (max, sum exp(z - max), target logit if the label falls in this slice else 0) of the local slice;
+//   grad kernel:  reads every member's statistics (plain loads; the buffers may live in peer GPUs' memory), combines
+//                 them into the row's global log-sum-exp and target logit, and writes d(loss)/d(local logits).
+// Rows come from `n_src` sources (the members' own token shards, `rows_per_src` rows each); a row is normalised by the
+// number of counted labels of its source, and a member adds to its loss sums only the rows of its own source.
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(CE_THREADS)
+    ce_vp_stats_kernel(const float* __restrict__ logits, long long ld, const long long* __restrict__ labels,
+                       float* __restrict__ stats, int V, long long vocab_offset, float softcap) {
+  __shared__ MaxSum red[CE_THREADS / 32];
+  const long long row = blockIdx.x;
+  const float* lrow = logits + row * ld;
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+  MaxSum acc{-INFINITY, 0.f};
+  for (int i = threadIdx.x; i < V; i += CE_THREADS) {
+    float x = lrow[i];
+    if (softcap > 0.f) x = softcap * tanh_fast(x * inv_cap);
+    acc = combine(acc, MaxSum{x, 1.f});
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    MaxSum o{__shfl_xor_sync(0xffffffffu, acc.m, off), __shfl_xor_sync(0xffffffffu, acc.s, off)};
+    acc = combine(acc, o);
+  }
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    MaxSum t = red[0];
+    for (int i = 1; i < CE_THREADS / 32; ++i) t = combine(t, red[i]);
+    const long long local = labels[row] - vocab_offset;
+    float tl = 0.f;
+    if (local >= 0 && local < V) {
+      tl = lrow[local];
+      if (softcap > 0.f) tl = softcap * tanh_fast(tl * inv_cap);
+    }
+    float4 out = make_float4(t.m, t.s, tl, 0.f);
+    *reinterpret_cast<float4*>(stats + row * 4) = out;
+  }
+}
+
+__global__ void __launch_bounds__(CE_THREADS)
+    ce_vp_grad_kernel(const float* __restrict__ logits, long long ld, const long long* __restrict__ labels,
+                      bf16* __restrict__ dlogits, long long ld_d, const float* const* __restrict__ peer_stats, int n_peers,
+                      const float* __restrict__ inv_counts, long long rows_per_src, long long row0, int my_src,
+                      float* __restrict__ loss_sums, int V, long long vocab_offset, long long V_total, int ignore_index,
+                      float softcap, float z_loss, float grad_scale) {
+  __shared__ float sh[3];
+  const long long row = blockIdx.x;
+  const float* lrow = logits + row * ld;
+  const long long label = labels[row];
+  const bool counted = label != (long long)ignore_index;
+  const bool in_range = counted && label >= 0 && label < V_total;
+  if (threadIdx.x == 0) {
+    float m = -INFINITY;
+    for (int r = 0; r < n_peers; ++r) m = fmaxf(m, peer_stats[r][row * 4]);
+    float ssum = 0.f, t = 0.f;
+    for (int r = 0; r < n_peers; ++r) {
+      const float4 st = *reinterpret_cast<const float4*>(peer_stats[r] + row * 4);
+      ssum += st.y * __expf(st.x - m);
+      t += st.z;
+    }
+    const float lse = m + __logf(ssum);
+    const int src = (int)((row0 + row) / rows_per_src);
+    sh[0] = lse;
+    sh[1] = inv_counts[src];
+    if (src == my_src) {
+      if (in_range) atomicAdd(&loss_sums[0], lse - t);
+      if (counted) atomicAdd(&loss_sums[1], lse * lse);
+    }
+  }
+  __syncthreads();
+  if (dlogits == nullptr) return;
+  const float lse = sh[0];
+  const float gs = in_range ? grad_scale * sh[1] : 0.f;
+  const float gz = counted ? grad_scale * sh[1] * 2.f * z_loss * lse : 0.f;
+  const float sm_scale = gs + gz;
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+  const long long local_label = label - vocab_offset;
+  bf16* drow = dlogits + row * ld_d;
+  for (int i = threadIdx.x; i < V; i += CE_THREADS) {
+    float x = lrow[i], dcap = 1.f;
+    if (softcap > 0.f) {
+      const float t = tanh_fast(x * inv_cap);
+      x = softcap * t;
+      dcap = 1.f - t * t;
+    }
+    float g = __expf(x - lse) * sm_scale;
+    if ((long long)i == local_label) g -= gs;
+    drow[i] = __float2bfloat16(g * dcap);
+  }
+}
+
 // out[0] = 1 / max(1, #labels != ignore_index), out[1] = that count
 __global__ void count_valid_kernel(const long long* __restrict__ labels, long long n, int ignore_index, int V,
                                    float* __restrict__ out, int* __restrict__ counter) {
@@ -279,6 +374,30 @@ extern "C" int ob_ce_fwd_bwd(const float* logits, long long ld, const long long*
 extern "C" int ob_count_valid(const long long* labels, long long n, int ignore_index, int V, float* out, int* counter,
                               cudaStream_t stream) {
   count_valid_kernel<<<blocks_for(n, 256, 2), 256, 0, stream>>>(labels, n, ignore_index, V, out, counter);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_ce_vp_stats(const float* logits, long long ld, const long long* labels, float* stats, long long rows,
+                              int V, long long vocab_offset, float softcap, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (reinterpret_cast<uintptr_t>(stats) & 15) OB_FAIL(-3, "vocab-parallel statistics need a 16-byte aligned buffer");
+  ce_vp_stats_kernel<<<(unsigned)rows, CE_THREADS, 0, stream>>>(logits, ld, labels, stats, V, vocab_offset, softcap);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_ce_vp_grad(const float* logits, long long ld, const long long* labels, void* dlogits, long long ld_d,
+                             const float* const* peer_stats, int n_peers, const float* inv_counts, long long rows_per_src,
+                             long long row0, int my_src, float* loss_sums, long long rows, int V, long long vocab_offset,
+                             long long V_total, int ignore_index, float softcap, float z_loss, float grad_scale,
+                             cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (n_peers < 1 || rows_per_src <= 0) OB_FAIL(-3, "vocab-parallel loss: bad group description");
+  ce_vp_grad_kernel<<<(unsigned)rows, CE_THREADS, 0, stream>>>(logits, ld, labels, reinterpret_cast<bf16*>(dlogits), ld_d,
+                                                              peer_stats, n_peers, inv_counts, rows_per_src, row0, my_src,
+                                                              loss_sums, V, vocab_offset, V_total, ignore_index, softcap,
+                                                              z_loss, grad_scale);
   OB_CUDA_OK(cudaGetLastError());
   return 0;
 }

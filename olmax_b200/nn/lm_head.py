@@ -11,8 +11,11 @@ from typing import Optional, Tuple
 
 import torch
 
+from ..exceptions import OLMaxConfigurationError
 from ..ops import functional as F
 from ..ops import reference as ref
+from ..parallel import collectives as coll
+from ..parallel.mesh import TPStyle
 from .linear import Linear
 from .module import Module, current_build_context
 
@@ -21,16 +24,21 @@ __all__ = ["LMHead", "LMHeadConfig"]
 
 class LMHead(Module):
     def __init__(self, d_model: int, vocab_size: int, bias: bool = False, tied_weight=None,
-                 logit_softcap: Optional[float] = None, init_std: float = 0.02):
+                 logit_softcap: Optional[float] = None, init_std: float = 0.02, vocab_parallel: bool = False):
         super().__init__()
         if bias:
             raise ValueError("LMHead bias is not supported by the fused loss")
         self.vocab_size = vocab_size
         self.logit_softcap = logit_softcap
         self.proj: Optional[Linear] = None
+        # vocabulary parallelism: the head's rows (classes) are split over the tensor-parallel group
+        self.vocab_parallel = bool(vocab_parallel) and self.mesh.tp.size > 1
+        if self.vocab_parallel and tied_weight is not None:
+            raise OLMaxConfigurationError("a vocabulary-parallel LM head cannot share the (unsplit) embedding matrix")
         if tied_weight is None:
             with current_build_context().scope("proj"):
-                self.proj = Linear(d_model, vocab_size, init_std=init_std)
+                self.proj = Linear(d_model, vocab_size, init_std=init_std,
+                                   tp_style=TPStyle.colwise if self.vocab_parallel else None)
             self._weight = self.proj.weight
         else:
             self._weight = tied_weight
@@ -40,11 +48,23 @@ class LMHead(Module):
         return self._weight
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        logits = F.linear(x, self._weight).float()
+        if self.vocab_parallel:
+            # every member computes its vocabulary slice for the gathered rows; the slices are concatenated and each
+            # member keeps the logits of its own rows
+            tp = self.mesh.tp
+            rows = x.shape[0]
+            part = F.linear(coll.all_gather(x.contiguous(), tp, dim=0), self._weight).float()
+            logits = coll.all_gather(part.contiguous(), tp, dim=1)[tp.rank * rows : (tp.rank + 1) * rows]
+        else:
+            logits = F.linear(x, self._weight).float()
         return ref.softcap(logits, self.logit_softcap or 0.0)
 
     def loss(self, x: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100, z_loss_multiplier: float = 0.0,
              chunk_rows: int = 2048) -> Tuple[torch.Tensor, torch.Tensor]:
+        if self.vocab_parallel:
+            tpc = self.store.tp_symm if x.is_cuda else None
+            return F.vocab_parallel_linear_cross_entropy(x, self._weight, labels, self.mesh.tp, tpc, ignore_index,
+                                                         self.logit_softcap or 0.0, z_loss_multiplier, chunk_rows)
         return F.linear_cross_entropy(x, self._weight, labels, ignore_index, self.logit_softcap or 0.0,
                                       z_loss_multiplier, chunk_rows)
 
@@ -53,6 +73,9 @@ class LMHead(Module):
 class LMHeadConfig:
     bias: bool = False
     logit_softcap: Optional[float] = None
+    vocab_parallel: bool = False
+    """Split the head's vocabulary over the tensor-parallel axis and compute the loss from the members' slices
+    (``ops/functional.py: vocab_parallel_linear_cross_entropy``); no effect on a mesh without a TP axis."""
 
     def build(self, d_model: int, vocab_size: int, tied_weight=None, init_std: float = 0.02) -> LMHead:
-        return LMHead(d_model, vocab_size, self.bias, tied_weight, self.logit_softcap, init_std)
+        return LMHead(d_model, vocab_size, self.bias, tied_weight, self.logit_softcap, init_std, self.vocab_parallel)

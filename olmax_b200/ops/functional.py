@@ -16,8 +16,10 @@ import math
 from typing import Optional, Tuple
 
 import torch
+import torch.distributed as dist
 
 from . import kernels as K
+from ..parallel import collectives as coll
 from . import reference as ref
 
 __all__ = [
@@ -791,6 +793,129 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
         (dx,) = ctx.saved_tensors
         # dloss is 1 for loss.backward(); the weight gradient was already accumulated under that assumption
         return dx.view(ctx.shape) * dloss.to(dx.dtype), None, None, None, None, None, None
+
+
+class _VocabParallelLinearCrossEntropyFn(torch.autograd.Function):
+    """
+    LM head + cross entropy with the VOCABULARY split over a tensor-parallel group (north-star "fused vocab-parallel
+    cross-entropy"; replaces ``olmax/nn/lm_head.py:59-61`` + ``olmax/nn/functional.py:94-121``).  Every member owns
+    ``V / n`` rows of the head weight.  ``x`` holds this member's rows of the sequence-parallel activation; the rows
+    of all members are gathered, each member computes the logits of ITS vocabulary slice for all of them (a chunk of
+    rows at a time), the per-row softmax statistics of the slices (max, sum-exp, target logit) are exchanged and
+    combined (on the GPU: written to peer-mapped buffers, one bounded flag barrier, then every member's gradient
+    kernel reads all members' statistics with plain loads), and the input gradient leaves through a reduce-scatter
+    over the group.  No member ever holds logits or logit gradients for more than ``chunk_rows x V / n`` entries and
+    the head's weight gradient needs no reduction over the group.  A row is normalised by the number of counted labels
+    of the member it came from, so every member reports the mean loss of its own tokens, as without vocabulary
+    parallelism.  Like :class:`_LinearCrossEntropyFn` the weight gradient is accumulated in forward (unit upstream
+    gradient assumed).
+    """
+
+    @staticmethod
+    def forward(ctx, x, handle, labels, ignore_index, softcap, z_loss, chunk_rows, group, tpc):
+        shp = x.shape
+        d = shp[-1]
+        x2 = x.reshape(-1, d).contiguous()
+        lab = labels.reshape(-1).contiguous()
+        n, me = group.size, group.rank
+        M_l = x2.shape[0]
+        M = n * M_l
+        V_l = handle.tp_shape[0]
+        V, voff = V_l * n, me * V_l
+        need_grad = bool(ctx.needs_input_grad[0])
+        dev = x.device
+        counts = (lab != ignore_index).sum().to(torch.float32).clamp(min=1).view(1)
+        inv_counts = 1.0 / coll.all_gather(counts, group, dim=0)              # [n]
+        x_full = coll.all_gather(x2, group, dim=0)                            # [M, d]
+        lab_full = coll.all_gather(lab, group, dim=0)                         # [M]
+        rc = min(chunk_rows, M)
+        dx_full = torch.empty((M, d), dtype=x2.dtype, device=dev) if need_grad else None
+        if _on_gpu(x):
+            loss_sums = torch.zeros(2, dtype=torch.float32, device=dev)
+            logits = torch.empty((rc, V_l), dtype=torch.float32, device=dev)
+            single_wgrad = need_grad and getattr(handle.store, "symm_rs", None) is not None and handle.shard_count > 1
+            dlogits = torch.empty((M if single_wgrad else rc, V_l), dtype=torch.bfloat16, device=dev) if need_grad else None
+            for ci, r0 in enumerate(range(0, M, rc)):
+                r1 = min(M, r0 + rc)
+                rows = r1 - r0
+                xc = x_full[r0:r1]
+                _gemm_fwd(xc, handle, out=logits[:rows], epi=K.EPI_F32)
+                if tpc is not None:
+                    stats, table = tpc.stats_buffer(rc * 4, ci)
+                    K.ce_vp_stats(logits[:rows], lab_full[r0:r1], stats, V=V_l, vocab_offset=voff, softcap=softcap)
+                    tpc.barrier()    # every member's statistics of this chunk are in its buffer
+                else:
+                    mine = torch.empty(rc * 4, dtype=torch.float32, device=dev)
+                    K.ce_vp_stats(logits[:rows], lab_full[r0:r1], mine, V=V_l, vocab_offset=voff, softcap=softcap)
+                    gathered = coll.all_gather(mine.view(1, -1), group, dim=0)          # [n, rc * 4]
+                    table = K.pointer_table([gathered[r].data_ptr() for r in range(n)], dev)
+                dl = (dlogits[r0:r1] if single_wgrad else dlogits[:rows]) if need_grad else None
+                K.ce_vp_grad(logits[:rows], lab_full[r0:r1], dl, table, n, inv_counts, loss_sums, V=V_l, vocab_offset=voff,
+                             V_total=V, rows_per_src=M_l, row0=r0, my_src=me, ignore_index=ignore_index, softcap=softcap,
+                             z_loss=z_loss)
+                if need_grad:
+                    _gemm_dgrad(dl, handle, out=dx_full[r0:r1])
+                    if not single_wgrad:
+                        _gemm_wgrad(dl, xc, handle)
+            if single_wgrad:
+                _gemm_wgrad(dlogits, x_full, handle)
+                handle.store.reduce_unit_now(handle.unit)
+            loss = loss_sums[0] * inv_counts[me]
+            zl = loss_sums[1] * inv_counts[me] * z_loss
+        else:
+            w = handle.full().float()                                          # [V_l, d]
+            z = ref.softcap(x_full.float() @ w.t(), softcap)                    # [M, V_l]
+            m = z.max(dim=-1).values
+            mg = m.clone()
+            dist.all_reduce(mg, op=dist.ReduceOp.MAX, group=group.pg)
+            ssum = (z - mg[:, None]).exp().sum(-1)
+            local = lab_full - voff
+            here = (local >= 0) & (local < V_l)
+            t = torch.where(here, z.gather(1, local.clamp(0, V_l - 1)[:, None])[:, 0], torch.zeros_like(m))
+            packed = torch.stack([ssum, t])
+            dist.all_reduce(packed, group=group.pg)
+            lse = mg + packed[0].log()
+            counted = lab_full != ignore_index
+            in_range = counted & (lab_full >= 0) & (lab_full < V)
+            src = torch.arange(M, device=dev) // M_l
+            w_row = inv_counts[src]
+            mine = src == me
+            loss = (torch.where(in_range & mine, lse - packed[1], torch.zeros_like(lse))).sum() * inv_counts[me]
+            zl = torch.where(counted & mine, lse.pow(2), torch.zeros_like(lse)).sum() * inv_counts[me] * z_loss
+            if need_grad:
+                gs = torch.where(in_range, w_row, torch.zeros_like(w_row))
+                gz = torch.where(counted, w_row * 2.0 * z_loss * lse, torch.zeros_like(w_row))
+                g = (z - lse[:, None]).exp() * (gs + gz)[:, None]
+                onehot_rows = here & in_range
+                g[onehot_rows, local[onehot_rows]] -= gs[onehot_rows]
+                if softcap:
+                    raw = x_full.float() @ w.t()
+                    g = g * (1.0 - torch.tanh(raw / softcap).pow(2))
+                dx_full = (g @ w).to(x2.dtype)
+                handle.add_grad(g.t() @ x_full.float())
+        if need_grad:
+            dx_local = coll.reduce_scatter(dx_full.contiguous(), group, dim=0)
+            ctx.save_for_backward(dx_local)
+        else:
+            ctx.save_for_backward(torch.empty(0))
+        ctx.shape = shp
+        zl = zl.detach()
+        ctx.mark_non_differentiable(zl)
+        return (loss + zl if z_loss else loss).detach(), zl
+
+    @staticmethod
+    def backward(ctx, dloss, _dz):
+        (dx,) = ctx.saved_tensors
+        return dx.view(ctx.shape) * dloss.to(dx.dtype), None, None, None, None, None, None, None, None
+
+
+def vocab_parallel_linear_cross_entropy(x: torch.Tensor, handle, labels: torch.Tensor, group, tpc=None,
+                                        ignore_index: int = -100, logit_softcap: float = 0.0,
+                                        z_loss_multiplier: float = 0.0, chunk_rows: int = 2048):
+    """(loss, z_loss) with the head weight ``handle`` split over ``group`` along the vocabulary (``tp_dim = 0``); ``x`` and
+    ``labels`` are this member's rows of the sequence-parallel batch.  ``tpc``: the group's ``TPSymmContext`` (GPU)."""
+    return _VocabParallelLinearCrossEntropyFn.apply(x, handle, labels, ignore_index, float(logit_softcap or 0.0),
+                                                    float(z_loss_multiplier or 0.0), int(chunk_rows), group, tpc)
 
 
 def linear_cross_entropy(x: torch.Tensor, handle, labels: torch.Tensor, ignore_index: int = -100,

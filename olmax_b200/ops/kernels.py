@@ -24,7 +24,7 @@ from ._lib import KernelError, ObAttnArgs, ObGemmArgs, check, lib, register_sign
 __all__ = [
     "EPI_BF16", "EPI_F32", "EPI_F32_ACC", "EPI_F32_RED", "EPI_SWIGLU", "EPI_GEGLU", "EPI_BF16_ACC",
     "gemm", "flash_attn_fwd", "flash_attn_bwd", "rmsnorm_fwd", "rmsnorm_bwd", "rope", "glu_fwd", "glu_bwd",
-    "embed_gather", "embed_scatter", "ce_fwd_bwd", "count_valid", "adamw", "sumsq", "clip_coef", "cast_f32_bf16",
+    "embed_gather", "embed_scatter", "ce_fwd_bwd", "ce_vp_stats", "ce_vp_grad", "count_valid", "adamw", "sumsq", "clip_coef", "cast_f32_bf16",
     "layernorm_fwd", "layernorm_bwd", "gather_shards", "scatter_add_shards", "allreduce_p2p", "allreduce_multimem",
     "peer_barrier", "peer_signal", "peer_wait", "copy_bytes", "push_copy", "fold_slots_bf16", "reduce_slots",
     "launch_count", "reset_launch_count", "pointer_table",
@@ -65,6 +65,8 @@ register_signature("ob_glu_bwd", [_vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _vp])
 register_signature("ob_embed_gather", [_vp, _vp, _i, _i, _vp, _ll, _i, _f, _vp])
 register_signature("ob_embed_scatter", [_vp, _vp, _i, _i, _vp, _ll, _i, _f, _vp])
 register_signature("ob_ce_fwd_bwd", [_vp, _ll, _vp, _vp, _ll, _vp, _vp, _vp, _ll, _i, _i, _f, _f, _f, _vp])
+register_signature("ob_ce_vp_stats", [_vp, _ll, _vp, _vp, _ll, _i, _ll, _f, _vp])
+register_signature("ob_ce_vp_grad", [_vp, _ll, _vp, _vp, _ll, _vp, _i, _vp, _ll, _ll, _i, _vp, _ll, _i, _ll, _ll, _i, _f, _f, _f, _vp])
 register_signature("ob_count_valid", [_vp, _ll, _i, _i, _vp, _vp, _vp])
 register_signature("ob_adamw", [_vp, _vp, _vp, _vp, _vp, _ll, _f, _f, _f, _f, _f, _f, _f, _vp, _i, _vp])
 register_signature("ob_sumsq", [_vp, _ll, _vp, _vp])
@@ -317,6 +319,24 @@ def ce_fwd_bwd(logits, labels, dlogits, stats, inv_count, *, V, ignore_index=-10
     _count()
 
 
+def ce_vp_stats(logits, labels, stats, *, V, vocab_offset, softcap=0.0) -> None:
+    """Per-row (max, sum exp, target logit) of this rank's vocabulary slice ``logits [rows, V]`` -> ``stats [rows, 4]``."""
+    check(lib().ob_ce_vp_stats(logits.data_ptr(), logits.stride(0), labels.data_ptr(), stats.data_ptr(), logits.shape[0], V,
+                               vocab_offset, softcap, stream_ptr(logits.device)), "ce_vp_stats")
+    _count()
+
+
+def ce_vp_grad(logits, labels, dlogits, peer_stats, n_peers, inv_counts, loss_sums, *, V, vocab_offset, V_total,
+               rows_per_src, row0, my_src, ignore_index=-100, softcap=0.0, z_loss=0.0, grad_scale=1.0) -> None:
+    """Combine the members' statistics (``peer_stats``: device pointer table) and write the gradient of the local logits."""
+    check(lib().ob_ce_vp_grad(logits.data_ptr(), logits.stride(0), labels.data_ptr(), _ptr(dlogits),
+                              dlogits.stride(0) if dlogits is not None else 0, peer_stats.data_ptr(), n_peers,
+                              inv_counts.data_ptr(), rows_per_src, row0, my_src, loss_sums.data_ptr(), logits.shape[0], V,
+                              vocab_offset, V_total, ignore_index, softcap, z_loss, grad_scale, stream_ptr(logits.device)),
+          "ce_vp_grad")
+    _count()
+
+
 def count_valid(labels, ignore_index, V, out, counter) -> None:
     check(lib().ob_count_valid(labels.data_ptr(), labels.numel(), ignore_index, V, out.data_ptr(), counter.data_ptr(),
                                stream_ptr(labels.device)), "count_valid")
@@ -510,7 +530,8 @@ def format_timing(report: dict, top: int = 40) -> str:
 
 
 for _name in ("gemm", "flash_attn_fwd", "flash_attn_bwd", "rmsnorm_fwd", "rmsnorm_bwd", "layernorm_fwd", "layernorm_bwd",
-              "rope", "glu_fwd", "glu_bwd", "embed_gather", "embed_scatter", "ce_fwd_bwd", "count_valid", "adamw", "sumsq",
+              "rope", "glu_fwd", "glu_bwd", "embed_gather", "embed_scatter", "ce_fwd_bwd", "ce_vp_stats", "ce_vp_grad", "count_valid",
+              "adamw", "sumsq",
               "clip_coef", "cast_f32_bf16", "gather_shards", "scatter_add_shards", "allreduce_p2p", "allreduce_multimem",
               "copy_bytes", "push_copy", "fold_slots_bf16", "reduce_slots", "peer_barrier", "peer_signal", "peer_wait"):
     globals()[_name] = _timed(_name, globals()[_name])

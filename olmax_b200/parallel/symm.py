@@ -71,6 +71,7 @@ class PeerBarrier:
         self.use_flags = os.environ.get("OLMAX_B200_BARRIER", "flags") == "flags" and self.n <= 64
         self.timeout_s = float(os.environ.get("OLMAX_B200_BARRIER_TIMEOUT_S", "600"))
         self.epoch = 0
+        self._last_waited = 0   # newest epoch this rank has waited for (debug check)
         self._token = torch.zeros(1, dtype=torch.float32, device=device)
         self._flags = symm_mem.empty(64, dtype=torch.int32, device=device)
         self._flags.zero_()
@@ -87,6 +88,7 @@ class PeerBarrier:
             dist.all_reduce(self._token, group=self.pg)
             return
         self.epoch += 1
+        self._last_waited = self.epoch
         K.peer_barrier(self._table, self.me, self.n, self.epoch, self.timeout_s)
 
     # Split-phase use: ``token = arrive()`` when this rank's stores are done, ``wait(token)`` right before the others'
@@ -103,11 +105,30 @@ class PeerBarrier:
 
     def wait(self, token) -> None:
         if token is not None:
+            self._last_waited = max(self._last_waited, token)
             K.peer_wait(self._table, self.me, self.n, token, self.timeout_s)
+
+    def check_flags(self) -> None:
+        """Debug check (synchronises): after this rank's last barrier / wait every member's word in this rank's flag
+        array must be the current epoch or one of the few a member may have published since (members run at most a
+        handful of publishes ahead), never an older or a far newer one: a word outside that window means a member
+        skipped a barrier, ran one twice, or a stray store hit the array."""
+        if self.n <= 1 or not self.use_flags:
+            return
+        torch.cuda.synchronize(self._flags.device)
+        words = self._flags[: self.n].tolist()
+        for r, w in enumerate(words):
+            if not (self._last_waited <= w <= self.epoch + 8):
+                raise RuntimeError(f"barrier flag of member {r} is {w}; this rank last waited for {self._last_waited} and has "
+                                   f"published {self.epoch}")
+        if any(self._flags[self.n:].tolist()):
+            raise RuntimeError("words of the flag array beyond the group size were written")
 
 
 class SymmContext:
     N_STAGE = 3   # reduce-scatter staging buffers in rotation
+    GUARD = 256   # guard words (fp32) on either side of the staging area
+    CANARY = -7.25e22
 
     def __init__(self, store, numel: int):
         import torch.distributed._symmetric_memory as symm_mem
@@ -145,9 +166,14 @@ class SymmContext:
         self.rs_stage = None
         self.stage_ptrs: List[int] = []
         if self.R > 1 and os.environ.get("OLMAX_B200_FUSED_RS", "1") == "1":
-            self.rs_stage = symm_mem.empty(self.N_STAGE * self.R * self.stage_slot, dtype=torch.float32, device=dev)
-            self._h_stage = symm_mem.rendezvous(self.rs_stage, world)
-            all_stage = [int(p) for p in self._h_stage.buffer_ptrs]
+            # guard words before and after the staging area: peers only ever store inside it (check_canaries)
+            n_stage = self.N_STAGE * self.R * self.stage_slot
+            self._stage_alloc = symm_mem.empty(n_stage + 2 * self.GUARD, dtype=torch.float32, device=dev)
+            self._stage_alloc[: self.GUARD] = self.CANARY
+            self._stage_alloc[self.GUARD + n_stage:] = self.CANARY
+            self.rs_stage = self._stage_alloc[self.GUARD : self.GUARD + n_stage]
+            self._h_stage = symm_mem.rendezvous(self._stage_alloc, world)
+            all_stage = [int(p) + self.GUARD * 4 for p in self._h_stage.buffer_ptrs]
             self.stage_ptrs = [all_stage[r] for r in mesh.shard.ranks]
         self.flags = torch.zeros(max(1, self.R) * 4096, dtype=torch.int32, device=dev)
         self._rs_pending = None   # (unit, names, barrier token) of the unit whose fold is still to come
@@ -199,6 +225,17 @@ class SymmContext:
             stage = self.rs_stage[base + m.unit_offset:]
             acc = self.grad[m.offset : m.offset + m.numel_local]
             K.reduce_slots(stage, acc, m.numel_local, self.R, self.stage_slot, self.store.grad_scale)
+
+    def check_canaries(self) -> None:
+        """Debug check (synchronises): the guard words around this rank's reduce-scatter staging area are intact, i.e.
+        no peer's weight-gradient epilogue stored outside the slots it owns; also checks the barrier's flag words."""
+        torch.cuda.synchronize(self.store.device)
+        if self.rs_stage is not None:
+            g = self.GUARD
+            lo, hi = self._stage_alloc[:g], self._stage_alloc[-g:]
+            if not (bool((lo == self.CANARY).all()) and bool((hi == self.CANARY).all())):
+                raise RuntimeError("guard words around the reduce-scatter staging buffer were overwritten")
+        self._barrier.check_flags()
 
     def rs_unit_done(self, unit, names) -> None:
         """This rank has launched every weight-gradient GEMM of ``unit`` (their epilogues store into the owners'
@@ -309,6 +346,25 @@ class TPSymmContext:
 
     def barrier(self) -> None:
         self._barrier()
+
+    def stats_buffer(self, numel: int, index: int):
+        """(fp32 tensor of ``numel`` elements in symmetric memory, device table of the group's addresses of that
+        buffer) for small per-row statistics exchanged between the members (vocabulary-parallel cross entropy).  Two
+        buffers alternate with ``index``: a buffer is written again only after a later barrier of the group, which every
+        member passes after the kernel that read the previous contents."""
+        import torch.distributed._symmetric_memory as symm_mem
+
+        key = ("stats", numel)
+        if key not in self._x:
+            pair = []
+            for _ in range(2):
+                t = symm_mem.empty(numel, dtype=torch.float32, device=self.device)
+                t.zero_()
+                h = symm_mem.rendezvous(t, dist.group.WORLD)
+                ptrs = [int(p) for p in h.buffer_ptrs]
+                pair.append((t, K.pointer_table([ptrs[r] for r in self.group.ranks], self.device)))
+            self._x[key] = pair
+        return self._x[key][index & 1]
 
     # ---- all-gather -> GEMM -----------------------------------------------------------------------------------------
     def gather_begin(self, x_local: torch.Tensor):

@@ -11,7 +11,7 @@ from olmax_b200.testing import run_distributed_test
 
 
 def _model(mesh_resource, seed=0, layer="default", tie=False, kv=None, cp_strategy=None, window=None, softcap=None,
-           ac=None):
+           ac=None, vocab_parallel=False, final_softcap=None):
     from olmax_b200.models import (DefaultTransformerConfig, DefaultTransformerLayerConfig, GemmaTransformerLayerConfig,
                                    ReorderedNormTransformerLayerConfig)
     from olmax_b200.nn import MultiheadSelfAttentionConfig, RMSNormConfig
@@ -21,8 +21,11 @@ def _model(mesh_resource, seed=0, layer="default", tie=False, kv=None, cp_strate
     attn = MultiheadSelfAttentionConfig(n_heads=4, n_kv_heads=kv, head_dim=16,
                                         qk_norm=RMSNormConfig() if layer != "default" else None, use_head_qk_norm=True,
                                         cp_strategy=cp_strategy, window_size=window, logit_softcap=softcap)
+    from olmax_b200.nn import LMHeadConfig
+
     cfg = DefaultTransformerConfig(vocab_size=64, d_model=64, hidden_size=96, num_layers=2, layer=layer_cls(attention=attn),
-                                   tie_embeddings=tie, scale_embeddings=tie, ce_chunk_rows=16, layer_ac_policy=_policy(ac))
+                                   tie_embeddings=tie, scale_embeddings=tie, ce_chunk_rows=16, layer_ac_policy=_policy(ac),
+                                   lm_head=LMHeadConfig(vocab_parallel=vocab_parallel, logit_softcap=final_softcap))
     return cfg.build(seed=seed, mesh_resource=mesh_resource)
 
 
@@ -212,6 +215,48 @@ def test_recomputation_repeats_the_collectives_consistently(mesh_kind, ac, cp_st
             assert torch.allclose(g1[n], g0[n], rtol=1e-5, atol=1e-7), n
 
 
+def _vocab_parallel_worker(vocab_parallel, world_kind):
+    import torch.distributed as dist
+
+    from olmax_b200.parallel import MeshResource, dist_utils
+
+    world = dist_utils.get_world_size()
+    res = MeshResource.FSDP_with_TP(2, world)
+    model = _model(res, layer="reordered_norm", kv=2, vocab_parallel=vocab_parallel, final_softcap=30.0)
+    assert model.lm_head.vocab_parallel == vocab_parallel
+    assert model.lm_head.weight.meta.tp_dim == (0 if vocab_parallel else None)
+    mesh = model.mesh
+    ids, labels = _global_batch()
+    labels[1, 3] = 64   # out of range but counted
+    per = ids.shape[0] // mesh.data_parallel_size
+    ids = ids[mesh.data_parallel_rank * per : (mesh.data_parallel_rank + 1) * per]
+    labels = labels[mesh.data_parallel_rank * per : (mesh.data_parallel_rank + 1) * per]
+    model.store.set_grad_scale(1.0 / world)
+    loss, zl = model(ids, labels, z_loss_multiplier=1e-3)
+    loss.backward()
+    model.store.finish_backward()
+    model.store.reduce_replicated_grads()
+    t = loss.detach().clone()
+    dist.all_reduce(t, group=dist_utils.control_group())
+    logits = model(ids)   # the inference path gathers the vocabulary slices
+    return (t / world).item(), {n: model.store.full_gradient(n) for n, _ in model.store.named_parameters()}, logits
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_vocab_parallel_loss_matches_replicated_head(world):
+    """Splitting the LM head's vocabulary over the TP group (every member computes its slice of the logits for the
+    gathered rows; softmax statistics are combined across the members) gives the loss, the z-loss-inclusive gradients
+    and the logits of the head that is replicated over the TP group."""
+    base = run_distributed_test(_vocab_parallel_worker, world_size=world, func_args=(False, "tp"))
+    vp = run_distributed_test(_vocab_parallel_worker, world_size=world, func_args=(True, "tp"))
+    for (l0, g0, z0), (l1, g1, z1) in zip(base, vp):
+        assert l1 == pytest.approx(l0, rel=1e-5)
+        assert set(g0) == set(g1)
+        for n in g0:
+            assert torch.allclose(g1[n], g0[n], rtol=1e-4, atol=1e-7), n
+        assert torch.allclose(z1, z0, rtol=1e-4, atol=1e-5)
+
+
 def _collectives_worker():
     import torch.distributed as dist
 
@@ -293,3 +338,62 @@ def test_hsdp_all_reduces_once_per_optimizer_step():
         want = 2 * (rep - 1) * numel * 4 // rep
         assert all(s["all_reduce_bytes"] == want for s in steps1 + steps2)
         assert all(s2["reduce_scatter_bytes"] == 2 * s1["reduce_scatter_bytes"] for s1, s2 in zip(steps1, steps2))
+
+
+def test_split_phase_barrier_protocol_with_threads_as_peers():
+    """Host model of the reduce-scatter staging protocol of the peer-memory backend, with CPU threads standing in for
+    the GPUs and a shared array for their peer-mapped memory: every member stores its contribution to unit u into the
+    owners' slots of staging buffer u % 3, then waits for the members' epoch of the PREVIOUS unit, folds that unit and
+    only then publishes its epoch for u (publish after fold).  Random delays shuffle the interleavings; every fold must
+    see exactly the contributions of its unit, which fails if a buffer could be rewritten before its owner has folded it."""
+    import random
+    import threading
+    import time
+
+    import numpy as np
+
+    n, units, n_buf, width = 4, 40, 3, 8
+    flags = np.zeros((n, n), dtype=np.int64)              # flags[owner][member] = newest epoch `member` published
+    stage = np.zeros((n, n_buf, n, width))                # stage[owner][buffer][member slot][...]
+    results = [[] for _ in range(n)]
+    errors = []
+
+    def member(me):
+        rng = random.Random(me)
+        pending = None                                    # (unit, epoch) whose fold is still to come
+        epoch = 0
+        try:
+            for u in range(units):
+                time.sleep(rng.random() * 1e-3)
+                for owner in range(n):                    # "weight-gradient epilogue": stores into the owners' slots
+                    stage[owner, u % n_buf, me, :] = 1000 * u + me
+                if pending is not None:
+                    pu, pe = pending
+                    deadline = time.time() + 20
+                    while flags[me].min() < pe:           # bounded wait
+                        if time.time() > deadline:
+                            raise TimeoutError(f"member {me} waiting for epoch {pe}: {flags[me]}")
+                        time.sleep(1e-5)
+                    results[me].append((pu, stage[me, pu % n_buf].sum(axis=0).copy()))
+                epoch += 1
+                for owner in range(n):                    # publish AFTER the fold
+                    flags[owner, me] = epoch
+                pending = (u, epoch)
+            pu, pe = pending
+            while flags[me].min() < pe:
+                time.sleep(1e-5)
+            results[me].append((pu, stage[me, pu % n_buf].sum(axis=0).copy()))
+        except Exception as e:  # noqa: BLE001
+            errors.append(e)
+
+    threads = [threading.Thread(target=member, args=(r,)) for r in range(n)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(60)
+    assert not errors, errors
+    for me in range(n):
+        assert [u for u, _ in results[me]] == list(range(units))
+        for u, total in results[me]:
+            assert np.all(total == n * 1000 * u + sum(range(n))), (me, u, total)
+    assert (flags == units).all()                        # epochs advanced in step on every member

@@ -221,6 +221,8 @@ def _train_worker(backend, mesh_kind="fsdp", barrier="nccl"):
         losses.append(loss.item())
     torch.cuda.synchronize()
     _lib.check_status(dev)
+    if model.store.symm is not None:
+        model.store.symm.check_canaries()   # nobody stored outside its staging slots; barrier epochs are in step
     full = {n: model.store.full_parameter(n).cpu() for n, _ in model.store.named_parameters()}
     return losses, first_grads.cpu(), full
 
@@ -319,6 +321,59 @@ def test_fused_tensor_parallel_matches_nccl_tensor_parallel(world):
         assert all(abs(a - b) < 2e-2 * abs(b) for a, b in zip(lf, ln)), (lf, ln)
         for name in pn:
             assert rel_err(pf[name], pn[name]) < 1e-2, name
+
+
+def _vp_worker(backend, vocab_parallel):
+    from olmax_b200.models import DefaultTransformerConfig, ReorderedNormTransformerLayerConfig
+    from olmax_b200.nn import LMHeadConfig, MultiheadSelfAttentionConfig
+    from olmax_b200.ops import _lib
+    from olmax_b200.optim import AdamWConfig, ConstantSchedule
+    from olmax_b200.parallel import MeshResource, dist_utils
+
+    world, rank = dist_utils.get_world_size(), dist_utils.get_rank()
+    dev = torch.device("cuda", rank)
+    attn = MultiheadSelfAttentionConfig(n_heads=4, n_kv_heads=2, head_dim=128)
+    cfg = DefaultTransformerConfig(vocab_size=4096, d_model=512, hidden_size=1024, num_layers=2,
+                                   layer=ReorderedNormTransformerLayerConfig(attention=attn),
+                                   lm_head=LMHeadConfig(logit_softcap=30.0, vocab_parallel=vocab_parallel), ce_chunk_rows=256)
+    model = cfg.build(seed=5, mesh_resource=MeshResource.FSDP_with_TP(2, world), device=dev, comm_backend=backend)
+    assert model.lm_head.vocab_parallel == vocab_parallel
+    optim = AdamWConfig(lr=ConstantSchedule(1e-3)).build(model, 1)
+    gen = torch.Generator().manual_seed(7)
+    cache = model.get_buffer_cache(256, dev)
+    mesh = model.mesh
+    losses = []
+    for step in range(3):
+        ids = torch.randint(0, 4096, (4, 256), generator=gen)
+        per = 4 // mesh.data_parallel_size
+        mine = ids[mesh.data_parallel_rank * per : (mesh.data_parallel_rank + 1) * per]
+        labels = torch.roll(mine, -1, 1)
+        labels[:, -1] = -100
+        loss, _ = model(mine.to(dev), labels.to(dev), cache, z_loss_multiplier=1e-4)
+        loss.backward()
+        optim.accumulate()
+        optim.step()
+        t = loss.detach().clone()
+        torch.distributed.all_reduce(t)
+        losses.append(t.item() / world)
+    torch.cuda.synchronize()
+    _lib.check_status(dev)
+    return losses, {n: model.store.full_parameter(n).cpu() for n, _ in model.store.named_parameters()}
+
+
+@pytest.mark.parametrize("world,backend", [(2, "fused"), (2, "nccl"), (4, "fused")])
+def test_vocab_parallel_head_trains_like_the_replicated_head(world, backend):
+    """The LM head's vocabulary split over the TP pair (statistics exchanged through peer memory on the fused backend,
+    through NCCL otherwise) trains like the head replicated over the pair."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    vp = run_distributed_test(_vp_worker, world_size=world, backend="nccl", func_args=(backend, True), timeout=300)
+    base = run_distributed_test(_vp_worker, world_size=world, backend="nccl", func_args=("nccl", False), timeout=300)
+    lv, pv = vp[0]
+    lb, pb = base[0]
+    assert all(abs(a - b) < 2e-2 * abs(b) for a, b in zip(lv, lb)), (lv, lb)
+    for name in pb:
+        assert rel_err(pv[name], pb[name]) < 1e-2, name
 
 
 def test_fused_fsdp_with_tied_embeddings_matches_nccl():

@@ -380,6 +380,54 @@ def test_cross_entropy_kernel(K, softcap, z):
     _check_status()
 
 
+@pytest.mark.parametrize("softcap,z", [(0.0, 0.0), (30.0, 1e-3)])
+def test_vocab_parallel_cross_entropy_kernels(K, softcap, z):
+    """Two vocabulary slices of one logits matrix, processed like two members of a group on one GPU: per-slice
+    statistics, then each slice's gradient from both members' statistics, against the unsplit cross entropy."""
+    dev = "cuda"
+    torch.manual_seed(11)
+    rows, V, n = 96, 2 * 1032, 2
+    Vl = V // n
+    logits = (torch.randn(rows, V, device=dev) * 3).contiguous()
+    labels = torch.randint(0, V, (rows,), device=dev)
+    labels[::5] = -100
+    labels[2::9] = V
+    lf = logits.clone().requires_grad_(True)
+    loss, zl = ref.fused_cross_entropy(lf, labels, z_loss_multiplier=z, logit_softcap=softcap)
+    (gl,) = torch.autograd.grad(loss + zl, lf)
+    # rows come from two sources (48 rows each) with their own counts, as under sequence parallelism
+    per = rows // n
+    cnt = torch.stack([(labels[i * per : (i + 1) * per] != -100).sum() for i in range(n)]).float().clamp(min=1)
+    inv = (1.0 / cnt).to(dev)
+    slices = [logits[:, i * Vl : (i + 1) * Vl].contiguous() for i in range(n)]
+    stats = [torch.empty(rows * 4, device=dev) for _ in range(n)]
+    for i in range(n):
+        K.ce_vp_stats(slices[i], labels, stats[i], V=Vl, vocab_offset=i * Vl, softcap=softcap)
+    table = K.pointer_table([t.data_ptr() for t in stats], torch.device(dev))
+    total, ztotal = 0.0, 0.0
+    grads = []
+    for i in range(n):
+        sums = torch.zeros(2, device=dev)
+        dl = torch.empty(rows, Vl, device=dev, dtype=torch.bfloat16)
+        K.ce_vp_grad(slices[i], labels, dl, table, n, inv, sums, V=Vl, vocab_offset=i * Vl, V_total=V, rows_per_src=per,
+                     row0=0, my_src=i, softcap=softcap, z_loss=z)
+        grads.append(dl.float())
+        total += (sums[0] * inv[i]).item() / n          # mean over the two sources of their own mean losses
+        ztotal += (sums[1] * inv[i] * z).item() / n
+    # reference with the same per-source normalisation: mean of the two halves' mean losses
+    halves = [ref.fused_cross_entropy(logits[i * per : (i + 1) * per], labels[i * per : (i + 1) * per],
+                                      z_loss_multiplier=z, logit_softcap=softcap) for i in range(n)]
+    want = sum(h[0].item() for h in halves) / n
+    assert abs(total - want) < 2e-3 * max(1.0, abs(want))
+    assert abs(ztotal - sum(h[1].item() for h in halves) / n) < 2e-3 * max(1e-6, abs(ztotal))
+    lf2 = logits.clone().requires_grad_(True)
+    obj = sum(sum(ref.fused_cross_entropy(lf2[i * per : (i + 1) * per], labels[i * per : (i + 1) * per],
+                                          z_loss_multiplier=z, logit_softcap=softcap)) for i in range(n))
+    (g2,) = torch.autograd.grad(obj, lf2)
+    assert rel_err(torch.cat(grads, dim=1), g2) < 8e-3
+    _check_status()
+
+
 def test_adamw_and_norm_kernels(K):
     dev = "cuda"
     torch.manual_seed(8)
