@@ -90,6 +90,20 @@ class NothingSaveable(ActivationCheckpointingPolicy):
 @ActivationCheckpointingPolicy.register("dots_saveable")
 @dataclass
 class DotsSaveable(ActivationCheckpointingPolicy):
+    """
+    In the reference this policy keeps matrix-product results and recomputes every element-wise result between them.
+    Here no region is wrapped for recomputation under it, and the autograd nodes decide what they keep:
+
+    * recomputed in backward, never stored: the gated activation ``act(gate) * up`` (the gated-MLP node keeps the two
+      projections and forms the product again), attention probabilities (flash attention keeps the log-sum-exp only),
+      logits and their gradients beyond one chunk of rows;
+    * still stored although element-wise: the outputs of the normalisation layers (block-output norms of OLMo2 / Gemma,
+      pre-norm outputs, QK-norm outputs) and the rotated q / k.  For OLMo2-7B at 2 x 4096 tokens per micro-batch that is
+      6 x [tokens, 4096] bf16 per layer = 12.9 GB of the 154 GB peak over 32 layers; a run that needs that memory
+      back uses ``save_anything_except_these_names`` with ``layers.*.attention`` / ``layers.*.mlp`` (sub-block
+      recomputation) or ``nothing_saveable``.
+    """
+
     def should_recompute(self, region_name: str) -> bool:
         return False
 
