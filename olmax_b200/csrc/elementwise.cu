@@ -376,6 +376,169 @@ __global__ void rope_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, co
   }
 }
 
+// q / k normalisation fused with the rotary embedding:  y = rope(bf16(rmsnorm(x) * w)).
+// A row (d elements, the span of one RMS statistic) is d / hd heads of hd elements: d == hd for a head-wise norm,
+// d == n_heads * hd for a norm over the whole projection.  A thread owns PPT "pairs": 8 elements of the first half
+// of a head and the 8 elements of the second half that rotate with them, so the rotation needs no exchange.
+// Position of a row on the table axis: (row / heads) % S.  The normalised value is rounded to bf16 before the
+// rotation, which is what the two separate kernels produce.  Replaces the q_norm / k_norm + rotary sequence of
+// `olmax/nn/attention.py:270-300` for RMS norms.
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16(v)); }
+
+template <int TPR, int PPT>
+__global__ void __launch_bounds__(NORM_THREADS)
+    rmsnorm_rope_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
+                            float* __restrict__ rstd_out, const float* __restrict__ cos_t,
+                            const float* __restrict__ sin_t, long long rows, int d, int hd, int heads, long long ld_x,
+                            long long ld_y, int S, float eps) {
+  __shared__ float red[NORM_THREADS / 32];
+  constexpr int ROWS_PER_BLOCK = NORM_THREADS / TPR;
+  const int sub = threadIdx.x / TPR, tr = threadIdx.x % TPR;
+  const int half = hd / 2, pph = hd / 16, npair = d / 16;
+  for (long long row0 = (long long)blockIdx.x * ROWS_PER_BLOCK; row0 < rows; row0 += (long long)gridDim.x * ROWS_PER_BLOCK) {
+    const long long row = row0 + sub;
+    const bool live = row < rows;
+    const long long ox = live ? row_offset(row, heads, ld_x, d) : 0;
+    const long long oy = live ? row_offset(row, heads, ld_y, d) : 0;
+    const long long pos = live ? (row / heads) % S : 0;
+    float lo[PPT][8], hi[PPT][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < PPT; ++i) {
+      const int pi = tr + i * TPR;
+      if (live && pi < npair) {
+        const int e = (pi / pph) * hd + (pi % pph) * 8;
+        load8(x + ox + e, lo[i]);
+        load8(x + ox + e + half, hi[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += lo[i][j] * lo[i][j] + hi[i][j] * hi[i][j];
+      }
+    }
+    ss = row_sum<TPR>(ss, red);
+    const float rstd = rsqrtf(ss / (float)d + eps);
+    if (live && tr == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+#pragma unroll
+    for (int i = 0; i < PPT; ++i) {
+      const int pi = tr + i * TPR;
+      if (live && pi < npair) {
+        const int c0 = (pi % pph) * 8, e = (pi / pph) * hd + c0;
+        float wl[8], wh[8], c[8], sn[8], olo[8], ohi[8];
+        load8(w + e, wl);
+        load8(w + e + half, wh);
+        load8f(cos_t + pos * half + c0, c);
+        load8f(sin_t + pos * half + c0, sn);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float nl = round_bf16(lo[i][j] * rstd * wl[j]), nh = round_bf16(hi[i][j] * rstd * wh[j]);
+          olo[j] = nl * c[j] - nh * sn[j];
+          ohi[j] = nh * c[j] + nl * sn[j];
+        }
+        store8(y + oy + e, olo);
+        store8(y + oy + e + half, ohi);
+      }
+    }
+  }
+}
+
+// Backward of the fused op: g = bf16(rope^T(dy)), then the RMS-norm backward with g as the incoming gradient.
+template <int TPR, int PPT>
+__global__ void __launch_bounds__(NORM_THREADS, PPT <= 1 ? 4 : 2)
+    rmsnorm_rope_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                            const float* __restrict__ rstd_in, bf16* __restrict__ dx, float* __restrict__ dw,
+                            const float* __restrict__ cos_t, const float* __restrict__ sin_t, long long rows, int d,
+                            int hd, int heads, long long ld_dy, long long ld_x, long long ld_dx, int S,
+                            float dw_scale) {
+  __shared__ float red[NORM_THREADS / 32];
+  extern __shared__ float dw_part[];  // [d] per-block partial of dw
+  constexpr int ROWS_PER_BLOCK = NORM_THREADS / TPR;
+  const int sub = threadIdx.x / TPR, tr = threadIdx.x % TPR;
+  const int half = hd / 2, pph = hd / 16, npair = d / 16;
+  float dwl[PPT][8], dwh[PPT][8];
+#pragma unroll
+  for (int i = 0; i < PPT; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwl[i][j] = dwh[i][j] = 0.f;
+  for (long long row0 = (long long)blockIdx.x * ROWS_PER_BLOCK; row0 < rows; row0 += (long long)gridDim.x * ROWS_PER_BLOCK) {
+    const long long row = row0 + sub;
+    const bool live = row < rows;
+    const long long ody = live ? row_offset(row, heads, ld_dy, d) : 0;
+    const long long ox = live ? row_offset(row, heads, ld_x, d) : 0;
+    const long long odx = live ? row_offset(row, heads, ld_dx, d) : 0;
+    const long long pos = live ? (row / heads) % S : 0;
+    const float rstd = live ? rstd_in[row] : 0.f;
+    float gl[PPT][8], gh[PPT][8], xl[PPT][8], xh[PPT][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < PPT; ++i) {
+      const int pi = tr + i * TPR;
+      if (live && pi < npair) {
+        const int c0 = (pi % pph) * 8, e = (pi / pph) * hd + c0;
+        float dl[8], dh[8], c[8], sn[8], wl[8], wh[8];
+        load8(dy + ody + e, dl);
+        load8(dy + ody + e + half, dh);
+        load8f(cos_t + pos * half + c0, c);
+        load8f(sin_t + pos * half + c0, sn);
+        load8(x + ox + e, xl[i]);
+        load8(x + ox + e + half, xh[i]);
+        load8(w + e, wl);
+        load8(w + e + half, wh);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float a = round_bf16(dl[j] * c[j] + dh[j] * sn[j]);   // transpose of the rotation
+          float b = round_bf16(dh[j] * c[j] - dl[j] * sn[j]);
+          xl[i][j] *= rstd;
+          xh[i][j] *= rstd;
+          dwl[i][j] += a * xl[i][j];
+          dwh[i][j] += b * xh[i][j];
+          a *= wl[j];
+          b *= wh[j];
+          dot += a * xl[i][j] + b * xh[i][j];
+          gl[i][j] = a;
+          gh[i][j] = b;
+        }
+      }
+    }
+    dot = row_sum<TPR>(dot, red) / (float)d;
+#pragma unroll
+    for (int i = 0; i < PPT; ++i) {
+      const int pi = tr + i * TPR;
+      if (live && pi < npair) {
+        const int e = (pi / pph) * hd + (pi % pph) * 8;
+        float ol[8], oh[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          ol[j] = rstd * (gl[i][j] - xl[i][j] * dot);
+          oh[j] = rstd * (gh[i][j] - xh[i][j] * dot);
+        }
+        store8(dx + odx + e, ol);
+        store8(dx + odx + e + half, oh);
+      }
+    }
+  }
+  if (dw == nullptr) return;
+  for (int i = threadIdx.x; i < d; i += NORM_THREADS) dw_part[i] = 0.f;
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < PPT; ++i) {
+    const int pi = tr + i * TPR;
+    if (pi < npair) {
+      const int e = (pi / pph) * hd + (pi % pph) * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (ROWS_PER_BLOCK > 1) {
+          atomicAdd(&dw_part[e + j], dwl[i][j]);
+          atomicAdd(&dw_part[e + half + j], dwh[i][j]);
+        } else {
+          dw_part[e + j] = dwl[i][j];
+          dw_part[e + half + j] = dwh[i][j];
+        }
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < d; i += NORM_THREADS) atomicAdd(dw + i, dw_part[i] * dw_scale);
+}
+
 __device__ __forceinline__ float act_silu(float x) { return x / (1.f + __expf(-x)); }
 __device__ __forceinline__ float act_silu_grad(float x) {
   const float s = 1.f / (1.f + __expf(-x));
@@ -606,6 +769,54 @@ extern "C" int ob_rope(const void* x, void* y, const float* cos_t, const float* 
                                                         ysb, yss, ysh, sign, pos_offset);
   OB_CUDA_OK(cudaGetLastError());
   return 0;
+}
+
+// Thread layout of the fused norm + rotary kernels for a row of d / 16 pairs.
+template <typename F>
+static inline int norm_rope_dispatch(int d, int hd, const char* what, F&& launch) {
+  if (hd % 16 != 0 || hd <= 0 || d % hd != 0) OB_FAIL(-1, "%s: d (%d) must be a multiple of the head dim (%d), itself a multiple of 16", what, d, hd);
+  const int npair = d / 16;
+  if (npair <= 8) launch(NormShape<8, 1>{});
+  else if (npair <= 32) launch(NormShape<32, 1>{});
+  else if (npair <= 64) launch(NormShape<32, 2>{});
+  else if (npair <= 128) launch(NormShape<32, 4>{});
+  else if (npair <= 256) launch(NormShape<NORM_THREADS, 1>{});
+  else if (npair <= 512) launch(NormShape<NORM_THREADS, 2>{});
+  else if (npair <= 1024) launch(NormShape<NORM_THREADS, 4>{});
+  else OB_FAIL(-2, "%s: d (%d) too large (max %d)", what, d, NORM_THREADS * 16 * 4);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_rmsnorm_rope_fwd(const void* x, const void* w, void* y, float* rstd, const float* cos_t,
+                                   const float* sin_t, long long rows, int d, int hd, int heads, long long ld_x,
+                                   long long ld_y, int S, float eps, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (S <= 0) OB_FAIL(-3, "rmsnorm_rope: sequence length must be positive");
+  return norm_rope_dispatch(d, hd, "rmsnorm_rope", [&](auto shape) {
+    using Sh = decltype(shape);
+    const int rpb = NORM_THREADS / Sh::TPR;
+    auto kernel = rmsnorm_rope_fwd_kernel<Sh::TPR, Sh::VPT>;
+    kernel<<<resident_grid(kernel, (rows + rpb - 1) / rpb, 0), NORM_THREADS, 0, stream>>>(
+        (const bf16*)x, (const bf16*)w, (bf16*)y, rstd, cos_t, sin_t, rows, d, hd, heads, ld_x, ld_y, S, eps);
+  });
+}
+
+extern "C" int ob_rmsnorm_rope_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw,
+                                   const float* cos_t, const float* sin_t, long long rows, int d, int hd, int heads,
+                                   long long ld_dy, long long ld_x, long long ld_dx, int S, float dw_scale,
+                                   cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (S <= 0) OB_FAIL(-3, "rmsnorm_rope: sequence length must be positive");
+  const size_t smem = (size_t)d * sizeof(float);
+  return norm_rope_dispatch(d, hd, "rmsnorm_rope", [&](auto shape) {
+    using Sh = decltype(shape);
+    const int rpb = NORM_THREADS / Sh::TPR;
+    auto kernel = rmsnorm_rope_bwd_kernel<Sh::TPR, Sh::VPT>;
+    kernel<<<resident_grid(kernel, (rows + rpb - 1) / rpb, smem), NORM_THREADS, smem, stream>>>(
+        (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (bf16*)dx, dw, cos_t, sin_t, rows, d, hd, heads, ld_dy,
+        ld_x, ld_dx, S, dw_scale);
+  });
 }
 
 extern "C" int ob_glu_fwd(const void* g, const void* u, void* a, long long n, int gelu, cudaStream_t stream) {

@@ -27,6 +27,15 @@ int ob_layernorm_bwd(const void* dy, const void* x, const void* w, const float* 
 int ob_rope(const void* x, void* y, const float* cos_t, const float* sin_t, int B, int S, int H, int D, long long sb,
             long long ss, long long sh, long long ysb, long long yss, long long ysh, float sign, int pos_offset,
             cudaStream_t stream);
+// y = rope(bf16(rmsnorm(x) * w)) in one pass (q / k normalisation followed by the rotary embedding).  A row of d
+// elements is d / hd heads; rows are addressed like ob_rmsnorm_fwd; the table row of a row is (row / heads) % S.
+int ob_rmsnorm_rope_fwd(const void* x, const void* w, void* y, float* rstd, const float* cos_t, const float* sin_t,
+                        long long rows, int d, int hd, int heads, long long ld_x, long long ld_y, int S, float eps,
+                        cudaStream_t stream);
+// backward of the fused op: the rotation's transpose, then the RMS-norm backward; dw (fp32) += dw_scale * ...
+int ob_rmsnorm_rope_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw,
+                        const float* cos_t, const float* sin_t, long long rows, int d, int hd, int heads,
+                        long long ld_dy, long long ld_x, long long ld_dx, int S, float dw_scale, cudaStream_t stream);
 // a = act(g) * u with act = silu (gelu = 0) or tanh-gelu (gelu = 1)
 int ob_glu_fwd(const void* g, const void* u, void* a, long long n, int gelu, cudaStream_t stream);
 int ob_glu_bwd(const void* g, const void* u, const void* da, void* dg, void* du, void* a_out, long long n, int gelu,

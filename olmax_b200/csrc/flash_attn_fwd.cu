@@ -1,12 +1,18 @@
 // Flash-attention forward for sm_100a (head_dim 128, bf16 in/out, fp32 softmax statistics).
 //
-// One CTA handles one 128-row query tile of one (batch, head).  S = Q K^T and O += P V run on tcgen05 tensor
-// cores with accumulators in TMEM: S occupies 128 fp32 columns, O another 128; P (bf16) is written back over the
-// S columns and is consumed from TMEM as the A operand of the second MMA, so P never touches shared memory.
-// The softmax is done by 256 threads, two per query row (TMEM lane == row; the two column halves exchange their row
-// maximum through shared memory, no shuffles).  The running maximum is only raised when it grows by more than 2^8 ("lazy rescale"), which keeps the
-// O correction (a TMEM read-modify-write) off most iterations.  A CTA uses 256 TMEM columns and ~97 KiB of shared
-// memory so that two CTAs share an SM: while one is in its softmax the other one's MMAs keep the tensor cores busy.
+// A persistent CTA (one per SM) takes work items from a counter in global memory.  A work item is a pair of
+// 128-row query tiles of one (batch, head).  S = Q K^T and O += P V run on tcgen05 tensor cores with accumulators in
+// TMEM: each query tile owns 128 fp32 columns for S and 128 for O (512 columns in all); P (bf16) is written back
+// over its S columns and is consumed from TMEM as the A operand of the second MMA, so P never touches shared
+// memory.  Each query tile has its own softmax warpgroup (4 warps, one thread per query row, the whole 128-score
+// row in registers, so no exchange between threads), and the MMA warp interleaves the two tiles:
+//     P V (tile 0, keys j), Q K^T (tile 0, keys j+1), P V (tile 1, keys j), Q K^T (tile 1, keys j+1), ...
+// so that the tensor cores work on one tile while the other tile is in its softmax.  K and V tiles go through
+// two-stage rings shared by both query tiles.  The running maximum is only raised when it grows by more than 2^8
+// ("lazy rescale"), which keeps the O correction (a TMEM read-modify-write) off most iterations.
+//
+// Work items are handed out heaviest first inside groups of eight (batch, head) slices, so that the CTAs that run
+// at the same time read the K / V of few heads (L2 reuse) and the light items fill the tail.
 //
 // Supports: causal masking, grouped-query attention (H a multiple of Hkv), a left sliding window, tanh soft-capping
 // of the logits, arbitrary element strides for Q/K/V (so they can be slices of one fused QKV buffer) and sequence
@@ -14,6 +20,8 @@
 //
 // Takes the place of the cuDNN / TransformerEngine fused attention the reference calls in
 // `olmax/nn/attention.py:52-109`; soft-cap has no counterpart there.
+#include <atomic>
+
 #include "flash_attn.h"
 #include "host_common.h"
 #include "sm100.cuh"
@@ -22,16 +30,21 @@ namespace ob {
 
 namespace fa_fwd {
 
-constexpr int TQ = 128;   // query rows per CTA
+constexpr int TQ = 128;   // query rows per tile; a work item has two tiles
 constexpr int TK = 128;   // keys per iteration
 constexpr int HD = 128;   // head dim
 constexpr int BLK = 128 * 64 * 2;            // one [128 rows][64 elems] swizzled block: 16 KiB
 constexpr int TILE_BYTES = 2 * BLK;          // [128][128] bf16 as two blocks
-constexpr int SMEM_BYTES = 3 * TILE_BYTES + 1024 + 128 + 1024;  // + row-statistics exchange [2][128] floats
-constexpr int THREADS = 320;   // TMA warp, MMA warp, 8 softmax warps
-constexpr int TMEM_COLS = 256;
-constexpr int S_COL = 0;      // S (fp32, 128 cols); P (bf16x2, 64 cols) is written over its first 64 columns
-constexpr int O_COL = 128;    // O (fp32, 128 cols)
+constexpr int ST = 2;                        // K and V ring depth
+constexpr int SMEM_BYTES = (2 + 2 * ST) * TILE_BYTES + 1024 + 1024;   // Q pair, K ring, V ring, barriers, alignment
+constexpr int THREADS = 320;   // TMA / scheduler warp, MMA warp, 2 x 4 softmax warps
+constexpr int TMEM_COLS = 512;
+constexpr int S_COL = 0;      // S of tile i: columns [128 i, 128 i + 128); P (bf16x2, 64 cols) over its first 64
+constexpr int O_COL = 256;    // O of tile i: columns [256 + 128 i, ...)
+constexpr int GROUP = 8;      // (batch, head) slices per scheduling group
+constexpr int N_SCHED = 64;   // ring of work counters (one per launch in flight)
+
+__device__ int g_sched[N_SCHED];
 
 struct Params {
   int B, S, H, Hkv;
@@ -45,6 +58,8 @@ struct Params {
   long long o_sb, o_ss, o_sh;  // element strides of O
   float* lse;                  // [B, H, S]
   int* status;
+  int* sched;                  // work counter, zero at launch
+  int n_pairs, n_items;        // query-tile pairs per (batch, head); items in the padded schedule
 };
 
 __device__ __forceinline__ float fast_tanh(float x) {
@@ -58,53 +73,92 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(THREADS, 2)
+// Key-tile ranges of a work item.  Tile i covers query rows [q0 + 128 i, +128); it is inactive (lo > hi) when it
+// starts beyond the sequence.  The union [ulo, uhi] is what the K / V rings carry.
+struct Geo {
+  int q0, h, b, hkv;
+  int lo[2], hi[2], ulo, uhi;
+};
+__device__ __forceinline__ Geo item_geometry(const Params& p, int pair, int h, int b) {
+  Geo g;
+  g.q0 = pair * 2 * TQ;
+  g.h = h;
+  g.b = b;
+  g.hkv = h / (p.H / p.Hkv);
+  const int last = (p.Sk + TK - 1) / TK - 1;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int qp0 = p.q_off + g.q0 + i * TQ;
+    int hi = last, lo = 0;
+    if (p.causal) hi = min(hi, (qp0 + TQ - 1) / TK);
+    if (p.window >= 0) lo = max(0, (qp0 - p.window) / TK);
+    if (g.q0 + i * TQ >= p.S) { lo = 1; hi = 0; }
+    g.lo[i] = lo;
+    g.hi[i] = hi;
+  }
+  g.ulo = g.lo[0];
+  g.uhi = g.hi[0];
+  if (g.lo[1] <= g.hi[1]) g.uhi = max(g.uhi, g.hi[1]);   // lo[1] >= lo[0] always
+  return g;
+}
+
+// schedule position -> (pair, h, b); false for the padding of the last group
+__device__ __forceinline__ bool decode_item(const Params& p, int w, int& pair, int& h, int& b) {
+  const int per_group = GROUP * p.n_pairs;
+  const int g = w / per_group, r = w - g * per_group;
+  pair = p.n_pairs - 1 - r / GROUP;          // heaviest (longest causal rows) first
+  const int bh = g * GROUP + r % GROUP;
+  if (bh >= p.B * p.H) return false;
+  b = bh / p.H;
+  h = bh - b * p.H;
+  return true;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
     flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sK = smem + TILE_BYTES;
-  uint8_t* sV = smem + 2 * TILE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * TILE_BYTES);
-  uint64_t* q_full = bars + 0;
-  uint64_t* k_full = bars + 1;
-  uint64_t* k_empty = bars + 2;
-  uint64_t* v_full = bars + 3;
-  uint64_t* v_empty = bars + 4;
-  uint64_t* s_full = bars + 5;
-  uint64_t* p_full = bars + 6;
-  uint64_t* o_done = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint8_t* sQ = smem;                              // two tiles
+  uint8_t* sK = smem + 2 * TILE_BYTES;             // ST tiles
+  uint8_t* sV = smem + (2 + ST) * TILE_BYTES;      // ST tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (2 + 2 * ST) * TILE_BYTES);
+  uint64_t* item_full = bars + 0;     // [2]
+  uint64_t* item_empty = bars + 2;    // [2]  9 arrivals: MMA warp + 8 softmax warps
+  uint64_t* q_full = bars + 4;
+  uint64_t* q_empty = bars + 5;
+  uint64_t* k_full = bars + 6;        // [ST]
+  uint64_t* k_empty = bars + 6 + ST;
+  uint64_t* v_full = bars + 6 + 2 * ST;
+  uint64_t* v_empty = bars + 6 + 3 * ST;
+  uint64_t* s_full = bars + 6 + 4 * ST;   // [2]
+  uint64_t* p_full = s_full + 2;          // [2]  4 arrivals (one per softmax warp of the tile)
+  uint64_t* o_done = s_full + 4;          // [2]
+  uint64_t* o_free = s_full + 6;          // [2]  4 arrivals
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* xch = reinterpret_cast<float*>(bars + 16);   // [2][128] exchange between the two column halves of a row
+  volatile int* item_slot = reinterpret_cast<volatile int*>(tmem_slot + 4);   // [2][4]: pair (< 0: end), h, b
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n_q_tiles = (p.S + TQ - 1) / TQ;
-  const int q_tile = n_q_tiles - 1 - (int)blockIdx.x;  // heaviest (longest causal row) tiles first
-  const int h = blockIdx.y;
-  const int b = blockIdx.z;
-  const int hkv = h / (p.H / p.Hkv);
-  const int q0 = q_tile * TQ;
-
-  // key-tile range for this query tile
-  int kv_tile_lo = 0;
-  const int qp0 = p.q_off + q0;   // key-axis position of this tile's first query row
-  int kv_tile_hi = (p.Sk + TK - 1) / TK - 1;
-  if (p.causal) kv_tile_hi = min(kv_tile_hi, (qp0 + TQ - 1) / TK);
-  if (p.window >= 0) kv_tile_lo = max(0, (qp0 - p.window) / TK);
-  const int n_iters = kv_tile_hi - kv_tile_lo + 1;
 
   if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(item_full + i, 1);
+      mbar_init(item_empty + i, 9);
+      mbar_init(s_full + i, 1);
+      mbar_init(p_full + i, 4);
+      mbar_init(o_done + i, 1);
+      mbar_init(o_free + i, 4);
+    }
     mbar_init(q_full, 1);
-    mbar_init(k_full, 1);
-    mbar_init(k_empty, 1);
-    mbar_init(v_full, 1);
-    mbar_init(v_empty, 1);
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 8);      // one arrival per softmax warp (lane 0, after the warp has synchronised)
-    mbar_init(o_done, 1);
+    mbar_init(q_empty, 1);
+    for (int i = 0; i < ST; ++i) {
+      mbar_init(k_full + i, 1);
+      mbar_init(k_empty + i, 1);
+      mbar_init(v_full + i, 1);
+      mbar_init(v_empty + i, 1);
+    }
     *abort_flag = 0;
     mbar_fence_init();
     fence_proxy_async();
@@ -119,201 +173,315 @@ __global__ void __launch_bounds__(THREADS, 2)
   const uint32_t tmem_base = *tmem_slot;
 
   // The TMA and MMA warps run their loops with all 32 lanes so that the loop state stays warp-uniform; one elected
-  // lane issues.  A wait that gives up marks the warp `dead`: the loop then runs out without issuing anything.
+  // lane issues.  A wait that gives up marks the warp `dead`: the loops then run out without issuing anything.
   if (warp == 0) {
+    // ---------------- scheduler + TMA producer ----------------
     const bool leader = elect_one();
     bool dead = false;
     if (leader) {
       tma_prefetch_desc(&tmQ);
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
-      mbar_arrive_expect_tx(q_full, TILE_BYTES);
-      tma_load_4d(sQ, &tmQ, q_full, 0, h, q0, b);
-      tma_load_4d(sQ + BLK, &tmQ, q_full, 64, h, q0, b);
     }
-    for (int j = 0; j < n_iters; ++j) {
-      const int kv0 = (kv_tile_lo + j) * TK;
-      const uint32_t ph = (uint32_t)j & 1u;
-      if (!dead) dead = !mbar_wait(k_empty, ph ^ 1u, abort_flag, p.status, 400);
-      if (leader && !dead) {
-        mbar_arrive_expect_tx(k_full, TILE_BYTES);
-        tma_load_4d(sK, &tmK, k_full, 0, hkv, kv0, b);
-        tma_load_4d(sK + BLK, &tmK, k_full, 64, hkv, kv0, b);
+    uint32_t n_item = 0, k_it = 0;
+    while (!dead) {
+      int pair = -1, h = 0, b = 0;
+      for (;;) {
+        int w = 0;
+        if (lane == 0) w = atomicAdd(p.sched, 1);
+        w = __shfl_sync(0xffffffffu, w, 0);
+        if (w >= p.n_items) { pair = -1; break; }
+        if (decode_item(p, w, pair, h, b)) break;
       }
-      if (!dead) dead = !mbar_wait(v_empty, ph ^ 1u, abort_flag, p.status, 401);
-      if (leader && !dead) {
-        mbar_arrive_expect_tx(v_full, TILE_BYTES);
-        tma_load_4d(sV, &tmV, v_full, 0, hkv, kv0, b);
-        tma_load_4d(sV + BLK, &tmV, v_full, 64, hkv, kv0, b);
+      const uint32_t slot = n_item & 1u;
+      dead = !mbar_wait(item_empty + slot, ((n_item >> 1) & 1u) ^ 1u, abort_flag, p.status, 400);
+      if (dead) break;
+      if (lane == 0) {
+        item_slot[slot * 4 + 0] = pair;
+        item_slot[slot * 4 + 1] = h;
+        item_slot[slot * 4 + 2] = b;
+        mbar_arrive(item_full + slot);
       }
+      if (pair < 0) break;
+      const Geo g = item_geometry(p, pair, h, b);
+      dead = !mbar_wait(q_empty, (n_item & 1u) ^ 1u, abort_flag, p.status, 401);
+      if (leader && !dead) {
+        mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
+        tma_load_4d(sQ, &tmQ, q_full, 0, h, g.q0, b);
+        tma_load_4d(sQ + BLK, &tmQ, q_full, 64, h, g.q0, b);
+        tma_load_4d(sQ + TILE_BYTES, &tmQ, q_full, 0, h, g.q0 + TQ, b);
+        tma_load_4d(sQ + TILE_BYTES + BLK, &tmQ, q_full, 64, h, g.q0 + TQ, b);
+      }
+      for (int u = g.ulo; u <= g.uhi; ++u, ++k_it) {
+        const uint32_t st = k_it % ST, ph = (k_it / ST) & 1u;
+        const int kv0 = u * TK;
+        if (!dead) dead = !mbar_wait(k_empty + st, ph ^ 1u, abort_flag, p.status, 402);
+        if (leader && !dead) {
+          mbar_arrive_expect_tx(k_full + st, TILE_BYTES);
+          tma_load_4d(sK + st * TILE_BYTES, &tmK, k_full + st, 0, g.hkv, kv0, b);
+          tma_load_4d(sK + st * TILE_BYTES + BLK, &tmK, k_full + st, 64, g.hkv, kv0, b);
+        }
+        if (!dead) dead = !mbar_wait(v_empty + st, ph ^ 1u, abort_flag, p.status, 403);
+        if (leader && !dead) {
+          mbar_arrive_expect_tx(v_full + st, TILE_BYTES);
+          tma_load_4d(sV + st * TILE_BYTES, &tmV, v_full + st, 0, g.hkv, kv0, b);
+          tma_load_4d(sV + st * TILE_BYTES + BLK, &tmV, v_full + st, 64, g.hkv, kv0, b);
+        }
+      }
+      ++n_item;
     }
     __syncwarp();
   } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
     const bool leader = elect_one();
     constexpr uint32_t idesc_s = make_idesc_bf16(TQ, TK, 0, 0);
     constexpr uint32_t idesc_o = make_idesc_bf16(TQ, HD, 0, 1);
-    // shared-memory descriptors: constant high words, low words (start address in 16-byte units) advanced per k step
+    // shared-memory descriptors: constant high words, low words (start address in 16-byte units) advanced per step
     const uint64_t dQ = make_smem_desc(smem_u32(sQ), 0, 1024), dK = make_smem_desc(smem_u32(sK), 0, 1024);
     const uint64_t dV = make_smem_desc(smem_u32(sV), BLK, 1024);
     const uint32_t q_lo = (uint32_t)dQ, k_lo = (uint32_t)dK, v_lo = (uint32_t)dV;
     const uint32_t kk_hi = (uint32_t)(dQ >> 32), v_hi = (uint32_t)(dV >> 32);
-    bool dead = !mbar_wait(q_full, 0, abort_flag, p.status, 500);
-    for (int j = 0; j < n_iters; ++j) {
-      const uint32_t ph = (uint32_t)j & 1u;
-      if (!dead) dead = !mbar_wait(k_full, ph, abort_flag, p.status, 501);
-      tc_fence_after_sync();
+    constexpr uint32_t TILE16 = TILE_BYTES >> 4;
+    bool dead = false;
+    uint32_t n_item = 0, k_it = 0;
+    uint32_t cs[2] = {0, 0};   // S tiles issued per query tile (phase of s_full / p_full)
+    uint32_t ce[2] = {0, 0};   // items in which the query tile was active (phase of o_done / o_free)
+
+    // S_i = Q_i K^T into the S columns of tile i.  In-order execution of this thread's MMAs keeps it behind the
+    // previous P V of the same tile, which read P from these columns.
+    auto issue_s = [&](int i, uint32_t st) {
       if (leader && !dead) {
-        // S = Q K^T.  In-order execution of this thread's MMAs keeps it behind the previous P V, which read P
-        // from the same columns.
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = ((uint32_t)(kk >> 2) * BLK + (uint32_t)(kk & 3) * 32) >> 4;
-          umma_ss_lohi(tmem_base + S_COL, q_lo + off, kk_hi, k_lo + off, kk_hi, idesc_s, kk != 0 ? 1u : 0u);
+          umma_ss_lohi(tmem_base + S_COL + (uint32_t)i * 128u, q_lo + (uint32_t)i * TILE16 + off, kk_hi,
+                       k_lo + st * TILE16 + off, kk_hi, idesc_s, kk != 0 ? 1u : 0u);
         }
-        umma_commit(k_empty);
-        umma_commit(s_full);
+        umma_commit(s_full + i);
       }
-      if (!dead) dead = !mbar_wait(p_full, ph, abort_flag, p.status, 502);
-      if (!dead) dead = !mbar_wait(v_full, ph, abort_flag, p.status, 503);
-      tc_fence_after_sync();
+    };
+    // O_i += P_i V: A = P from TMEM (128 x 16 bf16 per step = 8 columns), B = V as an MN-major operand
+    auto issue_pv = [&](int i, uint32_t st, bool first) {
       if (leader && !dead) {
-        // O += P V: A = P from TMEM (128 x 16 bf16 per step = 8 columns), B = V as an MN-major operand
 #pragma unroll
         for (int kk = 0; kk < TK / 16; ++kk) {
-          umma_ts_lohi(tmem_base + O_COL, tmem_base + S_COL + (uint32_t)kk * 8, v_lo + (uint32_t)kk * 128u, v_hi, idesc_o,
-                       (j | kk) != 0 ? 1u : 0u);
+          umma_ts_lohi(tmem_base + O_COL + (uint32_t)i * 128u, tmem_base + S_COL + (uint32_t)i * 128u + (uint32_t)kk * 8,
+                       v_lo + st * TILE16 + (uint32_t)kk * 128u, v_hi, idesc_o, (!first || kk != 0) ? 1u : 0u);
         }
-        umma_commit(v_empty);
-        umma_commit(o_done);
       }
+    };
+
+    while (!dead) {
+      const uint32_t slot = n_item & 1u;
+      dead = !mbar_wait(item_full + slot, (n_item >> 1) & 1u, abort_flag, p.status, 500);
+      if (dead) break;
+      const int pair = item_slot[slot * 4 + 0], h = item_slot[slot * 4 + 1], b = item_slot[slot * 4 + 2];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(item_empty + slot);
+      if (pair < 0) break;
+      const Geo g = item_geometry(p, pair, h, b);
+      const bool act1 = g.lo[1] <= g.hi[1];
+      dead = !mbar_wait(q_full, n_item & 1u, abort_flag, p.status, 501);
+      // first K tile: S of both query tiles
+      {
+        const uint32_t st = k_it % ST, ph = (k_it / ST) & 1u;
+        if (!dead) dead = !mbar_wait(k_full + st, ph, abort_flag, p.status, 502);
+        tc_fence_after_sync();
+        issue_s(0, st);
+        if (act1 && g.lo[1] == g.ulo) issue_s(1, st);
+        if (leader && !dead) {
+          umma_commit(k_empty + st);
+          if (g.ulo == g.uhi) umma_commit(q_empty);
+        }
+      }
+      for (int u = g.ulo; u <= g.uhi; ++u, ++k_it) {
+        const uint32_t st = k_it % ST, ph = (k_it / ST) & 1u;
+        const uint32_t st_n = (k_it + 1) % ST, ph_n = ((k_it + 1) / ST) & 1u;
+        const bool more = u < g.uhi;
+        const bool in0 = u <= g.hi[0];
+        const bool in1 = act1 && u >= g.lo[1] && u <= g.hi[1];
+        if (!dead) dead = !mbar_wait(v_full + st, ph, abort_flag, p.status, 503);
+        if (in0) {
+          if (u == g.lo[0] && !dead) dead = !mbar_wait(o_free, (ce[0] & 1u) ^ 1u, abort_flag, p.status, 504);
+          if (!dead) dead = !mbar_wait(p_full, cs[0] & 1u, abort_flag, p.status, 505);
+          tc_fence_after_sync();
+          issue_pv(0, st, u == g.lo[0]);
+          if (u == g.hi[0] && leader && !dead) umma_commit(o_done);
+          ++cs[0];
+        }
+        if (more) {
+          if (!dead) dead = !mbar_wait(k_full + st_n, ph_n, abort_flag, p.status, 506);
+          tc_fence_after_sync();
+          if (u + 1 <= g.hi[0]) issue_s(0, st_n);
+        }
+        if (in1) {
+          if (u == g.lo[1] && !dead) dead = !mbar_wait(o_free + 1, (ce[1] & 1u) ^ 1u, abort_flag, p.status, 507);
+          if (!dead) dead = !mbar_wait(p_full + 1, cs[1] & 1u, abort_flag, p.status, 508);
+          tc_fence_after_sync();
+          issue_pv(1, st, u == g.lo[1]);
+          if (u == g.hi[1] && leader && !dead) umma_commit(o_done + 1);
+          ++cs[1];
+        }
+        if (leader && !dead) umma_commit(v_empty + st);
+        if (more) {
+          if (act1 && u + 1 >= g.lo[1] && u + 1 <= g.hi[1]) issue_s(1, st_n);
+          if (leader && !dead) {
+            umma_commit(k_empty + st_n);
+            if (u + 1 == g.uhi) umma_commit(q_empty);
+          }
+        }
+      }
+      ++ce[0];
+      if (act1) ++ce[1];
+      ++n_item;
     }
     __syncwarp();
   } else {
-    // ---------------- softmax + output: 8 warps, thread <-> (query row, 64-column half) ----------------
-    // Two warps share each TMEM lane quarter and split the 128 score columns; the halves exchange their row maxima
-    // through shared memory once per tile.  With two CTAs per SM every scheduler then has four softmax warps to hide
-    // TMEM and MUFU latency.
-    const int qd = warp & 3;
-    const int half = (warp - 2) >> 2;
+    // ---------------- softmax + output: one warpgroup per query tile, thread <-> query row ----------------
+    const int tile = (warp - 2) >> 2;          // 0: warps 2-5, 1: warps 6-9
+    const int qd = warp & 3;                   // TMEM lane quarter this warp may access
     const int row = qd * 32 + lane;
-    const int col0 = half * 64;
-    const int q_idx = q0 + row;
-    const int q_pos = p.q_off + q_idx;
     const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16);
+    const uint32_t t_s = t_lane + S_COL + (uint32_t)tile * 128u;
+    const uint32_t t_o = t_lane + O_COL + (uint32_t)tile * 128u;
     const bool capped = p.softcap > 0.f;
-    float m_run = -INFINITY;  // running max, log2 domain (identical in both halves of a row)
-    float l_run = 0.f;        // this half's share of the running sum
+    const float sc = capped ? 1.0f : p.scale_log2;   // soft-capped scores are already in the log2 domain
     bool ok = true;
-    for (int j = 0; j < n_iters && ok; ++j) {
-      const uint32_t ph = (uint32_t)j & 1u;
-      const int kv0 = (kv_tile_lo + j) * TK;
-      ok = mbar_wait(s_full, ph, abort_flag, p.status, 600);
+    uint32_t n_item = 0, cs = 0, ce = 0;
+    while (ok) {
+      const uint32_t slot = n_item & 1u;
+      ok = mbar_wait(item_full + slot, (n_item >> 1) & 1u, abort_flag, p.status, 600);
       if (!ok) break;
-      tc_fence_after_sync();
-      const bool need_mask = (kv0 + TK > p.Sk) || (p.causal && kv0 + TK - 1 > qp0) ||
-                             (p.window >= 0 && kv0 < qp0 + TQ - 1 - p.window);
+      const int pair = item_slot[slot * 4 + 0], h = item_slot[slot * 4 + 1], b = item_slot[slot * 4 + 2];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(item_empty + slot);
+      ++n_item;
+      if (pair < 0) break;
+      const Geo g = item_geometry(p, pair, h, b);
+      if (g.lo[tile] > g.hi[tile]) continue;
+      const int q0 = g.q0 + tile * TQ;
+      const int qp0 = p.q_off + q0;
+      const int q_idx = q0 + row;
+      const int q_pos = p.q_off + q_idx;
       const int kv_hi = p.causal ? min(q_pos, p.Sk - 1) : p.Sk - 1;  // last visible key
       const int kv_lo = p.window >= 0 ? q_pos - p.window : 0;        // first visible key
-      // this thread's 64 scores, kept in registers for both the max and the exponentials
-      uint32_t r0[32], r1[32];
-      tmem_ld32(t_lane + S_COL + (uint32_t)col0, r0);
-      tmem_ld32(t_lane + S_COL + (uint32_t)(col0 + 32), r1);
-      tmem_ld_wait();
-      if (capped) {
+      float m_run = -INFINITY;  // running max, log2 domain
+      float l_run = 0.f;
+      for (int u = g.lo[tile]; u <= g.hi[tile] && ok; ++u, ++cs) {
+        const int kv0 = u * TK;
+        ok = mbar_wait(s_full + tile, cs & 1u, abort_flag, p.status, 601);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const bool need_mask = (kv0 + TK > p.Sk) || (p.causal && kv0 + TK - 1 > qp0) ||
+                               (p.window >= 0 && kv0 < qp0 + TQ - 1 - p.window);
+        // the whole score row in registers, for both the maximum and the exponentials
+        uint32_t r[4][32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          r0[i] = __float_as_uint(p.cap_log2 * fast_tanh(__uint_as_float(r0[i]) * p.scale_over_cap));
-          r1[i] = __float_as_uint(p.cap_log2 * fast_tanh(__uint_as_float(r1[i]) * p.scale_over_cap));
+        for (int c = 0; c < 4; ++c) tmem_ld32(t_s + (uint32_t)c * 32u, r[c]);
+        tmem_ld_wait();
+        if (capped) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              r[c][i] = __float_as_uint(p.cap_log2 * fast_tanh(__uint_as_float(r[c][i]) * p.scale_over_cap));
         }
-      }
-      if (need_mask) {
+        if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kv = kv0 + col0 + i;
-          if (kv > kv_hi || kv < kv_lo) r0[i] = __float_as_uint(-INFINITY);
-          if (kv + 32 > kv_hi || kv + 32 < kv_lo) r1[i] = __float_as_uint(-INFINITY);
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int kv = kv0 + c * 32 + i;
+              if (kv > kv_hi || kv < kv_lo) r[c][i] = __float_as_uint(-INFINITY);
+            }
         }
-      }
-      // four independent chains: a single running maximum (or sum, below) would serialise 32 dependent operations
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        // eight independent chains: a single running maximum (or sum, below) would serialise 128 dependent operations
+        float mx8[8];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], fmaxf(__uint_as_float(r0[i]), __uint_as_float(r1[i])));
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      const float sc = capped ? 1.0f : p.scale_log2;   // soft-capped scores are already in the log2 domain
-      mx *= sc;                                        // sc > 0: max commutes with the scaling
-      xch[half * 128 + row] = mx;
-      asm volatile("bar.sync 2, 256;" ::: "memory");
-      const float m_new = fmaxf(m_run, fmaxf(mx, xch[(half ^ 1) * 128 + row]));
-      // lazy rescale: raise the running max only when it grows by more than 8 (factor 256); warp-uniform decision
-      const bool want = (m_new > m_run + 8.0f) || (m_run == -INFINITY && m_new > -INFINITY);
-      if (__any_sync(0xffffffffu, want)) {
-        const float m_next = want ? m_new : m_run;
-        const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_next);
-        if (j > 0) {
+        for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(__uint_as_float(r[0][i]), __uint_as_float(r[0][i + 8]));
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = (c == 0 ? 16 : 0); i < 32; i += 16)
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              mx8[k] = fmaxf(mx8[k], fmaxf(__uint_as_float(r[c][i + k]), __uint_as_float(r[c][i + 8 + k])));
+        float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                         fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+        mx *= sc;                                        // sc > 0: max commutes with the scaling
+        const float m_new = fmaxf(m_run, mx);
+        // lazy rescale: raise the running max only when it grows by more than 8 (factor 256); warp-uniform decision
+        const bool want = (m_new > m_run + 8.0f) || (m_run == -INFINITY && m_new > -INFINITY);
+        if (__any_sync(0xffffffffu, want)) {
+          const float m_next = want ? m_new : m_run;
+          const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_next);
+          if (u > g.lo[tile]) {
 #pragma unroll 1
-          for (int c = 0; c < 64; c += 16) {
-            uint32_t o[16];
-            tmem_ld16(t_lane + O_COL + (uint32_t)(col0 + c), o);
-            tmem_ld_wait();
+            for (int c = 0; c < 128; c += 32) {
+              uint32_t o[32];
+              tmem_ld32(t_o + (uint32_t)c, o);
+              tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st16(t_lane + O_COL + (uint32_t)(col0 + c), o);
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(t_o + (uint32_t)c, o);
+            }
+            tmem_st_wait();
           }
-          tmem_st_wait();
+          l_run *= alpha;
+          m_run = m_next;
         }
-        l_run *= alpha;
-        m_run = m_next;
-      }
-      const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
-      // P = exp2(s - m) as bf16 pairs, written over the S columns (both halves hold their scores in registers by now)
-      float lsum4[4] = {0.f, 0.f, 0.f, 0.f};
+        const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
+        // P = exp2(s - m) as bf16 pairs, written over the S columns (the scores are all in registers by now)
+        float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        uint32_t pk[16];
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float s0 = __uint_as_float(hh ? r1[i] : r0[i]), s1 = __uint_as_float(hh ? r1[i + 1] : r0[i + 1]);
-          const float e0 = fast_exp2(fmaf(s0, sc, neg_m)), e1 = fast_exp2(fmaf(s1, sc, neg_m));
-          lsum4[(i >> 1) & 3] += e0 + e1;
-          pk[i >> 1] = pack_bf16x2(e0, e1);
+          for (int i = 0; i < 32; i += 2) {
+            const float e0 = fast_exp2(fmaf(__uint_as_float(r[c][i]), sc, neg_m));
+            const float e1 = fast_exp2(fmaf(__uint_as_float(r[c][i + 1]), sc, neg_m));
+            ls[(i >> 1) & 3] += e0 + e1;
+            pk[i >> 1] = pack_bf16x2(e0, e1);
+          }
+          tmem_st16(t_s + (uint32_t)c * 16u, pk);
         }
-        tmem_st16(t_lane + S_COL + (uint32_t)(half * 32 + hh * 16), pk);
+        l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full + tile);
       }
-      l_run += (lsum4[0] + lsum4[1]) + (lsum4[2] + lsum4[3]);
-      tmem_st_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
-    }
-    // epilogue: wait for the last P V, combine the halves' sums, normalise, store
-    if (ok) ok = mbar_wait(o_done, (uint32_t)(n_iters - 1) & 1u, abort_flag, p.status, 601);
-    xch[half * 128 + row] = l_run;
-    asm volatile("bar.sync 2, 256;" ::: "memory");
-    if (ok) {
+      // epilogue: wait for the last P V, normalise, store
+      if (ok) ok = mbar_wait(o_done + tile, ce & 1u, abort_flag, p.status, 602);
+      ++ce;
+      if (!ok) break;
       tc_fence_after_sync();
-      const float l_tot = l_run + xch[(half ^ 1) * 128 + row];
-      const float inv_l = l_tot > 0.f ? 1.0f / l_tot : 0.f;
+      const float inv_l = l_run > 0.f ? 1.0f / l_run : 0.f;
       const bool row_ok = q_idx < p.S;
-      bf16* orow = p.o + (long long)b * p.o_sb + (long long)q_idx * p.o_ss + (long long)h * p.o_sh + col0;
+      bf16* orow = p.o + (long long)b * p.o_sb + (long long)q_idx * p.o_ss + (long long)h * p.o_sh;
 #pragma unroll 1
-      for (int c = 0; c < 64; c += 32) {
-        uint32_t r[32];
-        tmem_ld32(t_lane + O_COL + (uint32_t)(col0 + c), r);
+      for (int c = 0; c < 128; c += 32) {
+        uint32_t o[32];
+        tmem_ld32(t_o + (uint32_t)c, o);
         tmem_ld_wait();
         if (row_ok) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
+          for (int q = 0; q < 4; ++q) {
             uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(r[g * 8 + 0]) * inv_l, __uint_as_float(r[g * 8 + 1]) * inv_l);
-            v.y = pack_bf16x2(__uint_as_float(r[g * 8 + 2]) * inv_l, __uint_as_float(r[g * 8 + 3]) * inv_l);
-            v.z = pack_bf16x2(__uint_as_float(r[g * 8 + 4]) * inv_l, __uint_as_float(r[g * 8 + 5]) * inv_l);
-            v.w = pack_bf16x2(__uint_as_float(r[g * 8 + 6]) * inv_l, __uint_as_float(r[g * 8 + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + c + g * 8) = v;
+            v.x = pack_bf16x2(__uint_as_float(o[q * 8 + 0]) * inv_l, __uint_as_float(o[q * 8 + 1]) * inv_l);
+            v.y = pack_bf16x2(__uint_as_float(o[q * 8 + 2]) * inv_l, __uint_as_float(o[q * 8 + 3]) * inv_l);
+            v.z = pack_bf16x2(__uint_as_float(o[q * 8 + 4]) * inv_l, __uint_as_float(o[q * 8 + 5]) * inv_l);
+            v.w = pack_bf16x2(__uint_as_float(o[q * 8 + 6]) * inv_l, __uint_as_float(o[q * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c + q * 8) = v;
           }
         }
       }
-      if (row_ok && half == 0) {
-        const float lse = l_tot > 0.f ? (m_run + log2f(l_tot)) * 0.6931471805599453f : -INFINITY;
+      // O of this tile has been read: the next item's first P V may overwrite it
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(o_free + tile);
+      if (row_ok) {
+        const float lse = l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
         p.lse[((long long)b * p.H + h) * p.S + q_idx] = lse;
       }
     }
@@ -377,7 +545,26 @@ extern "C" int ob_flash_attn_fwd(const ObAttnArgs* a, cudaStream_t stream) {
                                     fa_fwd::SMEM_BYTES));
     attr_set[dev] = true;
   }
-  dim3 grid((a->S + 127) / 128, a->H, a->B);
+  // persistent CTAs, one per SM, fed from a work counter: a ring of counters so that launches in flight on different
+  // streams never share one; the launch's counter is cleared in stream order just before the kernel
+  static int n_sm[64] = {};
+  static int* sched_base[64] = {};
+  if (n_sm[dev] == 0) {
+    int n = 0;
+    OB_CUDA_OK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+    void* sym = nullptr;
+    OB_CUDA_OK(cudaGetSymbolAddress(&sym, fa_fwd::g_sched));
+    sched_base[dev] = static_cast<int*>(sym);
+    n_sm[dev] = n;
+  }
+  static std::atomic<unsigned> launch_no{0};
+  p.sched = sched_base[dev] + launch_no.fetch_add(1) % fa_fwd::N_SCHED;
+  p.n_pairs = (a->S + 2 * fa_fwd::TQ - 1) / (2 * fa_fwd::TQ);
+  const int groups = (a->B * a->H + fa_fwd::GROUP - 1) / fa_fwd::GROUP;
+  p.n_items = groups * fa_fwd::GROUP * p.n_pairs;
+  OB_CUDA_OK(cudaMemsetAsync(p.sched, 0, sizeof(int), stream));
+  const int valid_items = a->B * a->H * p.n_pairs;
+  dim3 grid(valid_items < n_sm[dev] ? valid_items : n_sm[dev]);
   fa_fwd::flash_fwd_kernel<<<grid, fa_fwd::THREADS, fa_fwd::SMEM_BYTES, stream>>>(tq, tk, tv, p);
   OB_CUDA_OK(cudaGetLastError());
   return 0;

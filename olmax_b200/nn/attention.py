@@ -22,7 +22,7 @@ from ..parallel.mesh import TPStyle
 from ..types import StrEnum
 from .linear import Linear
 from .module import Module, current_build_context
-from .normalization import NormalizerConfig, RMSNormConfig
+from .normalization import NormalizerConfig, RMSNorm, RMSNormConfig
 from .rope import BufferCache, RotaryPositionalEmbedding, RotaryPositionalEmbeddingConfig
 
 __all__ = ["AttentionImplementation", "AttentionKernel", "MultiheadSelfAttention", "MultiheadSelfAttentionConfig"]
@@ -129,18 +129,25 @@ class MultiheadSelfAttention(Module):
             v = self.v_proj(x)
         T = q.shape[0]
         S = T // batch_size
-        if self.q_norm is not None:
-            heads_q = self.local_heads if self.use_head_qk_norm else 1
-            heads_k = self.local_kv_heads if self.use_head_qk_norm else 1
-            q = self.q_norm(q, heads=heads_q)
-            k = self.k_norm(k, heads=heads_k)
-        q = q.view(batch_size, S, self.local_heads, self.head_dim)
-        k = k.view(batch_size, S, self.local_kv_heads, self.head_dim)
+        heads_q = self.local_heads if self.use_head_qk_norm else 1
+        heads_k = self.local_kv_heads if self.use_head_qk_norm else 1
         v = v.view(batch_size, S, self.local_kv_heads, self.head_dim)
-        if self.rope is not None:
+        if isinstance(self.q_norm, RMSNorm) and self.rope is not None:
+            # q / k normalisation and the rotary embedding in one pass over each projection
             cp = self.mesh.cp
-            q = self.rope(q, cache, cp.size, cp.rank)
-            k = self.rope(k, cache, cp.size, cp.rank)
+            cos, sin = self.rope.tables_for(S, x.device, cache, cp.size, cp.rank)
+            q = F.rms_norm_rope(q, self.q_norm.weight, self.q_norm.eps, heads_q, cos, sin, batch_size, self.head_dim)
+            k = F.rms_norm_rope(k, self.k_norm.weight, self.k_norm.eps, heads_k, cos, sin, batch_size, self.head_dim)
+        else:
+            if self.q_norm is not None:
+                q = self.q_norm(q, heads=heads_q)
+                k = self.k_norm(k, heads=heads_k)
+            q = q.view(batch_size, S, self.local_heads, self.head_dim)
+            k = k.view(batch_size, S, self.local_kv_heads, self.head_dim)
+            if self.rope is not None:
+                cp = self.mesh.cp
+                q = self.rope(q, cache, cp.size, cp.rank)
+                k = self.rope(k, cache, cp.size, cp.rank)
         o = self.sdpa(q, k, v).reshape(T, self.local_heads * self.head_dim)
         if tpc is not None:
             return F.tp_row_linear(o, tpc, self.o_proj.weight)   # reduce-scatter fused into the GEMM epilogue

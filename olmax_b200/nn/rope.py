@@ -47,12 +47,16 @@ class RotaryPositionalEmbedding(torch.nn.Module):
             cache[key] = out
         return out
 
+    def tables_for(self, local_len: int, device, cache: Optional[BufferCache] = None, cp_size: int = 1,
+                   cp_rank: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+        """The (cos, sin) rows for this rank's ``local_len`` tokens (all of the sequence without context parallelism)."""
+        if cp_size > 1:
+            return self.get_local_tables(local_len, cp_size, cp_rank, device, cache)
+        return self.get_tables(local_len, device, cache)
+
     def forward(self, x: torch.Tensor, cache: Optional[BufferCache] = None, cp_size: int = 1, cp_rank: int = 0) -> torch.Tensor:
         """x: [B, S, H, D] (S = this rank's tokens under context parallelism)."""
-        if cp_size > 1:
-            cos, sin = self.get_local_tables(x.shape[1], cp_size, cp_rank, x.device, cache)
-        else:
-            cos, sin = self.get_tables(x.shape[1], x.device, cache)
+        cos, sin = self.tables_for(x.shape[1], x.device, cache, cp_size, cp_rank)
         return F.rope(x, cos, sin)
 
 

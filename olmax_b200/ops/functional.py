@@ -585,6 +585,67 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
     return _RopeFn.apply(x, cos, sin)
 
 
+class _RMSNormRopeFn(torch.autograd.Function):
+    """``rope(rms_norm(x) * w)`` for the q / k projections in one kernel per direction: x ``[B * S, n * hd]`` ->
+    ``[B, S, n, hd]``.  ``heads`` = 1 normalises the whole projection, ``heads`` = n every head separately."""
+
+    @staticmethod
+    def forward(ctx, x, handle, eps, heads, cos, sin, batch, hd):
+        w = handle.full()
+        d = w.numel()
+        T, width = x.shape
+        S = T // batch
+        ctx.handle, ctx.cfg = handle, (eps, heads, batch, hd, d, S)
+        if _on_gpu(x):
+            xc = x.contiguous()
+            rows = T * heads
+            y = torch.empty_like(xc)
+            rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+            K.rmsnorm_rope_fwd(xc, w, y, rstd, cos, sin, rows=rows, d=d, hd=hd, heads=heads, seq_len=S, eps=eps,
+                               ld_x=width, ld_y=width)
+            ctx.save_for_backward(xc, w, rstd, cos, sin)
+            return y.view(batch, S, width // hd, hd)
+        xv = x.reshape(-1, d) if heads == 1 else x.reshape(-1, heads, d)
+        y = ref.rms_norm(xv, w, eps).reshape(batch, S, width // hd, hd)
+        ctx.save_for_backward(x, w, cos, sin)
+        return ref.apply_rope(y, cos, sin, 1.0)
+
+    @staticmethod
+    def backward(ctx, dy):
+        handle = ctx.handle
+        eps, heads, batch, hd, d, S = ctx.cfg
+        if _on_gpu(dy):
+            xc, w, rstd, cos, sin = ctx.saved_tensors
+            T, width = xc.shape
+            dyc = dy.contiguous().view(T, width)
+            dx = torch.empty_like(xc)
+            direct = handle.shard_count == 1 and getattr(handle.store, "symm_rs", None) is None
+            if direct:
+                dw, dw_scale = handle.local_grad, handle.store.grad_scale
+            else:
+                dw, dw_scale = torch.zeros(d, dtype=torch.float32, device=dy.device), 1.0
+            K.rmsnorm_rope_bwd(dyc, xc, w, rstd, dx, cos, sin, rows=T * heads, d=d, hd=hd, heads=heads, seq_len=S, dw=dw,
+                               dw_scale=dw_scale, ld_dy=width, ld_x=width, ld_dx=width)
+            if not direct:
+                handle.add_grad(dw)
+            return dx, None, None, None, None, None, None, None
+        x, w, cos, sin = ctx.saved_tensors
+        with torch.enable_grad():
+            xx = x.detach().requires_grad_(True)
+            ww = w.detach().requires_grad_(True)
+            xv = xx.reshape(-1, d) if heads == 1 else xx.reshape(-1, heads, d)
+            y = ref.apply_rope(ref.rms_norm(xv, ww, eps).reshape(dy.shape), cos, sin, 1.0)
+        dx, dw = torch.autograd.grad(y, (xx, ww), dy)
+        handle.add_grad(dw)
+        return dx, None, None, None, None, None, None, None
+
+
+def rms_norm_rope(x: torch.Tensor, handle, eps: float, heads: int, cos: torch.Tensor, sin: torch.Tensor, batch: int,
+                  head_dim: int) -> torch.Tensor:
+    """See :class:`_RMSNormRopeFn` (the q_norm / k_norm + rotary sequence of ``olmax/nn/attention.py:270-300``)."""
+    return _RMSNormRopeFn.apply(x, handle, eps, heads, cos, sin, batch, head_dim)
+
+
 # ----------------------------------------------------------------------------------------------------------------------
 # Attention
 # ----------------------------------------------------------------------------------------------------------------------

@@ -23,7 +23,7 @@ from ._lib import KernelError, ObAttnArgs, ObGemmArgs, check, lib, register_sign
 
 __all__ = [
     "EPI_BF16", "EPI_F32", "EPI_F32_ACC", "EPI_F32_RED", "EPI_SWIGLU", "EPI_GEGLU", "EPI_BF16_ACC",
-    "gemm", "flash_attn_fwd", "flash_attn_bwd", "rmsnorm_fwd", "rmsnorm_bwd", "rope", "glu_fwd", "glu_bwd",
+    "gemm", "flash_attn_fwd", "flash_attn_bwd", "rmsnorm_fwd", "rmsnorm_bwd", "rmsnorm_rope_fwd", "rmsnorm_rope_bwd", "rope", "glu_fwd", "glu_bwd",
     "embed_gather", "embed_scatter", "ce_fwd_bwd", "ce_vp_stats", "ce_vp_grad", "count_valid", "adamw", "sumsq", "clip_coef", "cast_f32_bf16",
     "layernorm_fwd", "layernorm_bwd", "gather_shards", "scatter_add_shards", "allreduce_p2p", "allreduce_multimem",
     "peer_barrier", "peer_signal", "peer_wait", "copy_bytes", "push_copy", "fold_slots_bf16", "reduce_slots",
@@ -60,6 +60,8 @@ register_signature("ob_rmsnorm_bwd", [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i
 register_signature("ob_layernorm_fwd", [_vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _f, _vp])
 register_signature("ob_layernorm_bwd", [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _f, _vp])
 register_signature("ob_rope", [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _ll, _f, _i, _vp])
+register_signature("ob_rmsnorm_rope_fwd", [_vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _ll, _ll, _i, _f, _vp])
+register_signature("ob_rmsnorm_rope_bwd", [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _ll, _ll, _ll, _i, _f, _vp])
 register_signature("ob_glu_fwd", [_vp, _vp, _vp, _ll, _i, _vp])
 register_signature("ob_glu_bwd", [_vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _vp])
 register_signature("ob_embed_gather", [_vp, _vp, _i, _i, _vp, _ll, _i, _f, _vp])
@@ -257,6 +259,26 @@ def rmsnorm_bwd(dy, x, w, rstd, dx, *, rows, d, dw=None, dsum=None, heads=1, ld_
                                _ptr(dw), rows, d, heads, ld_dy if ld_dy is not None else d,
                                ld_x if ld_x is not None else d, ld_dx if ld_dx is not None else d, dw_scale,
                                stream_ptr(x.device)), "rmsnorm_bwd")
+    _count()
+
+
+def rmsnorm_rope_fwd(x, w, y, rstd, cos, sin, *, rows, d, hd, heads, seq_len, eps, ld_x=None, ld_y=None) -> None:
+    """y = rope(rmsnorm(x) * w): rows of ``d`` elements (``d / hd`` heads each), table row ``(row / heads) % seq_len``."""
+    _req_bf16(x, w, y)
+    check(lib().ob_rmsnorm_rope_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), _ptr(rstd), cos.data_ptr(), sin.data_ptr(),
+                                    rows, d, hd, heads, ld_x if ld_x is not None else d, ld_y if ld_y is not None else d,
+                                    seq_len, eps, stream_ptr(x.device)), "rmsnorm_rope_fwd")
+    _count()
+
+
+def rmsnorm_rope_bwd(dy, x, w, rstd, dx, cos, sin, *, rows, d, hd, heads, seq_len, dw=None, dw_scale=1.0, ld_dy=None,
+                     ld_x=None, ld_dx=None) -> None:
+    _req_bf16(dy, x, w, dx)
+    check(lib().ob_rmsnorm_rope_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(), _ptr(dw),
+                                    cos.data_ptr(), sin.data_ptr(), rows, d, hd, heads,
+                                    ld_dy if ld_dy is not None else d, ld_x if ld_x is not None else d,
+                                    ld_dx if ld_dx is not None else d, seq_len, dw_scale, stream_ptr(x.device)),
+          "rmsnorm_rope_bwd")
     _count()
 
 
@@ -529,7 +551,8 @@ def format_timing(report: dict, top: int = 40) -> str:
     return "\n".join(lines)
 
 
-for _name in ("gemm", "flash_attn_fwd", "flash_attn_bwd", "rmsnorm_fwd", "rmsnorm_bwd", "layernorm_fwd", "layernorm_bwd",
+for _name in ("gemm", "flash_attn_fwd", "flash_attn_bwd", "rmsnorm_fwd", "rmsnorm_bwd", "rmsnorm_rope_fwd",
+              "rmsnorm_rope_bwd", "layernorm_fwd", "layernorm_bwd",
               "rope", "glu_fwd", "glu_bwd", "embed_gather", "embed_scatter", "ce_fwd_bwd", "ce_vp_stats", "ce_vp_grad", "count_valid",
               "adamw", "sumsq",
               "clip_coef", "cast_f32_bf16", "gather_shards", "scatter_add_shards", "allreduce_p2p", "allreduce_multimem",

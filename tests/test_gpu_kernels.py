@@ -138,6 +138,10 @@ def test_gemm_gated_epilogue(K, gelu):
     (1, 640, 2, 2, True, 200, 0.0),
     (1, 384, 2, 2, True, -1, 20.0),
     (1, 256, 2, 2, False, -1, 0.0),
+    (1, 128, 2, 2, True, -1, 0.0),        # one query tile: the second tile of the pair is inactive
+    (2, 2048, 16, 4, True, -1, 0.0),      # more work items than SMs: several items per persistent CTA
+    (3, 1024, 5, 5, True, 300, 0.0),      # 15 (batch, head) slices: a partly filled scheduling group; window
+    (1, 900, 3, 1, False, -1, 0.0),       # no mask, ragged length, equal-weight items
 ])
 def test_flash_attention(K, B, S, H, Hkv, causal, window, softcap):
     dev = "cuda"
@@ -330,6 +334,42 @@ def test_rope_and_glu(K):
         dg, du, a2 = torch.empty_like(g), torch.empty_like(g), torch.empty_like(g)
         K.glu_bwd(g, u, da, dg, du, a2, gelu)
         assert rel_err(dg, wg) < 6e-3 and rel_err(du, wu) < 6e-3 and rel_err(a2, want) < 5e-3
+    _check_status()
+
+
+@pytest.mark.parametrize("B,S,n,hd,head_wise", [
+    (2, 96, 32, 128, False),     # norm over the whole 4096-wide projection (256 pairs: one per thread)
+    (2, 96, 8, 128, False),      # 1024-wide k projection of a grouped-query model
+    (1, 200, 4, 128, True),      # head-wise norm
+    (2, 64, 3, 64, True),        # head dim 64
+    (1, 50, 64, 128, False),     # 8192-wide projection (two pairs per thread)
+])
+def test_fused_rmsnorm_rope_matches_the_two_kernels_and_the_fp32_reference(K, B, S, n, hd, head_wise):
+    dev = "cuda"
+    torch.manual_seed(9)
+    T, width = B * S, n * hd
+    heads, d = (n, hd) if head_wise else (1, width)
+    x = torch.randn(T, width, device=dev, dtype=torch.bfloat16)
+    w = (torch.randn(d, device=dev) * 0.1 + 1).to(torch.bfloat16)
+    cos, sin = ref.rope_tables(S, hd, 500000.0, device=dev)
+    rows = T * heads
+    y, rstd = torch.empty_like(x), torch.empty(rows, device=dev, dtype=torch.float32)
+    K.rmsnorm_rope_fwd(x, w, y, rstd, cos, sin, rows=rows, d=d, hd=hd, heads=heads, seq_len=S, eps=1e-5, ld_x=width,
+                       ld_y=width)
+    # the same through the separate kernels: identical up to the order of the row sums
+    yn, rstd2, y2 = torch.empty_like(x), torch.empty_like(rstd), torch.empty_like(x)
+    K.rmsnorm_fwd(x, w, yn, rows=rows, d=d, eps=1e-5, rstd=rstd2, heads=heads, ld_x=width, ld_y=width)
+    K.rope(yn.view(B, S, n, hd), y2.view(B, S, n, hd), cos, sin)
+    assert rel_err(y, y2) < 2e-3 and rel_err(rstd, rstd2) < 1e-5
+    xf, wf = x.float().requires_grad_(True), w.float().requires_grad_(True)
+    want = ref.apply_rope(ref.rms_norm(xf.view(T, heads, d), wf, 1e-5).view(B, S, n, hd), cos, sin)
+    assert rel_err(y.view(B, S, n, hd), want) < 6e-3
+    dy = torch.randn_like(x)
+    gx, gw = torch.autograd.grad(want, (xf, wf), dy.float().view(B, S, n, hd))
+    dx, dw = torch.empty_like(x), torch.zeros(d, device=dev, dtype=torch.float32)
+    K.rmsnorm_rope_bwd(dy, x, w, rstd, dx, cos, sin, rows=rows, d=d, hd=hd, heads=heads, seq_len=S, dw=dw, dw_scale=0.5,
+                       ld_dy=width, ld_x=width, ld_dx=width)
+    assert rel_err(dx, gx) < 1e-2 and rel_err(dw, 0.5 * gw) < 1e-2
     _check_status()
 
 
