@@ -37,7 +37,7 @@ constexpr int BLK = 128 * 64 * 2;            // one [128 rows][64 elems] swizzle
 constexpr int TILE_BYTES = 2 * BLK;          // [128][128] bf16 as two blocks
 constexpr int ST = 2;                        // K and V ring depth
 constexpr int SMEM_BYTES = (2 + 2 * ST) * TILE_BYTES + 1024 + 1024;   // Q pair, K ring, V ring, barriers, alignment
-constexpr int THREADS = 320;   // TMA / scheduler warp, MMA warp, 2 x 4 softmax warps
+constexpr int THREADS = 384;   // warpgroup 0: TMA / scheduler warp, MMA warp, two idle warps; warpgroups 1, 2: softmax
 constexpr int TMEM_COLS = 512;
 constexpr int S_COL = 0;      // S of tile i: columns [128 i, 128 i + 128); P (bf16x2, 64 cols) over its first 64
 constexpr int O_COL = 256;    // O of tile i: columns [256 + 128 i, ...)
@@ -67,6 +67,18 @@ __device__ __forceinline__ float fast_tanh(float x) {
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// max of three in one instruction
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// The softmax warpgroups keep a whole 128-score row per thread: they take registers from warpgroup 0, whose two
+// working warps need few (setmaxnreg moves the per-thread register limit of a whole warpgroup).
+template <int N>
+__device__ __forceinline__ void reg_dealloc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -132,10 +144,10 @@ __global__ void __launch_bounds__(THREADS, 1)
   uint64_t* v_full = bars + 6 + 2 * ST;
   uint64_t* v_empty = bars + 6 + 3 * ST;
   uint64_t* s_full = bars + 6 + 4 * ST;   // [2]
-  uint64_t* p_full = s_full + 2;          // [2]  4 arrivals (one per softmax warp of the tile)
-  uint64_t* o_done = s_full + 4;          // [2]
-  uint64_t* o_free = s_full + 6;          // [2]  4 arrivals
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 8);
+  uint64_t* p_full = s_full + 2;          // [2 tiles][2 halves of P]  4 arrivals (one per softmax warp of the tile)
+  uint64_t* o_done = s_full + 6;          // [2]
+  uint64_t* o_free = s_full + 8;          // [2]  4 arrivals
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 10);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* item_slot = reinterpret_cast<volatile int*>(tmem_slot + 4);   // [2][4]: pair (< 0: end), h, b
 
@@ -147,7 +159,8 @@ __global__ void __launch_bounds__(THREADS, 1)
       mbar_init(item_full + i, 1);
       mbar_init(item_empty + i, 9);
       mbar_init(s_full + i, 1);
-      mbar_init(p_full + i, 4);
+      mbar_init(p_full + 2 * i, 4);
+      mbar_init(p_full + 2 * i + 1, 4);
       mbar_init(o_done + i, 1);
       mbar_init(o_free + i, 4);
     }
@@ -176,6 +189,7 @@ __global__ void __launch_bounds__(THREADS, 1)
   // lane issues.  A wait that gives up marks the warp `dead`: the loops then run out without issuing anything.
   if (warp == 0) {
     // ---------------- scheduler + TMA producer ----------------
+    reg_dealloc<48>();
     const bool leader = elect_one();
     bool dead = false;
     if (leader) {
@@ -233,6 +247,7 @@ __global__ void __launch_bounds__(THREADS, 1)
     __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
+    reg_dealloc<48>();
     const bool leader = elect_one();
     constexpr uint32_t idesc_s = make_idesc_bf16(TQ, TK, 0, 0);
     constexpr uint32_t idesc_o = make_idesc_bf16(TQ, HD, 0, 1);
@@ -261,10 +276,12 @@ __global__ void __launch_bounds__(THREADS, 1)
       }
     };
     // O_i += P_i V: A = P from TMEM (128 x 16 bf16 per step = 8 columns), B = V as an MN-major operand
-    auto issue_pv = [&](int i, uint32_t st, bool first) {
+    // (issued in two halves of 64 keys, each as soon as its part of P has been written)
+    auto issue_pv = [&](int i, int hf, uint32_t st, bool first) {
       if (leader && !dead) {
 #pragma unroll
-        for (int kk = 0; kk < TK / 16; ++kk) {
+        for (int k4 = 0; k4 < TK / 32; ++k4) {
+          const int kk = hf * (TK / 32) + k4;
           umma_ts_lohi(tmem_base + O_COL + (uint32_t)i * 128u, tmem_base + S_COL + (uint32_t)i * 128u + (uint32_t)kk * 8,
                        v_lo + st * TILE16 + (uint32_t)kk * 128u, v_hi, idesc_o, (!first || kk != 0) ? 1u : 0u);
         }
@@ -305,7 +322,10 @@ __global__ void __launch_bounds__(THREADS, 1)
           if (u == g.lo[0] && !dead) dead = !mbar_wait(o_free, (ce[0] & 1u) ^ 1u, abort_flag, p.status, 504);
           if (!dead) dead = !mbar_wait(p_full, cs[0] & 1u, abort_flag, p.status, 505);
           tc_fence_after_sync();
-          issue_pv(0, st, u == g.lo[0]);
+          issue_pv(0, 0, st, u == g.lo[0]);
+          if (!dead) dead = !mbar_wait(p_full + 1, cs[0] & 1u, abort_flag, p.status, 509);
+          tc_fence_after_sync();
+          issue_pv(0, 1, st, u == g.lo[0]);
           if (u == g.hi[0] && leader && !dead) umma_commit(o_done);
           ++cs[0];
         }
@@ -316,9 +336,12 @@ __global__ void __launch_bounds__(THREADS, 1)
         }
         if (in1) {
           if (u == g.lo[1] && !dead) dead = !mbar_wait(o_free + 1, (ce[1] & 1u) ^ 1u, abort_flag, p.status, 507);
-          if (!dead) dead = !mbar_wait(p_full + 1, cs[1] & 1u, abort_flag, p.status, 508);
+          if (!dead) dead = !mbar_wait(p_full + 2, cs[1] & 1u, abort_flag, p.status, 508);
           tc_fence_after_sync();
-          issue_pv(1, st, u == g.lo[1]);
+          issue_pv(1, 0, st, u == g.lo[1]);
+          if (!dead) dead = !mbar_wait(p_full + 3, cs[1] & 1u, abort_flag, p.status, 510);
+          tc_fence_after_sync();
+          issue_pv(1, 1, st, u == g.lo[1]);
           if (u == g.hi[1] && leader && !dead) umma_commit(o_done + 1);
           ++cs[1];
         }
@@ -336,9 +359,12 @@ __global__ void __launch_bounds__(THREADS, 1)
       ++n_item;
     }
     __syncwarp();
+  } else if (warp < 4) {
+    reg_dealloc<48>();   // the rest of warpgroup 0 has no work; the instruction is per warpgroup
   } else {
     // ---------------- softmax + output: one warpgroup per query tile, thread <-> query row ----------------
-    const int tile = (warp - 2) >> 2;          // 0: warps 2-5, 1: warps 6-9
+    reg_alloc<224>();
+    const int tile = (warp - 4) >> 2;          // 0: warps 4-7, 1: warps 8-11
     const int qd = warp & 3;                   // TMEM lane quarter this warp may access
     const int row = qd * 32 + lane;
     const uint32_t t_lane = tmem_base + ((uint32_t)(qd * 32) << 16);
@@ -374,40 +400,70 @@ __global__ void __launch_bounds__(THREADS, 1)
         tc_fence_after_sync();
         const bool need_mask = (kv0 + TK > p.Sk) || (p.causal && kv0 + TK - 1 > qp0) ||
                                (p.window >= 0 && kv0 < qp0 + TQ - 1 - p.window);
-        // the whole score row in registers, for both the maximum and the exponentials
+        // the whole score row in registers, for both the maximum and the exponentials; the second half of the row is
+        // still on its way from TMEM while the maximum of the first half is taken
         uint32_t r[4][32];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld32(t_s + (uint32_t)c * 32u, r[c]);
+        tmem_ld32(t_s, r[0]);
+        tmem_ld32(t_s + 32u, r[1]);
         tmem_ld_wait();
-        if (capped) {
+        tmem_ld32(t_s + 64u, r[2]);
+        tmem_ld32(t_s + 96u, r[3]);
+        float mx;
+        if (!capped && !need_mask) {
+          // eight independent chains: a single running maximum would serialise 128 dependent operations
+          float m8[8];
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+          for (int k = 0; k < 8; ++k)
+            m8[k] = fmax3(__uint_as_float(r[0][k]), __uint_as_float(r[0][k + 8]), __uint_as_float(r[0][k + 16]));
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              r[c][i] = __float_as_uint(p.cap_log2 * fast_tanh(__uint_as_float(r[c][i]) * p.scale_over_cap));
-        }
-        if (need_mask) {
+          for (int k = 0; k < 8; ++k)
+            m8[k] = fmax3(m8[k], __uint_as_float(r[0][k + 24]), __uint_as_float(r[1][k]));
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+          for (int k = 0; k < 8; ++k)
+            m8[k] = fmax3(m8[k], __uint_as_float(r[1][k + 8]), __uint_as_float(r[1][k + 16]));
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int kv = kv0 + c * 32 + i;
-              if (kv > kv_hi || kv < kv_lo) r[c][i] = __float_as_uint(-INFINITY);
+          for (int k = 0; k < 8; ++k)
+            m8[k] = fmax3(m8[k], __uint_as_float(r[1][k + 24]), __uint_as_float(r[2][k]));
+#pragma unroll
+          for (int c = 2; c < 4; ++c)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              m8[k] = fmax3(m8[k], __uint_as_float(r[c][k + 8]), __uint_as_float(r[c][k + 16]));
+              if (c == 2) m8[k] = fmax3(m8[k], __uint_as_float(r[2][k + 24]), __uint_as_float(r[3][k]));
+              else m8[k] = fmaxf(m8[k], __uint_as_float(r[3][k + 24]));
             }
+          mx = fmax3(fmax3(m8[0], m8[1], m8[2]), fmax3(m8[3], m8[4], m8[5]), fmaxf(m8[6], m8[7]));
+        } else {
+          tmem_ld_wait();
+          if (capped) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                r[c][i] = __float_as_uint(p.cap_log2 * fast_tanh(__uint_as_float(r[c][i]) * p.scale_over_cap));
+          }
+          if (need_mask) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const int kv = kv0 + c * 32 + i;
+                if (kv > kv_hi || kv < kv_lo) r[c][i] = __float_as_uint(-INFINITY);
+              }
+          }
+          float m8[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) m8[k] = -INFINITY;
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; i += 16)
+#pragma unroll
+              for (int k = 0; k < 8; ++k)
+                m8[k] = fmax3(m8[k], __uint_as_float(r[c][i + k]), __uint_as_float(r[c][i + 8 + k]));
+          mx = fmax3(fmax3(m8[0], m8[1], m8[2]), fmax3(m8[3], m8[4], m8[5]), fmaxf(m8[6], m8[7]));
         }
-        // eight independent chains: a single running maximum (or sum, below) would serialise 128 dependent operations
-        float mx8[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(__uint_as_float(r[0][i]), __uint_as_float(r[0][i + 8]));
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = (c == 0 ? 16 : 0); i < 32; i += 16)
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-              mx8[k] = fmaxf(mx8[k], fmaxf(__uint_as_float(r[c][i + k]), __uint_as_float(r[c][i + 8 + k])));
-        float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                         fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
         mx *= sc;                                        // sc > 0: max commutes with the scaling
         const float m_new = fmaxf(m_run, mx);
         // lazy rescale: raise the running max only when it grows by more than 8 (factor 256); warp-uniform decision
@@ -417,13 +473,13 @@ __global__ void __launch_bounds__(THREADS, 1)
           const float alpha = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_next);
           if (u > g.lo[tile]) {
 #pragma unroll 1
-            for (int c = 0; c < 128; c += 32) {
-              uint32_t o[32];
-              tmem_ld32(t_o + (uint32_t)c, o);
+            for (int c = 0; c < 128; c += 16) {
+              uint32_t o[16];
+              tmem_ld16(t_o + (uint32_t)c, o);
               tmem_ld_wait();
 #pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-              tmem_st32(t_o + (uint32_t)c, o);
+              for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st16(t_o + (uint32_t)c, o);
             }
             tmem_st_wait();
           }
@@ -431,7 +487,9 @@ __global__ void __launch_bounds__(THREADS, 1)
           m_run = m_next;
         }
         const float neg_m = (m_run == -INFINITY) ? 0.f : -m_run;
-        // P = exp2(s - m) as bf16 pairs, written over the S columns (the scores are all in registers by now)
+        // P = exp2(s - m) as bf16 pairs, written over the S columns (the scores are all in registers by now).  The
+        // first half of P is announced while the third quarter is being computed, so that the first half of P V runs
+        // under the rest of the exponentials.
         float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -444,12 +502,19 @@ __global__ void __launch_bounds__(THREADS, 1)
             pk[i >> 1] = pack_bf16x2(e0, e1);
           }
           tmem_st16(t_s + (uint32_t)c * 16u, pk);
+          if (c == 2) {
+            // the stores of quarters 0 and 1 have had a quarter's worth of exponentials to land
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full + 2 * tile);
+          }
         }
         l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
         tmem_st_wait();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(p_full + tile);
+        if (lane == 0) mbar_arrive(p_full + 2 * tile + 1);
       }
       // epilogue: wait for the last P V, normalise, store
       if (ok) ok = mbar_wait(o_done + tile, ce & 1u, abort_flag, p.status, 602);
