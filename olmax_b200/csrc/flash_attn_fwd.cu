@@ -218,14 +218,6 @@ __global__ void __launch_bounds__(THREADS, 1)
       }
       if (pair < 0) break;
       const Geo g = item_geometry(p, pair, h, b);
-      dead = !mbar_wait(q_empty, (n_item & 1u) ^ 1u, abort_flag, p.status, 401);
-      if (leader && !dead) {
-        mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
-        tma_load_4d(sQ, &tmQ, q_full, 0, h, g.q0, b);
-        tma_load_4d(sQ + BLK, &tmQ, q_full, 64, h, g.q0, b);
-        tma_load_4d(sQ + TILE_BYTES, &tmQ, q_full, 0, h, g.q0 + TQ, b);
-        tma_load_4d(sQ + TILE_BYTES + BLK, &tmQ, q_full, 64, h, g.q0 + TQ, b);
-      }
       for (int u = g.ulo; u <= g.uhi; ++u, ++k_it) {
         const uint32_t st = k_it % ST, ph = (k_it / ST) & 1u;
         const int kv0 = u * TK;
@@ -234,6 +226,17 @@ __global__ void __launch_bounds__(THREADS, 1)
           mbar_arrive_expect_tx(k_full + st, TILE_BYTES);
           tma_load_4d(sK + st * TILE_BYTES, &tmK, k_full + st, 0, g.hkv, kv0, b);
           tma_load_4d(sK + st * TILE_BYTES + BLK, &tmK, k_full + st, 64, g.hkv, kv0, b);
+        }
+        if (u == g.ulo) {
+          // Q after the first K tile: that one can already travel while the previous item's last Q K^T runs
+          if (!dead) dead = !mbar_wait(q_empty, (n_item & 1u) ^ 1u, abort_flag, p.status, 401);
+          if (leader && !dead) {
+            mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
+            tma_load_4d(sQ, &tmQ, q_full, 0, h, g.q0, b);
+            tma_load_4d(sQ + BLK, &tmQ, q_full, 64, h, g.q0, b);
+            tma_load_4d(sQ + TILE_BYTES, &tmQ, q_full, 0, h, g.q0 + TQ, b);
+            tma_load_4d(sQ + TILE_BYTES + BLK, &tmQ, q_full, 64, h, g.q0 + TQ, b);
+          }
         }
         if (!dead) dead = !mbar_wait(v_empty + st, ph ^ 1u, abort_flag, p.status, 403);
         if (leader && !dead) {
