@@ -35,8 +35,8 @@ constexpr int TK = 128;   // keys per iteration
 constexpr int HD = 128;   // head dim
 constexpr int BLK = 128 * 64 * 2;            // one [128 rows][64 elems] swizzled block: 16 KiB
 constexpr int TILE_BYTES = 2 * BLK;          // [128][128] bf16 as two blocks
-constexpr int ST = 2;                        // K and V ring depth
-constexpr int SMEM_BYTES = (2 + 2 * ST) * TILE_BYTES + 1024 + 1024;   // Q pair, K ring, V ring, barriers, alignment
+constexpr int STK = 3, STV = 2;             // K and V ring depths (K is needed one MMA group earlier than V)
+constexpr int SMEM_BYTES = (2 + STK + STV) * TILE_BYTES + 1024 + 1024;   // Q pair, K ring, V ring, barriers, alignment
 constexpr int THREADS = 384;   // warpgroup 0: TMA / scheduler warp, MMA warp, two idle warps; warpgroups 1, 2: softmax
 constexpr int TMEM_COLS = 512;
 constexpr int S_COL = 0;      // S of tile i: columns [128 i, 128 i + 128); P (bf16x2, 64 cols) over its first 64
@@ -132,18 +132,18 @@ __global__ void __launch_bounds__(THREADS, 1)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;                              // two tiles
-  uint8_t* sK = smem + 2 * TILE_BYTES;             // ST tiles
-  uint8_t* sV = smem + (2 + ST) * TILE_BYTES;      // ST tiles
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (2 + 2 * ST) * TILE_BYTES);
+  uint8_t* sK = smem + 2 * TILE_BYTES;             // STK tiles
+  uint8_t* sV = smem + (2 + STK) * TILE_BYTES;     // STV tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (2 + STK + STV) * TILE_BYTES);
   uint64_t* item_full = bars + 0;     // [2]
   uint64_t* item_empty = bars + 2;    // [2]  9 arrivals: MMA warp + 8 softmax warps
   uint64_t* q_full = bars + 4;
   uint64_t* q_empty = bars + 5;
-  uint64_t* k_full = bars + 6;        // [ST]
-  uint64_t* k_empty = bars + 6 + ST;
-  uint64_t* v_full = bars + 6 + 2 * ST;
-  uint64_t* v_empty = bars + 6 + 3 * ST;
-  uint64_t* s_full = bars + 6 + 4 * ST;   // [2]
+  uint64_t* k_full = bars + 6;        // [STK]
+  uint64_t* k_empty = bars + 6 + STK;
+  uint64_t* v_full = bars + 6 + 2 * STK;   // [STV]
+  uint64_t* v_empty = bars + 6 + 2 * STK + STV;
+  uint64_t* s_full = bars + 6 + 2 * STK + 2 * STV;   // [2]
   uint64_t* p_full = s_full + 2;          // [2 tiles][2 halves of P]  4 arrivals (one per softmax warp of the tile)
   uint64_t* o_done = s_full + 6;          // [2]
   uint64_t* o_free = s_full + 8;          // [2]  4 arrivals
@@ -166,9 +166,11 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
     mbar_init(q_full, 1);
     mbar_init(q_empty, 1);
-    for (int i = 0; i < ST; ++i) {
+    for (int i = 0; i < STK; ++i) {
       mbar_init(k_full + i, 1);
       mbar_init(k_empty + i, 1);
+    }
+    for (int i = 0; i < STV; ++i) {
       mbar_init(v_full + i, 1);
       mbar_init(v_empty + i, 1);
     }
@@ -218,31 +220,34 @@ __global__ void __launch_bounds__(THREADS, 1)
       }
       if (pair < 0) break;
       const Geo g = item_geometry(p, pair, h, b);
-      for (int u = g.ulo; u <= g.uhi; ++u, ++k_it) {
-        const uint32_t st = k_it % ST, ph = (k_it / ST) & 1u;
-        const int kv0 = u * TK;
+      // K runs one tile ahead of V: the MMA warp issues Q K^T of tile u + 1 before P V of tile u
+      auto load_k = [&](int u, uint32_t it) {
+        const uint32_t st = it % STK, ph = (it / STK) & 1u;
         if (!dead) dead = !mbar_wait(k_empty + st, ph ^ 1u, abort_flag, p.status, 402);
         if (leader && !dead) {
           mbar_arrive_expect_tx(k_full + st, TILE_BYTES);
-          tma_load_4d(sK + st * TILE_BYTES, &tmK, k_full + st, 0, g.hkv, kv0, b);
-          tma_load_4d(sK + st * TILE_BYTES + BLK, &tmK, k_full + st, 64, g.hkv, kv0, b);
+          tma_load_4d(sK + st * TILE_BYTES, &tmK, k_full + st, 0, g.hkv, u * TK, b);
+          tma_load_4d(sK + st * TILE_BYTES + BLK, &tmK, k_full + st, 64, g.hkv, u * TK, b);
         }
-        if (u == g.ulo) {
-          // Q after the first K tile: that one can already travel while the previous item's last Q K^T runs
-          if (!dead) dead = !mbar_wait(q_empty, (n_item & 1u) ^ 1u, abort_flag, p.status, 401);
-          if (leader && !dead) {
-            mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
-            tma_load_4d(sQ, &tmQ, q_full, 0, h, g.q0, b);
-            tma_load_4d(sQ + BLK, &tmQ, q_full, 64, h, g.q0, b);
-            tma_load_4d(sQ + TILE_BYTES, &tmQ, q_full, 0, h, g.q0 + TQ, b);
-            tma_load_4d(sQ + TILE_BYTES + BLK, &tmQ, q_full, 64, h, g.q0 + TQ, b);
-          }
-        }
+      };
+      load_k(g.ulo, k_it);
+      // Q after the first K tile: that one can already travel while the previous item's last Q K^T runs
+      if (!dead) dead = !mbar_wait(q_empty, (n_item & 1u) ^ 1u, abort_flag, p.status, 401);
+      if (leader && !dead) {
+        mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
+        tma_load_4d(sQ, &tmQ, q_full, 0, h, g.q0, b);
+        tma_load_4d(sQ + BLK, &tmQ, q_full, 64, h, g.q0, b);
+        tma_load_4d(sQ + TILE_BYTES, &tmQ, q_full, 0, h, g.q0 + TQ, b);
+        tma_load_4d(sQ + TILE_BYTES + BLK, &tmQ, q_full, 64, h, g.q0 + TQ, b);
+      }
+      for (int u = g.ulo; u <= g.uhi; ++u, ++k_it) {
+        if (u < g.uhi) load_k(u + 1, k_it + 1);
+        const uint32_t st = k_it % STV, ph = (k_it / STV) & 1u;
         if (!dead) dead = !mbar_wait(v_empty + st, ph ^ 1u, abort_flag, p.status, 403);
         if (leader && !dead) {
           mbar_arrive_expect_tx(v_full + st, TILE_BYTES);
-          tma_load_4d(sV + st * TILE_BYTES, &tmV, v_full + st, 0, g.hkv, kv0, b);
-          tma_load_4d(sV + st * TILE_BYTES + BLK, &tmV, v_full + st, 64, g.hkv, kv0, b);
+          tma_load_4d(sV + st * TILE_BYTES, &tmV, v_full + st, 0, g.hkv, u * TK, b);
+          tma_load_4d(sV + st * TILE_BYTES + BLK, &tmV, v_full + st, 64, g.hkv, u * TK, b);
         }
       }
       ++n_item;
@@ -304,7 +309,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       dead = !mbar_wait(q_full, n_item & 1u, abort_flag, p.status, 501);
       // first K tile: S of both query tiles
       {
-        const uint32_t st = k_it % ST, ph = (k_it / ST) & 1u;
+        const uint32_t st = k_it % STK, ph = (k_it / STK) & 1u;
         if (!dead) dead = !mbar_wait(k_full + st, ph, abort_flag, p.status, 502);
         tc_fence_after_sync();
         issue_s(0, st);
@@ -315,8 +320,8 @@ __global__ void __launch_bounds__(THREADS, 1)
         }
       }
       for (int u = g.ulo; u <= g.uhi; ++u, ++k_it) {
-        const uint32_t st = k_it % ST, ph = (k_it / ST) & 1u;
-        const uint32_t st_n = (k_it + 1) % ST, ph_n = ((k_it + 1) / ST) & 1u;
+        const uint32_t st = k_it % STV, ph = (k_it / STV) & 1u;                 // V stage of tile u
+        const uint32_t st_n = (k_it + 1) % STK, ph_n = ((k_it + 1) / STK) & 1u;   // K stage of tile u + 1
         const bool more = u < g.uhi;
         const bool in0 = u <= g.hi[0];
         const bool in1 = act1 && u >= g.lo[1] && u <= g.hi[1];

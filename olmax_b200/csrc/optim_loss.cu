@@ -263,10 +263,11 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float
   const float gs = gscale != nullptr ? *gscale : 1.f;
   const long long n4 = n / 4;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
-    float4 pv = reinterpret_cast<float4*>(p)[i];
-    float4 mv = reinterpret_cast<float4*>(m)[i];
-    float4 vv = reinterpret_cast<float4*>(v)[i];
-    float4 gv = reinterpret_cast<float4*>(g)[i];
+    // streaming accesses: nothing of the optimizer state is read again before it has left the L2
+    float4 pv = __ldcs(reinterpret_cast<const float4*>(p) + i);
+    float4 mv = __ldcs(reinterpret_cast<const float4*>(m) + i);
+    float4 vv = __ldcs(reinterpret_cast<const float4*>(v) + i);
+    float4 gv = __ldcs(reinterpret_cast<const float4*>(g) + i);
     float pa[4] = {pv.x, pv.y, pv.z, pv.w}, ma[4] = {mv.x, mv.y, mv.z, mv.w}, va[4] = {vv.x, vv.y, vv.z, vv.w},
           ga[4] = {gv.x, gv.y, gv.z, gv.w};
 #pragma unroll
@@ -277,15 +278,15 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float
       const float mh = ma[j] * inv_bc1, vh = va[j] * inv_bc2;
       pa[j] -= lr * (mh / (sqrtf(vh) + eps) + wd * pa[j]);
     }
-    reinterpret_cast<float4*>(p)[i] = make_float4(pa[0], pa[1], pa[2], pa[3]);
-    reinterpret_cast<float4*>(m)[i] = make_float4(ma[0], ma[1], ma[2], ma[3]);
-    reinterpret_cast<float4*>(v)[i] = make_float4(va[0], va[1], va[2], va[3]);
-    if (zero_grad) reinterpret_cast<float4*>(g)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    __stcs(reinterpret_cast<float4*>(p) + i, make_float4(pa[0], pa[1], pa[2], pa[3]));
+    __stcs(reinterpret_cast<float4*>(m) + i, make_float4(ma[0], ma[1], ma[2], ma[3]));
+    __stcs(reinterpret_cast<float4*>(v) + i, make_float4(va[0], va[1], va[2], va[3]));
+    if (zero_grad) __stcs(reinterpret_cast<float4*>(g) + i, make_float4(0.f, 0.f, 0.f, 0.f));
     if (shadow != nullptr) {
       uint2 s;
       s.x = pack_bf16x2(pa[0], pa[1]);
       s.y = pack_bf16x2(pa[2], pa[3]);
-      reinterpret_cast<uint2*>(shadow)[i] = s;
+      __stcs(reinterpret_cast<uint2*>(shadow) + i, s);
     }
   }
   // tail (n not a multiple of 4)
