@@ -98,6 +98,9 @@ def comm_selfcheck(args, model_cfg, mesh, mesh_res, dev, seq, inst_local, k):
                 optim.accumulate()
                 losses.append(loss.detach().float())
             if step == 0:
+                # peers add their embedding / norm-weight contributions straight into this rank's accumulator: they
+                # have all landed only after the barrier that the optimizer step would begin with
+                model.store.sync_peers()
                 first_grad = model.store.grad.detach().clone()
             optim.step()
         torch.cuda.synchronize()

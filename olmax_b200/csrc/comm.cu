@@ -81,6 +81,34 @@ __global__ void __launch_bounds__(AR_THREADS)
   }
 }
 
+// The same fold for bf16 slots (the reduce-scatter wire format that halves the bytes crossing NVLink and read here):
+// acc[i] += scale * sum_r float(stage[r * slot_stride + i]); n8 groups of 8 elements, slot_stride in elements.
+__global__ void __launch_bounds__(AR_THREADS)
+    reduce_slots_bf16_kernel(const bf16* __restrict__ stage, float* __restrict__ acc, long long n8, int R,
+                             long long slot_stride, float scale) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float sum[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sum[e] = 0.f;
+    for (int r = 0; r < R; ++r) {
+      const uint4 v = __ldcs(reinterpret_cast<const uint4*>(stage + r * slot_stride) + i);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = unpack_bf16x2(w[e]);
+        sum[2 * e] += f.x;
+        sum[2 * e + 1] += f.y;
+      }
+    }
+    float4* a = reinterpret_cast<float4*>(acc) + 2 * i;
+    float4 a0 = a[0], a1 = a[1];
+    a0.x += scale * sum[0]; a0.y += scale * sum[1]; a0.z += scale * sum[2]; a0.w += scale * sum[3];
+    a1.x += scale * sum[4]; a1.y += scale * sum[5]; a1.z += scale * sum[6]; a1.w += scale * sum[7];
+    a[0] = a0;
+    a[1] = a1;
+  }
+}
+
 // out[i] = (accumulate ? out[i] : 0) + sum over slots r != skip of stage[r * slot_stride + i], bf16 storage, fp32 sums
 __global__ void __launch_bounds__(AR_THREADS)
     fold_slots_bf16_kernel(bf16* __restrict__ out, const bf16* __restrict__ stage, long long n8,
@@ -295,6 +323,19 @@ extern "C" int ob_allreduce_multimem_f32(float* mc, long long n, int me, int wor
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   allreduce_multimem_kernel<<<(unsigned)blocks, AR_THREADS, 0, stream>>>(mc, n, me, world);
+  OB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int ob_reduce_slots_bf16(const void* stage, float* acc, long long n, int R, long long slot_stride, float scale,
+                                    cudaStream_t stream) {
+  if (n <= 0 || R <= 0) return 0;
+  if (n % 8 != 0 || slot_stride % 8 != 0) OB_FAIL(-1, "reduce_slots_bf16: element counts must be multiples of 8");
+  long long blocks = (n / 8 + AR_THREADS - 1) / AR_THREADS;
+  const long long cap = 8LL * sm_count();
+  if (blocks > cap) blocks = cap;
+  reduce_slots_bf16_kernel<<<(unsigned)blocks, AR_THREADS, 0, stream>>>((const bf16*)stage, acc, n / 8, R, slot_stride,
+                                                                        scale);
   OB_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -17,6 +17,9 @@ int ob_allreduce_multimem_f32(float* mc, long long n, int me, int world, int max
 // acc[i] += scale * sum over r < R of stage[r * slot_stride + i]   (fp32, local memory)
 int ob_reduce_slots_f32(const float* stage, float* acc, long long n, int R, long long slot_stride, float scale,
                         cudaStream_t stream);
+// the same with bf16 slots (n and slot_stride multiples of 8 elements)
+int ob_reduce_slots_bf16(const void* stage, float* acc, long long n, int R, long long slot_stride, float scale,
+                        cudaStream_t stream);
 
 // Stream-ordered barrier of n GPUs over peer memory: flags = DEVICE array of the members' flag arrays (n words each,
 // zero-initialised, peer-mapped), epoch = 1, 2, 3, ... (the same sequence on every member).  A member that does not see

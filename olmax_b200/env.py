@@ -37,6 +37,10 @@ class RuntimeConfig:
     peer_barrier: str = "flags"
     """How the peer-memory backend separates its phases: ``flags`` (the bounded flag-word barrier kernel, default) or
     ``nccl`` (a one-element all-reduce); ``OLMAX_B200_BARRIER``."""
+    rs_wire: str = "fp32"
+    """Format of the partial weight gradients that the fused reduce-scatter stores into the owners' staging slots:
+    ``fp32``, or ``bf16`` (half the NVLink bytes and half the fold's reads; each rank's partial sum is rounded once,
+    sums and the accumulator stay fp32); ``OLMAX_B200_RS_WIRE``."""
     peer_wait_timeout_ms: int = 600_000
     """Upper bound of the flag barrier's wait for another GPU (``OLMAX_B200_BARRIER_TIMEOUT_S``); a wait that runs out
     raises on the host instead of hanging the GPU.  The waits inside the GEMMs have a fixed iteration limit."""
@@ -51,6 +55,7 @@ class RuntimeConfig:
     def apply(self) -> None:
         set_env_var("OLMAX_B200_COMM_BACKEND", self.comm_backend, override=True)
         set_env_var("OLMAX_B200_BARRIER", self.peer_barrier, override=True)
+        set_env_var("OLMAX_B200_RS_WIRE", self.rs_wire, override=True)
         set_env_var("OLMAX_B200_BARRIER_TIMEOUT_S", str(self.peer_wait_timeout_ms / 1000.0), override=True)
         set_env_var("OLMAX_B200_NVTX", "1" if self.nvtx else "0", override=True)
 

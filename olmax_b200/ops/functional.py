@@ -115,7 +115,8 @@ def _gemm_wgrad(dy2: torch.Tensor, x2: torch.Tensor, handle) -> None:
     if peer is not None:
         # reduce-scatter fused into the epilogue: row block r is STORED into this rank's slot of GPU r's staging buffer
         # (plain stores over NVLink, rank-staggered tile order); the owner folds the slots after the unit's barrier
-        K.gemm(dy2, x2, handle.local_grad, N, Kd, M, a_mn=True, b_mn=True, epi=K.EPI_F32, alpha=1.0, ldc=Kd,
+        epi = K.EPI_BF16 if symm.wire_dtype == torch.bfloat16 else K.EPI_F32
+        K.gemm(dy2, x2, handle.local_grad, N, Kd, M, a_mn=True, b_mn=True, epi=epi, alpha=1.0, ldc=Kd,
                M_s=handle.rows_local, c_shards=peer, prefetch=pf, m_shard_rot=handle.store.mesh.shard.rank)
         handle.unit._staged.add(handle.name)
     else:

@@ -85,6 +85,7 @@ register_signature("ob_scatter_add_shards", [_vp, _vp, _ll, _i, _f, _vp])
 register_signature("ob_allreduce_p2p_f32", [_vp, _ll, _i, _i, _f, _i, _vp])
 register_signature("ob_allreduce_multimem_f32", [_vp, _ll, _i, _i, _i, _vp])
 register_signature("ob_reduce_slots_f32", [_vp, _vp, _ll, _i, _ll, _f, _vp])
+register_signature("ob_reduce_slots_bf16", [_vp, _vp, _ll, _i, _ll, _f, _vp])
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -457,9 +458,9 @@ def fold_slots_bf16(out, stage, n, slots, slot_stride, *, skip=-1, accumulate=Fa
 
 
 def reduce_slots(stage, acc, n, R, slot_stride, scale=1.0) -> None:
-    """acc[:n] += scale * sum_r stage[r * slot_stride : r * slot_stride + n] (fp32, local)."""
-    check(lib().ob_reduce_slots_f32(stage.data_ptr(), acc.data_ptr(), n, R, slot_stride, scale, stream_ptr(acc.device)),
-          "reduce_slots")
+    """acc[:n] += scale * sum_r stage[r * slot_stride : r * slot_stride + n] (fp32 accumulator; fp32 or bf16 slots)."""
+    fn = lib().ob_reduce_slots_bf16 if stage.dtype == torch.bfloat16 else lib().ob_reduce_slots_f32
+    check(fn(stage.data_ptr(), acc.data_ptr(), n, R, slot_stride, scale, stream_ptr(acc.device)), "reduce_slots")
     _count()
 
 

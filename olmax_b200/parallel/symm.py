@@ -163,17 +163,29 @@ class SymmContext:
         # (index % 3): a buffer is written again for unit u-3 only after this rank has passed wait(u-1), and a member
         # publishes (u-1) only after its fold(u), the previous user of that buffer.
         self.stage_slot = max((u.numel_local for u in store.units), default=0)
+        self.stage_slot = (self.stage_slot + 7) // 8 * 8
         self.rs_stage = None
         self.stage_ptrs: List[int] = []
+        # Wire format of the staged partial gradients: fp32, or bf16 (half the bytes over NVLink and in the fold; each
+        # rank's partial sum is rounded once, the fold and the accumulator stay fp32).  bf16 needs every parameter's
+        # local slice to start and end on a multiple of 8 elements.
+        wire = os.environ.get("OLMAX_B200_RS_WIRE", "fp32")
+        if wire not in ("fp32", "bf16"):
+            raise ValueError(f"OLMAX_B200_RS_WIRE must be fp32 or bf16, got {wire!r}")
+        if wire == "bf16" and any(h.meta.unit_offset % 8 or h.meta.numel_local % 8 for u in store.units for h in u.params):
+            log.warning("bf16 reduce-scatter wire needs 8-element aligned parameter slices; using fp32")
+            wire = "fp32"
+        self.wire_dtype = torch.bfloat16 if wire == "bf16" else torch.float32
+        self.wire_bytes = 2 if wire == "bf16" else 4
         if self.R > 1 and os.environ.get("OLMAX_B200_FUSED_RS", "1") == "1":
             # guard words before and after the staging area: peers only ever store inside it (check_canaries)
             n_stage = self.N_STAGE * self.R * self.stage_slot
-            self._stage_alloc = symm_mem.empty(n_stage + 2 * self.GUARD, dtype=torch.float32, device=dev)
+            self._stage_alloc = symm_mem.empty(n_stage + 2 * self.GUARD, dtype=self.wire_dtype, device=dev)
             self._stage_alloc[: self.GUARD] = self.CANARY
             self._stage_alloc[self.GUARD + n_stage:] = self.CANARY
             self.rs_stage = self._stage_alloc[self.GUARD : self.GUARD + n_stage]
             self._h_stage = symm_mem.rendezvous(self._stage_alloc, world)
-            all_stage = [int(p) + self.GUARD * 4 for p in self._h_stage.buffer_ptrs]
+            all_stage = [int(p) + self.GUARD * self.wire_bytes for p in self._h_stage.buffer_ptrs]
             self.stage_ptrs = [all_stage[r] for r in mesh.shard.ranks]
         self.flags = torch.zeros(max(1, self.R) * 4096, dtype=torch.int32, device=dev)
         self._rs_pending = None   # (unit, names, barrier token) of the unit whose fold is still to come
@@ -208,7 +220,7 @@ class SymmContext:
         key = ("stage", handle.name, buf)
         t = self._tables.get(key)
         if t is None:
-            off = ((buf * self.R + self.rank) * self.stage_slot + handle.meta.unit_offset) * 4
+            off = ((buf * self.R + self.rank) * self.stage_slot + handle.meta.unit_offset) * self.wire_bytes
             t = K.pointer_table([p + off for p in self.stage_ptrs], self.store.device)
             self._tables[key] = t
         return t

@@ -182,12 +182,13 @@ def test_small_shard_helpers():
     _check()
 
 
-def _train_worker(backend, mesh_kind="fsdp", barrier="nccl"):
+def _train_worker(backend, mesh_kind="fsdp", barrier="nccl", wire="fp32"):
     import os
 
     import torch.distributed as dist
 
     os.environ["OLMAX_B200_BARRIER"] = barrier   # read when the peer-memory context is built
+    os.environ["OLMAX_B200_RS_WIRE"] = wire      # likewise: format of the staged partial gradients
 
     from olmax_b200.models import DefaultTransformerConfig, ReorderedNormTransformerLayerConfig
     from olmax_b200.nn import MultiheadSelfAttentionConfig, RMSNormConfig
@@ -216,6 +217,7 @@ def _train_worker(backend, mesh_kind="fsdp", barrier="nccl"):
             loss.backward()
             optim.accumulate()
         if step == 0:
+            model.store.sync_peers()   # the peers' direct additions (embedding, norm weights) have landed after this
             first_grads = model.store.grad.clone()
         optim.step()
         losses.append(loss.item())
@@ -227,13 +229,15 @@ def _train_worker(backend, mesh_kind="fsdp", barrier="nccl"):
     return losses, first_grads.cpu(), full
 
 
-@pytest.mark.parametrize("mesh_kind,world,barrier", [("fsdp", 2, "nccl"), ("fsdp", 2, "flags"), ("ddp", 2, "nccl"),
-                                                      ("hsdp", 4, "nccl")])
-def test_peer_memory_backend_matches_nccl(mesh_kind, world, barrier):
+@pytest.mark.parametrize("mesh_kind,world,barrier,wire", [
+    ("fsdp", 2, "nccl", "fp32"), ("fsdp", 2, "flags", "fp32"), ("ddp", 2, "nccl", "fp32"), ("hsdp", 4, "nccl", "fp32"),
+    ("fsdp", 2, "flags", "bf16"),   # partial weight gradients cross NVLink as bf16
+])
+def test_peer_memory_backend_matches_nccl(mesh_kind, world, barrier, wire):
     if not torch.cuda.is_available() or torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    fused = run_distributed_test(_train_worker, world_size=world, backend="nccl", func_args=("fused", mesh_kind, barrier),
-                                 timeout=300)
+    fused = run_distributed_test(_train_worker, world_size=world, backend="nccl",
+                                 func_args=("fused", mesh_kind, barrier, wire), timeout=300)
     nccl = run_distributed_test(_train_worker, world_size=world, backend="nccl", func_args=("nccl", mesh_kind), timeout=300)
     for r in range(world):
         lf, gf, pf = fused[r]

@@ -373,6 +373,19 @@ def test_fused_rmsnorm_rope_matches_the_two_kernels_and_the_fp32_reference(K, B,
     _check_status()
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_reduce_slots_folds_fp32_and_bf16_staging(K, dtype):
+    dev = "cuda"
+    torch.manual_seed(12)
+    R, n, stride = 4, 8 * 1000, 8 * 1300
+    stage = torch.randn(R * stride, device=dev).to(dtype)
+    acc = torch.randn(n, device=dev)
+    want = acc + 0.25 * stage.view(R, stride)[:, :n].float().sum(0)
+    K.reduce_slots(stage, acc, n, R, stride, 0.25)
+    assert rel_err(acc, want) < 1e-6
+    _check_status()
+
+
 def test_embedding_kernels(K):
     dev = torch.device("cuda")
     torch.manual_seed(6)
