@@ -37,10 +37,12 @@ class RuntimeConfig:
     peer_barrier: str = "flags"
     """How the peer-memory backend separates its phases: ``flags`` (the bounded flag-word barrier kernel, default) or
     ``nccl`` (a one-element all-reduce); ``OLMAX_B200_BARRIER``."""
-    rs_wire: str = "fp32"
+    rs_wire: str = "bf16"
     """Format of the partial weight gradients that the fused reduce-scatter stores into the owners' staging slots:
-    ``fp32``, or ``bf16`` (half the NVLink bytes and half the fold's reads; each rank's partial sum is rounded once,
-    sums and the accumulator stay fp32); ``OLMAX_B200_RS_WIRE``."""
+    ``bf16`` (default: half the NVLink bytes and half the fold's reads; each rank's partial sum is rounded once, sums
+    and the accumulator stay fp32) or ``fp32``; ``OLMAX_B200_RS_WIRE``.  The reference takes its gradients with respect
+    to the bf16 copy of the parameters and casts them to fp32 afterwards (``olmax/train/trainer.py:728-739``), so its
+    reduce-scatter moves bf16 as well."""
     peer_wait_timeout_ms: int = 600_000
     """Upper bound of the flag barrier's wait for another GPU (``OLMAX_B200_BARRIER_TIMEOUT_S``); a wait that runs out
     raises on the host instead of hanging the GPU.  The waits inside the GEMMs have a fixed iteration limit."""

@@ -166,10 +166,11 @@ class SymmContext:
         self.stage_slot = (self.stage_slot + 7) // 8 * 8
         self.rs_stage = None
         self.stage_ptrs: List[int] = []
-        # Wire format of the staged partial gradients: fp32, or bf16 (half the bytes over NVLink and in the fold; each
-        # rank's partial sum is rounded once, the fold and the accumulator stay fp32).  bf16 needs every parameter's
-        # local slice to start and end on a multiple of 8 elements.
-        wire = os.environ.get("OLMAX_B200_RS_WIRE", "fp32")
+        # Wire format of the staged partial gradients: bf16 (half the bytes over NVLink and in the fold; each rank's
+        # partial sum is rounded once, the fold and the accumulator stay fp32; the reference reduces bf16 gradients
+        # too, `olmax/train/trainer.py:728-739`) or fp32.  bf16 needs every parameter's local slice to start and end
+        # on a multiple of 8 elements.
+        wire = os.environ.get("OLMAX_B200_RS_WIRE", "bf16")
         if wire not in ("fp32", "bf16"):
             raise ValueError(f"OLMAX_B200_RS_WIRE must be fp32 or bf16, got {wire!r}")
         if wire == "bf16" and any(h.meta.unit_offset % 8 or h.meta.numel_local % 8 for u in store.units for h in u.params):

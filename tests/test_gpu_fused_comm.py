@@ -182,7 +182,7 @@ def test_small_shard_helpers():
     _check()
 
 
-def _train_worker(backend, mesh_kind="fsdp", barrier="nccl", wire="fp32"):
+def _train_worker(backend, mesh_kind="fsdp", barrier="nccl", wire="bf16"):
     import os
 
     import torch.distributed as dist
@@ -230,8 +230,8 @@ def _train_worker(backend, mesh_kind="fsdp", barrier="nccl", wire="fp32"):
 
 
 @pytest.mark.parametrize("mesh_kind,world,barrier,wire", [
-    ("fsdp", 2, "nccl", "fp32"), ("fsdp", 2, "flags", "fp32"), ("ddp", 2, "nccl", "fp32"), ("hsdp", 4, "nccl", "fp32"),
-    ("fsdp", 2, "flags", "bf16"),   # partial weight gradients cross NVLink as bf16
+    ("fsdp", 2, "nccl", "bf16"), ("fsdp", 2, "flags", "bf16"), ("ddp", 2, "nccl", "bf16"), ("hsdp", 4, "nccl", "bf16"),
+    ("fsdp", 2, "flags", "fp32"),   # partial weight gradients cross NVLink as fp32
 ])
 def test_peer_memory_backend_matches_nccl(mesh_kind, world, barrier, wire):
     if not torch.cuda.is_available() or torch.cuda.device_count() < world:
