@@ -25,6 +25,15 @@ __device__ __forceinline__ void load8(const bf16* p, float (&f)[8]) {
     f[2 * i + 1] = t.y;
   }
 }
+__device__ __forceinline__ bf16x8 load_raw8(const bf16* p) { return *reinterpret_cast<const bf16x8*>(p); }
+__device__ __forceinline__ void unpack8(const bf16x8& raw, float (&f)[8]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = unpack_bf16x2(raw.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
 __device__ __forceinline__ void store8(bf16* p, const float (&f)[8]) {
   bf16x8 raw;
 #pragma unroll
@@ -67,6 +76,8 @@ __device__ __forceinline__ long long row_offset(long long row, int heads, long l
 }
 
 // t = x (+ res if add_before);  sum_out = t (optional);  y = t * rstd * w (+ res if !add_before and res given)
+// The elements of the NEXT row group are fetched (as raw bf16) before the current one is reduced, so that loads stay
+// in flight across the two barriers of the block-wide sum.
 template <int TPR, int VPT>
 __global__ void __launch_bounds__(NORM_THREADS)
     rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res, const bf16* __restrict__ w,
@@ -76,22 +87,41 @@ __global__ void __launch_bounds__(NORM_THREADS)
   constexpr int ROWS_PER_BLOCK = NORM_THREADS / TPR;
   const int sub = threadIdx.x / TPR, tr = threadIdx.x % TPR;
   const int nvec = d / 8;
-  for (long long row0 = (long long)blockIdx.x * ROWS_PER_BLOCK; row0 < rows; row0 += (long long)gridDim.x * ROWS_PER_BLOCK) {
+  const long long stride = (long long)gridDim.x * ROWS_PER_BLOCK;
+  const bool with_res = res != nullptr;
+  bf16x8 nx[VPT], nr[VPT];
+  auto fetch = [&](long long row0) {
+    const long long row = row0 + sub;
+    if (row < rows) {
+      const long long ox = row_offset(row, heads, ld_x, d), ores = row_offset(row, heads, ld_res, d);
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int vi = tr + i * TPR;
+        if (vi < nvec) {
+          nx[i] = load_raw8(x + ox + vi * 8);
+          if (with_res) nr[i] = load_raw8(res + ores + vi * 8);
+        }
+      }
+    }
+  };
+  long long row0 = (long long)blockIdx.x * ROWS_PER_BLOCK;
+  if (row0 < rows) fetch(row0);
+  for (; row0 < rows; row0 += stride) {
     const long long row = row0 + sub;
     const bool live = row < rows;
-    const long long ox = live ? row_offset(row, heads, ld_x, d) : 0;
-    const long long ores = live ? row_offset(row, heads, ld_res, d) : 0;
     const long long oy = live ? row_offset(row, heads, ld_y, d) : 0;
     float t[VPT][8];
+    bf16x8 cr[VPT];   // this row's residual, raw (the fetch below overwrites nr)
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int vi = tr + i * TPR;
       if (live && vi < nvec) {
-        load8(x + ox + vi * 8, t[i]);
-        if (res != nullptr && add_before) {
+        unpack8(nx[i], t[i]);
+        if (with_res) cr[i] = nr[i];
+        if (with_res && add_before) {
           float r[8];
-          load8(res + ores + vi * 8, r);
+          unpack8(cr[i], r);
 #pragma unroll
           for (int j = 0; j < 8; ++j) t[i][j] = __bfloat162float(__float2bfloat16(t[i][j] + r[j]));
           if (sum_out != nullptr) store8(sum_out + oy + vi * 8, t[i]);
@@ -100,6 +130,7 @@ __global__ void __launch_bounds__(NORM_THREADS)
         for (int j = 0; j < 8; ++j) ss += t[i][j] * t[i][j];
       }
     }
+    if (row0 + stride < rows) fetch(row0 + stride);
     ss = row_sum<TPR>(ss, red);
     const float rstd = rsqrtf(ss / (float)d + eps);
     if (live && tr == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
@@ -111,9 +142,9 @@ __global__ void __launch_bounds__(NORM_THREADS)
         load8(w + vi * 8, wv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = t[i][j] * rstd * wv[j];
-        if (res != nullptr && !add_before) {
+        if (with_res && !add_before) {
           float r[8];
-          load8(res + ores + vi * 8, r);
+          unpack8(cr[i], r);
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] = __bfloat162float(__float2bfloat16(o[j])) + r[j];
         }
@@ -124,8 +155,9 @@ __global__ void __launch_bounds__(NORM_THREADS)
 }
 
 // dx = rstd * (w*dy - xhat * mean(w*dy*xhat)) (+ dsum);  dw += sum_rows dy * xhat  (fp32 atomics, accumulating)
+// (next row group fetched before the current one is reduced, as in the forward kernel)
 template <int TPR, int VPT>
-__global__ void __launch_bounds__(NORM_THREADS, VPT <= 2 ? 4 : 2)
+__global__ void __launch_bounds__(NORM_THREADS, VPT <= 1 ? 4 : (VPT <= 2 ? 3 : 2))
     rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
                        const float* __restrict__ rstd_in, const bf16* __restrict__ dsum, bf16* __restrict__ dx,
                        float* __restrict__ dw, long long rows, int d, int heads, long long ld_dy, long long ld_x,
@@ -135,18 +167,36 @@ __global__ void __launch_bounds__(NORM_THREADS, VPT <= 2 ? 4 : 2)
   constexpr int ROWS_PER_BLOCK = NORM_THREADS / TPR;
   const int sub = threadIdx.x / TPR, tr = threadIdx.x % TPR;
   const int nvec = d / 8;
+  const long long stride = (long long)gridDim.x * ROWS_PER_BLOCK;
   float dwacc[VPT][8];
 #pragma unroll
   for (int i = 0; i < VPT; ++i)
 #pragma unroll
     for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
-  for (long long row0 = (long long)blockIdx.x * ROWS_PER_BLOCK; row0 < rows; row0 += (long long)gridDim.x * ROWS_PER_BLOCK) {
+  bf16x8 ng[VPT], nx[VPT];
+  float nrstd = 0.f;
+  auto fetch = [&](long long row0) {
+    const long long row = row0 + sub;
+    if (row < rows) {
+      const long long ody = row_offset(row, heads, ld_dy, d), ox = row_offset(row, heads, ld_x, d);
+      nrstd = rstd_in[row];
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int vi = tr + i * TPR;
+        if (vi < nvec) {
+          ng[i] = load_raw8(dy + ody + vi * 8);
+          nx[i] = load_raw8(x + ox + vi * 8);
+        }
+      }
+    }
+  };
+  long long row0 = (long long)blockIdx.x * ROWS_PER_BLOCK;
+  if (row0 < rows) fetch(row0);
+  for (; row0 < rows; row0 += stride) {
     const long long row = row0 + sub;
     const bool live = row < rows;
-    const long long ody = live ? row_offset(row, heads, ld_dy, d) : 0;
-    const long long ox = live ? row_offset(row, heads, ld_x, d) : 0;
     const long long odx = live ? row_offset(row, heads, ld_dx, d) : 0;
-    const float rstd = live ? rstd_in[row] : 0.f;
+    const float rstd = live ? nrstd : 0.f;
     float g[VPT][8], xh[VPT][8];
     float dot = 0.f;
 #pragma unroll
@@ -154,8 +204,8 @@ __global__ void __launch_bounds__(NORM_THREADS, VPT <= 2 ? 4 : 2)
       const int vi = tr + i * TPR;
       if (live && vi < nvec) {
         float wv[8];
-        load8(dy + ody + vi * 8, g[i]);
-        load8(x + ox + vi * 8, xh[i]);
+        unpack8(ng[i], g[i]);
+        unpack8(nx[i], xh[i]);
         load8(w + vi * 8, wv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -166,6 +216,7 @@ __global__ void __launch_bounds__(NORM_THREADS, VPT <= 2 ? 4 : 2)
         }
       }
     }
+    if (row0 + stride < rows) fetch(row0 + stride);
     dot = row_sum<TPR>(dot, red) / (float)d;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
@@ -376,15 +427,16 @@ __global__ void rope_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, co
   }
 }
 
-// q / k normalisation fused with the rotary embedding:  y = rope(bf16(rmsnorm(x) * w)).
+// q / k normalisation fused with the rotary embedding:  y = rope(rmsnorm(x) * w).
 // A row (d elements, the span of one RMS statistic) is d / hd heads of hd elements: d == hd for a head-wise norm,
 // d == n_heads * hd for a norm over the whole projection.  A thread owns PPT "pairs": 8 elements of the first half
 // of a head and the 8 elements of the second half that rotate with them, so the rotation needs no exchange.
-// Position of a row on the table axis: (row / heads) % S.  The normalised value is rounded to bf16 before the
-// rotation, which is what the two separate kernels produce.  Replaces the q_norm / k_norm + rotary sequence of
+// Position of a row on the table axis: (row / heads) % S.  The normalised value stays in fp32 until the rotation is
+// done (the two separate kernels round it to bf16 in between).  Replaces the q_norm / k_norm + rotary sequence of
 // `olmax/nn/attention.py:270-300` for RMS norms.
-__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16(v)); }
-
+// Both kernels fetch the NEXT row group's elements (as raw bf16, 4 registers per 8 elements) before they reduce the
+// current one: the block-wide sum costs two barriers per row, and without loads in flight across them the kernel
+// runs at the latency of a row, not at the memory bandwidth.
 template <int TPR, int PPT>
 __global__ void __launch_bounds__(NORM_THREADS)
     rmsnorm_rope_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
@@ -395,41 +447,60 @@ __global__ void __launch_bounds__(NORM_THREADS)
   constexpr int ROWS_PER_BLOCK = NORM_THREADS / TPR;
   const int sub = threadIdx.x / TPR, tr = threadIdx.x % TPR;
   const int half = hd / 2, pph = hd / 16, npair = d / 16;
-  for (long long row0 = (long long)blockIdx.x * ROWS_PER_BLOCK; row0 < rows; row0 += (long long)gridDim.x * ROWS_PER_BLOCK) {
+  const long long stride = (long long)gridDim.x * ROWS_PER_BLOCK;
+  int e_of[PPT];
+#pragma unroll
+  for (int i = 0; i < PPT; ++i) {
+    const int pi = tr + i * TPR;
+    e_of[i] = pi < npair ? (pi / pph) * hd + (pi % pph) * 8 : -1;
+  }
+  bf16x8 nlo[PPT], nhi[PPT];
+  auto fetch = [&](long long row0) {
+    const long long row = row0 + sub;
+    if (row < rows) {
+      const long long ox = row_offset(row, heads, ld_x, d);
+#pragma unroll
+      for (int i = 0; i < PPT; ++i)
+        if (e_of[i] >= 0) {
+          nlo[i] = load_raw8(x + ox + e_of[i]);
+          nhi[i] = load_raw8(x + ox + e_of[i] + half);
+        }
+    }
+  };
+  long long row0 = (long long)blockIdx.x * ROWS_PER_BLOCK;
+  if (row0 < rows) fetch(row0);
+  for (; row0 < rows; row0 += stride) {
     const long long row = row0 + sub;
     const bool live = row < rows;
-    const long long ox = live ? row_offset(row, heads, ld_x, d) : 0;
     const long long oy = live ? row_offset(row, heads, ld_y, d) : 0;
-    const long long pos = live ? (row / heads) % S : 0;
+    const unsigned pos = live ? ((unsigned)row / (unsigned)heads) % (unsigned)S : 0u;   // rows < 2^31 (checked by the launcher)
     float lo[PPT][8], hi[PPT][8];
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < PPT; ++i) {
-      const int pi = tr + i * TPR;
-      if (live && pi < npair) {
-        const int e = (pi / pph) * hd + (pi % pph) * 8;
-        load8(x + ox + e, lo[i]);
-        load8(x + ox + e + half, hi[i]);
+      if (live && e_of[i] >= 0) {
+        unpack8(nlo[i], lo[i]);
+        unpack8(nhi[i], hi[i]);
 #pragma unroll
         for (int j = 0; j < 8; ++j) ss += lo[i][j] * lo[i][j] + hi[i][j] * hi[i][j];
       }
     }
+    if (row0 + stride < rows) fetch(row0 + stride);
     ss = row_sum<TPR>(ss, red);
     const float rstd = rsqrtf(ss / (float)d + eps);
     if (live && tr == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
 #pragma unroll
     for (int i = 0; i < PPT; ++i) {
-      const int pi = tr + i * TPR;
-      if (live && pi < npair) {
-        const int c0 = (pi % pph) * 8, e = (pi / pph) * hd + c0;
+      if (live && e_of[i] >= 0) {
+        const int e = e_of[i], c0 = e % hd;   // e % hd < half: the pair's position inside the head's first half
         float wl[8], wh[8], c[8], sn[8], olo[8], ohi[8];
         load8(w + e, wl);
         load8(w + e + half, wh);
-        load8f(cos_t + pos * half + c0, c);
-        load8f(sin_t + pos * half + c0, sn);
+        load8f(cos_t + (size_t)pos * half + c0, c);
+        load8f(sin_t + (size_t)pos * half + c0, sn);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float nl = round_bf16(lo[i][j] * rstd * wl[j]), nh = round_bf16(hi[i][j] * rstd * wh[j]);
+          const float nl = lo[i][j] * rstd * wl[j], nh = hi[i][j] * rstd * wh[j];
           olo[j] = nl * c[j] - nh * sn[j];
           ohi[j] = nh * c[j] + nl * sn[j];
         }
@@ -440,9 +511,9 @@ __global__ void __launch_bounds__(NORM_THREADS)
   }
 }
 
-// Backward of the fused op: g = bf16(rope^T(dy)), then the RMS-norm backward with g as the incoming gradient.
+// Backward of the fused op: g = rope^T(dy), then the RMS-norm backward with g as the incoming gradient.
 template <int TPR, int PPT>
-__global__ void __launch_bounds__(NORM_THREADS, PPT <= 1 ? 4 : 2)
+__global__ void __launch_bounds__(NORM_THREADS, PPT <= 1 ? 3 : 2)
     rmsnorm_rope_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
                             const float* __restrict__ rstd_in, bf16* __restrict__ dx, float* __restrict__ dw,
                             const float* __restrict__ cos_t, const float* __restrict__ sin_t, long long rows, int d,
@@ -453,39 +524,62 @@ __global__ void __launch_bounds__(NORM_THREADS, PPT <= 1 ? 4 : 2)
   constexpr int ROWS_PER_BLOCK = NORM_THREADS / TPR;
   const int sub = threadIdx.x / TPR, tr = threadIdx.x % TPR;
   const int half = hd / 2, pph = hd / 16, npair = d / 16;
+  const long long stride = (long long)gridDim.x * ROWS_PER_BLOCK;
+  int e_of[PPT];
+#pragma unroll
+  for (int i = 0; i < PPT; ++i) {
+    const int pi = tr + i * TPR;
+    e_of[i] = pi < npair ? (pi / pph) * hd + (pi % pph) * 8 : -1;
+  }
   float dwl[PPT][8], dwh[PPT][8];
 #pragma unroll
   for (int i = 0; i < PPT; ++i)
 #pragma unroll
     for (int j = 0; j < 8; ++j) dwl[i][j] = dwh[i][j] = 0.f;
-  for (long long row0 = (long long)blockIdx.x * ROWS_PER_BLOCK; row0 < rows; row0 += (long long)gridDim.x * ROWS_PER_BLOCK) {
+  bf16x8 ndl[PPT], ndh[PPT], nxl[PPT], nxh[PPT];
+  float nrstd = 0.f;
+  auto fetch = [&](long long row0) {
+    const long long row = row0 + sub;
+    if (row < rows) {
+      const long long ody = row_offset(row, heads, ld_dy, d), ox = row_offset(row, heads, ld_x, d);
+      nrstd = rstd_in[row];
+#pragma unroll
+      for (int i = 0; i < PPT; ++i)
+        if (e_of[i] >= 0) {
+          ndl[i] = load_raw8(dy + ody + e_of[i]);
+          ndh[i] = load_raw8(dy + ody + e_of[i] + half);
+          nxl[i] = load_raw8(x + ox + e_of[i]);
+          nxh[i] = load_raw8(x + ox + e_of[i] + half);
+        }
+    }
+  };
+  long long row0 = (long long)blockIdx.x * ROWS_PER_BLOCK;
+  if (row0 < rows) fetch(row0);
+  for (; row0 < rows; row0 += stride) {
     const long long row = row0 + sub;
     const bool live = row < rows;
-    const long long ody = live ? row_offset(row, heads, ld_dy, d) : 0;
-    const long long ox = live ? row_offset(row, heads, ld_x, d) : 0;
     const long long odx = live ? row_offset(row, heads, ld_dx, d) : 0;
-    const long long pos = live ? (row / heads) % S : 0;
-    const float rstd = live ? rstd_in[row] : 0.f;
+    const unsigned pos = live ? ((unsigned)row / (unsigned)heads) % (unsigned)S : 0u;   // rows < 2^31 (checked by the launcher)
+    const float rstd = live ? nrstd : 0.f;
     float gl[PPT][8], gh[PPT][8], xl[PPT][8], xh[PPT][8];
     float dot = 0.f;
 #pragma unroll
     for (int i = 0; i < PPT; ++i) {
-      const int pi = tr + i * TPR;
-      if (live && pi < npair) {
-        const int c0 = (pi % pph) * 8, e = (pi / pph) * hd + c0;
+      if (live && e_of[i] >= 0) {
+        const int e = e_of[i], c0 = e % hd;
         float dl[8], dh[8], c[8], sn[8], wl[8], wh[8];
-        load8(dy + ody + e, dl);
-        load8(dy + ody + e + half, dh);
-        load8f(cos_t + pos * half + c0, c);
-        load8f(sin_t + pos * half + c0, sn);
-        load8(x + ox + e, xl[i]);
-        load8(x + ox + e + half, xh[i]);
+        unpack8(ndl[i], dl);
+        unpack8(ndh[i], dh);
+        unpack8(nxl[i], xl[i]);
+        unpack8(nxh[i], xh[i]);
+        load8f(cos_t + (size_t)pos * half + c0, c);
+        load8f(sin_t + (size_t)pos * half + c0, sn);
         load8(w + e, wl);
         load8(w + e + half, wh);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          float a = round_bf16(dl[j] * c[j] + dh[j] * sn[j]);   // transpose of the rotation
-          float b = round_bf16(dh[j] * c[j] - dl[j] * sn[j]);
+          float a = dl[j] * c[j] + dh[j] * sn[j];   // transpose of the rotation
+          float b = dh[j] * c[j] - dl[j] * sn[j];
           xl[i][j] *= rstd;
           xh[i][j] *= rstd;
           dwl[i][j] += a * xl[i][j];
@@ -498,12 +592,12 @@ __global__ void __launch_bounds__(NORM_THREADS, PPT <= 1 ? 4 : 2)
         }
       }
     }
+    if (row0 + stride < rows) fetch(row0 + stride);
     dot = row_sum<TPR>(dot, red) / (float)d;
 #pragma unroll
     for (int i = 0; i < PPT; ++i) {
-      const int pi = tr + i * TPR;
-      if (live && pi < npair) {
-        const int e = (pi / pph) * hd + (pi % pph) * 8;
+      if (live && e_of[i] >= 0) {
+        const int e = e_of[i];
         float ol[8], oh[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -520,9 +614,8 @@ __global__ void __launch_bounds__(NORM_THREADS, PPT <= 1 ? 4 : 2)
   __syncthreads();
 #pragma unroll
   for (int i = 0; i < PPT; ++i) {
-    const int pi = tr + i * TPR;
-    if (pi < npair) {
-      const int e = (pi / pph) * hd + (pi % pph) * 8;
+    if (e_of[i] >= 0) {
+      const int e = e_of[i];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         if (ROWS_PER_BLOCK > 1) {
@@ -792,7 +885,7 @@ extern "C" int ob_rmsnorm_rope_fwd(const void* x, const void* w, void* y, float*
                                    const float* sin_t, long long rows, int d, int hd, int heads, long long ld_x,
                                    long long ld_y, int S, float eps, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (S <= 0) OB_FAIL(-3, "rmsnorm_rope: sequence length must be positive");
+  if (S <= 0 || rows >= (1LL << 31)) OB_FAIL(-3, "rmsnorm_rope: sequence length must be positive and rows below 2^31");
   return norm_rope_dispatch(d, hd, "rmsnorm_rope", [&](auto shape) {
     using Sh = decltype(shape);
     const int rpb = NORM_THREADS / Sh::TPR;
@@ -807,7 +900,7 @@ extern "C" int ob_rmsnorm_rope_bwd(const void* dy, const void* x, const void* w,
                                    long long ld_dy, long long ld_x, long long ld_dx, int S, float dw_scale,
                                    cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (S <= 0) OB_FAIL(-3, "rmsnorm_rope: sequence length must be positive");
+  if (S <= 0 || rows >= (1LL << 31)) OB_FAIL(-3, "rmsnorm_rope: sequence length must be positive and rows below 2^31");
   const size_t smem = (size_t)d * sizeof(float);
   return norm_rope_dispatch(d, hd, "rmsnorm_rope", [&](auto shape) {
     using Sh = decltype(shape);

@@ -27,7 +27,7 @@ int ob_layernorm_bwd(const void* dy, const void* x, const void* w, const float* 
 int ob_rope(const void* x, void* y, const float* cos_t, const float* sin_t, int B, int S, int H, int D, long long sb,
             long long ss, long long sh, long long ysb, long long yss, long long ysh, float sign, int pos_offset,
             cudaStream_t stream);
-// y = rope(bf16(rmsnorm(x) * w)) in one pass (q / k normalisation followed by the rotary embedding).  A row of d
+// y = rope(rmsnorm(x) * w) in one pass (q / k normalisation followed by the rotary embedding).  A row of d
 // elements is d / hd heads; rows are addressed like ob_rmsnorm_fwd; the table row of a row is (row / heads) % S.
 int ob_rmsnorm_rope_fwd(const void* x, const void* w, void* y, float* rstd, const float* cos_t, const float* sin_t,
                         long long rows, int d, int hd, int heads, long long ld_x, long long ld_y, int S, float eps,

@@ -356,11 +356,11 @@ def test_fused_rmsnorm_rope_matches_the_two_kernels_and_the_fp32_reference(K, B,
     y, rstd = torch.empty_like(x), torch.empty(rows, device=dev, dtype=torch.float32)
     K.rmsnorm_rope_fwd(x, w, y, rstd, cos, sin, rows=rows, d=d, hd=hd, heads=heads, seq_len=S, eps=1e-5, ld_x=width,
                        ld_y=width)
-    # the same through the separate kernels: identical up to the order of the row sums
+    # the same through the separate kernels, which round the normalised value to bf16 before the rotation
     yn, rstd2, y2 = torch.empty_like(x), torch.empty_like(rstd), torch.empty_like(x)
     K.rmsnorm_fwd(x, w, yn, rows=rows, d=d, eps=1e-5, rstd=rstd2, heads=heads, ld_x=width, ld_y=width)
     K.rope(yn.view(B, S, n, hd), y2.view(B, S, n, hd), cos, sin)
-    assert rel_err(y, y2) < 2e-3 and rel_err(rstd, rstd2) < 1e-5
+    assert rel_err(y, y2) < 4e-3 and rel_err(rstd, rstd2) < 1e-5
     xf, wf = x.float().requires_grad_(True), w.float().requires_grad_(True)
     want = ref.apply_rope(ref.rms_norm(xf.view(T, heads, d), wf, 1e-5).view(B, S, n, hd), cos, sin)
     assert rel_err(y.view(B, S, n, hd), want) < 6e-3
