@@ -142,6 +142,7 @@ def test_gemm_gated_epilogue(K, gelu):
     (2, 2048, 16, 4, True, -1, 0.0),      # more work items than SMs: several items per persistent CTA
     (3, 1024, 5, 5, True, 300, 0.0),      # 15 (batch, head) slices: a partly filled scheduling group; window
     (1, 900, 3, 1, False, -1, 0.0),       # no mask, ragged length, equal-weight items
+    (1, 2048, 8, 2, True, 512, 30.0),     # window + soft-cap + grouped heads together (the Gemma-like layer)
 ])
 def test_flash_attention(K, B, S, H, Hkv, causal, window, softcap):
     dev = "cuda"
