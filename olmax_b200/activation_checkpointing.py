@@ -4,6 +4,10 @@ Activation-checkpointing policies (registry names of ``olmax/activation_checkpoi
 A policy decides, for a named region of the model (a transformer layer ``layers.{i}`` or one of its sub-blocks
 ``layers.{i}.attention`` / ``layers.{i}.mlp``), whether the activations inside it are kept for the backward pass or
 recomputed from the region's input.  Recomputation re-invokes the same kernels; there is no compiler pass involved.
+Whole layers are recomputed through a checkpoint; the two sub-blocks recompute inside their own autograd nodes, so
+that only what is cheap runs twice: the MLP block keeps its input and repeats the gate / up GEMM (not the down
+projection), the attention block keeps its input, its output and the softmax statistics and repeats the q / k / v
+projections with their norm and rotation (neither the attention forward nor the output projection).
 
 Mapping of the reference's policy names:
 

@@ -48,7 +48,12 @@ class _LayerBase(Module):
         # already is (a nested checkpoint would run the sub-block's forward a third time)
         self._attn_fn, self._mlp_fn = self._attention_block, self._mlp_block
         if not self._whole_layer:
-            self._attn_fn = policy.wrap(self._attention_block, f"{self.checkpoint_name}.attention")
+            # the attention block rebuilds q / k / v inside its own autograd node (neither the attention forward nor the
+            # output projection runs again); only under context parallelism is it wrapped in a checkpoint
+            if self.attention.recomputes_itself:
+                self.attention.recompute = policy.should_recompute(f"{self.checkpoint_name}.attention")
+            else:
+                self._attn_fn = policy.wrap(self._attention_block, f"{self.checkpoint_name}.attention")
             # the MLP block recomputes inside its own autograd node (only its gate/up GEMM runs again) instead of being
             # wrapped in a checkpoint, which would also repeat the down projection
             self.mlp.recompute = policy.should_recompute(f"{self.checkpoint_name}.mlp")

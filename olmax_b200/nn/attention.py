@@ -112,11 +112,14 @@ class MultiheadSelfAttention(Module):
             with ctx.scope("k_norm"):
                 self.k_norm = qk_norm.build(kn)
         self.rope = rope.build(self.head_dim) if rope is not None else None
+        self.recompute = False
+        """Set by the layer when the activation-checkpointing policy recomputes this block: q / k / v are rebuilt in the
+        block's own backward node instead of being kept (``ops/functional.py: recomputed_attention``)."""
         self.sdpa = AttentionKernel(self.head_dim, window_size=window_size, logit_softcap=logit_softcap,
                                     cp_strategy=cp_strategy, cp_group=self.mesh.cp)
 
-    def forward(self, x: torch.Tensor, batch_size: int, cache: Optional[BufferCache] = None) -> torch.Tensor:
-        """x: [tokens, d_model] (tokens = batch * seq, or that divided by tp under sequence parallelism)."""
+    def _qkv(self, x: torch.Tensor, batch_size: int, cache: Optional[BufferCache]):
+        """Block input -> (q [B,S,H,D], k, v [B,S,Hkv,D]): projections, q / k norm, rotation."""
         tp = self.mesh.tp
         tpc = self.store.tp_symm if x.is_cuda else None
         if tpc is not None:
@@ -148,7 +151,25 @@ class MultiheadSelfAttention(Module):
                 cp = self.mesh.cp
                 q = self.rope(q, cache, cp.size, cp.rank)
                 k = self.rope(k, cache, cp.size, cp.rank)
-        o = self.sdpa(q, k, v).reshape(T, self.local_heads * self.head_dim)
+        return q, k, v
+
+    @property
+    def recomputes_itself(self) -> bool:
+        """True when the block can drop q / k / v after the forward pass and rebuild them in its own backward node
+        (not under context parallelism, whose attention is a composition of block kernels with its own backward)."""
+        return self.mesh.cp.size == 1
+
+    def forward(self, x: torch.Tensor, batch_size: int, cache: Optional[BufferCache] = None) -> torch.Tensor:
+        """x: [tokens, d_model] (tokens = batch * seq, or that divided by tp under sequence parallelism)."""
+        tp = self.mesh.tp
+        tpc = self.store.tp_symm if x.is_cuda else None
+        if self.recompute and self.recomputes_itself and torch.is_grad_enabled() and x.requires_grad:
+            k = self.sdpa
+            o = F.recomputed_attention(x, lambda t: self._qkv(t, batch_size, cache),
+                                       k.window_size if k.window_size is not None else -1, k.logit_softcap or 0.0, k.scale)
+        else:
+            o = self.sdpa(*self._qkv(x, batch_size, cache))
+        o = o.reshape(-1, self.local_heads * self.head_dim)
         if tpc is not None:
             return F.tp_row_linear(o, tpc, self.o_proj.weight)   # reduce-scatter fused into the GEMM epilogue
         y = self.o_proj(o)

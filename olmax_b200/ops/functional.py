@@ -683,6 +683,43 @@ def attention(q, k, v, causal: bool = True, window: int = -1, softcap: float = 0
     return _AttentionFn.apply(q, k, v, causal, window if window is not None else -1, softcap or 0.0, scale)
 
 
+class _RecomputedAttentionFn(torch.autograd.Function):
+    """The q / k / v projections (with their norm and rotation) and the attention as ONE autograd node that keeps only
+    the block input, the attention output and its row statistics.  Backward runs the projections again to get q, k, v
+    (their own nodes then take the weight gradients as usual), but neither the attention forward nor anything after
+    it.  This is what the activation-checkpointing policies that name ``layers.*.attention`` select
+    (``olmax/activation_checkpointing.py:19-182``); a plain checkpoint of the block would also repeat the attention
+    forward and the output projection."""
+
+    @staticmethod
+    def forward(ctx, x, qkv_fn, window, softcap, scale):
+        with torch.no_grad():
+            q, k, v = qkv_fn(x)
+            o, lse = attention_block_fwd(q, k, v, window=window, softcap=softcap, scale=scale)
+        ctx.qkv_fn, ctx.cfg = qkv_fn, (window, softcap, scale)
+        ctx.save_for_backward(x, o, lse)
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        x, o, lse = ctx.saved_tensors
+        window, softcap, scale = ctx.cfg
+        with torch.enable_grad():
+            xd = x.detach().requires_grad_(True)
+            q, k, v = ctx.qkv_fn(xd)
+        dq, dk, dv = attention_block_bwd(q.detach(), k.detach(), v.detach(), o, lse, d_o, window=window, softcap=softcap,
+                                         scale=scale)
+        torch.autograd.backward([q, k, v], [dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)])
+        return xd.grad, None, None, None, None
+
+
+def recomputed_attention(x: torch.Tensor, qkv_fn, window: int = -1, softcap: float = 0.0,
+                         scale: Optional[float] = None) -> torch.Tensor:
+    """``attention(*qkv_fn(x))`` (causal) keeping only x, the output and the row statistics for the backward pass; see
+    :class:`_RecomputedAttentionFn`.  ``qkv_fn`` maps the block input to (q [B,S,H,D], k, v [B,S,Hkv,D])."""
+    return _RecomputedAttentionFn.apply(x, qkv_fn, window if window is not None else -1, softcap or 0.0, scale)
+
+
 def attention_block_fwd(q, k, v, *, q_off: int = 0, causal: bool = True, window: int = -1, softcap: float = 0.0,
                         scale: Optional[float] = None):
     """One (query block, key block) pair without autograd: q [B,S,H,D], k/v [B,Sk,Hkv,D], query row i at key-axis

@@ -281,6 +281,45 @@ def test_gated_mlp_selective_recomputation_keeps_only_its_input():
         assert F.gated_mlp(x, *w, "silu", recompute=True).shape == (7, 16)
 
 
+@pytest.mark.parametrize("kv,qk_norm,window,softcap", [(None, True, None, None), (2, False, 4, 20.0)])
+def test_attention_block_recomputation_keeps_input_output_and_statistics(kv, qk_norm, window, softcap):
+    """recompute=True: same values and gradients; the block's node holds x, the attention output and the row
+    statistics instead of q, k, v and everything the projections, norms and rotation keep."""
+    cfg = MultiheadSelfAttentionConfig(n_heads=4, n_kv_heads=kv, head_dim=8, qk_norm=RMSNormConfig() if qk_norm else None,
+                                       rope=RotaryPositionalEmbeddingConfig(theta=1e4), window_size=window,
+                                       logit_softcap=softcap)
+    att = _build(lambda: cfg.build(32))
+    B, S = 2, 10
+    x = torch.randn(B * S, 32)
+    outs = {}
+    for recompute in (False, True):
+        att.recompute = recompute
+        att.store.zero_grad()
+        xi = x.clone().requires_grad_(True)
+        y = att(xi * 1.0, B)          # the block input is a non-leaf, as inside a layer
+        y.square().sum().backward()
+        outs[recompute] = (y.detach(), xi.grad.clone(), att.store.grad.clone())
+    for a, b in zip(outs[False], outs[True]):
+        assert torch.allclose(a, b, atol=1e-5), (a - b).abs().max()
+    # the node of the recomputed block saves three tensors: x, o, lse
+    att.recompute = True
+    y = att((x.clone().requires_grad_(True)) * 1.0, B)
+    node = y.grad_fn
+    seen, stack, found = set(), [node], None
+    while stack:
+        n = stack.pop()
+        if n is None or n in seen:
+            continue
+        seen.add(n)
+        if "RecomputedAttention" in type(n).__name__:
+            found = n
+            break
+        stack.extend(f for f, _ in n.next_functions)
+    assert found is not None and len(found.saved_tensors) == 3
+    with torch.no_grad():      # nothing to recompute without a backward pass
+        assert att(x, B).shape == (B * S, 32)
+
+
 def test_cross_entropy_counts_out_of_range_labels_in_mean_and_z_loss():
     """A label outside [0, V) that is not ``ignore_index`` (the sequential synthetic data yields label == V) has no
     cross-entropy term but stays in the mean and in the z-loss, as in the reference's ``fused_cross_entropy_loss``
