@@ -911,7 +911,8 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
   memset(&tB2, 0, sizeof(tB2));
   int rc;
   kp.a_single = kp.b_single = 0;
-  if (a->a_mn && a->M % 64 == 0 && !a->multi_box_mn) {
+  // (every tile must start on a multiple of 64 along M: with row shards of M_s rows, tile starts are s * M_s + 128 t)
+  if (a->a_mn && a->M % 64 == 0 && M_s % 64 == 0 && !a->multi_box_mn) {
     // view [Kc, M] as (64, Kc, M/64): a tile is ONE box of 64 x 64 x 2, which lands in shared memory as two
     // [64 k][128 B] blocks, the MN-major layout the MMA descriptor expects
     uint64_t dims[4] = {64, (uint64_t)a->Kc, (uint64_t)a->M / 64, 1};

@@ -112,6 +112,30 @@ def test_gemm_sharded_operands(K):
     _check_status()
 
 
+@pytest.mark.parametrize("N,Kd,M,R,epi_name", [
+    (4096, 4096, 8192, 4, "bf16"),
+    (4096, 4096, 8192, 2, "f32"),
+    (11008, 1024, 4096, 8, "bf16"),    # 1376-row shards: partly filled tiles at every shard boundary
+])
+def test_gemm_store_to_shards(K, N, Kd, M, R, epi_name):
+    """Weight-gradient GEMM whose row blocks are stored into per-owner buffers in either wire format (the fused
+    reduce-scatter's epilogue, here with all owners on this GPU)."""
+    dev = "cuda"
+    torch.manual_seed(13)
+    dy = torch.randn(M, N, device=dev, dtype=torch.bfloat16) * 0.25
+    x = torch.randn(M, Kd, device=dev, dtype=torch.bfloat16) * 0.25
+    dtype = torch.bfloat16 if epi_name == "bf16" else torch.float32
+    rows = N // R
+    outs = [torch.full((rows, Kd), float("nan"), device=dev, dtype=dtype) for _ in range(R)]
+    table = K.pointer_table([o.data_ptr() for o in outs], torch.device(dev))
+    K.gemm(dy, x, outs[0], N, Kd, M, a_mn=True, b_mn=True, epi=K.EPI_BF16 if epi_name == "bf16" else K.EPI_F32, ldc=Kd,
+           M_s=rows, c_shards=table)
+    got = torch.cat(outs).float()
+    assert torch.isfinite(got).all()
+    assert rel_err(got, dy.float().t() @ x.float()) < (5e-3 if epi_name == "bf16" else 1e-4)
+    _check_status()
+
+
 @pytest.mark.parametrize("gelu", [False, True])
 def test_gemm_gated_epilogue(K, gelu):
     dev = "cuda"
