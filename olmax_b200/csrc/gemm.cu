@@ -1034,7 +1034,10 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
   memset(&tC, 0, sizeof(tC));
   kp.tma_epi = 0;
   const bool tma_ok = (a->epi == EPI_BF16 || a->epi == EPI_F32 || a->epi == EPI_F32_ACC) && a->c_shards == nullptr &&
-                      !a->no_tma_epilogue && (kp.m_shards == 1 || a->c_shard_stride > 0 || M_s % BM == 0);
+                      !a->no_tma_epilogue && (kp.m_shards == 1 || a->c_shard_stride > 0 || M_s % BM == 0) &&
+                      // the store clips at the end of the matrix, not at a column shard's end: a shard's last tile may
+                      // only be written in whole 64-column chunks
+                      (kp.n_shards == 1 || N_s % 64 == 0);
   if (tma_ok) {
     const bool f32 = a->epi != EPI_BF16;
     const uint64_t es = f32 ? 4 : 2;

@@ -112,6 +112,29 @@ def test_gemm_sharded_operands(K):
     _check_status()
 
 
+def test_gemm_column_shards_that_end_inside_a_store_chunk(K):
+    """Forward GEMM over weights gathered as 8 row shards of 1376 rows (11008 / 8): a shard's last tile holds 96 output
+    columns, so the epilogue must not write whole 64-column chunks across the shard's end."""
+    dev = "cuda"
+    torch.manual_seed(3)
+    R, N, Kd, M = 8, 11008, 512, 1024
+    Ns, gap = N // R, 4096
+    x = torch.randn(M, Kd, device=dev, dtype=torch.bfloat16) * 0.25
+    W = torch.randn(N, Kd, device=dev, dtype=torch.bfloat16) * 0.05
+    stride = Ns * Kd + gap
+    buf = torch.zeros(R * stride, device=dev, dtype=torch.bfloat16)
+    for r in range(R):
+        buf[r * stride : r * stride + Ns * Kd] = W[r * Ns : (r + 1) * Ns].reshape(-1)
+    y = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    K.gemm(x, buf, y, M, N, Kd, ldb=Kd, ldc=N, N_s=Ns, b_shard_stride=stride)
+    assert rel_err(y, x.float() @ W.float().t()) < 5e-3
+    dy = torch.randn(M, N, device=dev, dtype=torch.bfloat16) * 0.25
+    dx = torch.empty(M, Kd, device=dev, dtype=torch.bfloat16)
+    K.gemm(dy, buf, dx, M, Kd, N, b_mn=True, ldb=Kd, ldc=Kd, Kc_s=Ns, b_shard_stride=stride)   # contraction over the shards
+    assert rel_err(dx, dy.float() @ W.float()) < 5e-3
+    _check_status()
+
+
 @pytest.mark.parametrize("N,Kd,M,R,epi_name", [
     (4096, 4096, 8192, 4, "bf16"),
     (4096, 4096, 8192, 2, "f32"),
