@@ -24,15 +24,15 @@ def _check():
     _lib.check_status()
 
 
-@pytest.mark.parametrize("rank", [0, 2])
-def test_all_gather_fused_gemm_single_gpu_emulation(rank):
+@pytest.mark.parametrize("rank,N,R", [(0, 2048, 4), (2, 2048, 4), (5, 11008, 8)])   # 11008 / 8: 1376-row shards
+def test_all_gather_fused_gemm_single_gpu_emulation(rank, N, R):
     if not torch.cuda.is_available():
         pytest.skip("needs a GPU")
     from olmax_b200.ops import kernels as K
 
     dev = torch.device("cuda")
     torch.manual_seed(20)
-    M, N, Kd, R = 1024, 2048, 512, 4
+    M, Kd = 1024, 512
     rows = N // R
     w = torch.randn(N, Kd, device=dev, dtype=torch.bfloat16)
     a = torch.randn(M, Kd, device=dev, dtype=torch.bfloat16)
