@@ -68,3 +68,16 @@ def test_tiny_llama_loss_curve_matches_single_process(tmp_path, single_process_c
         assert len(curve) == 10
         for got, want in zip(curve, single_process_curve):
             assert got == pytest.approx(want, rel=2e-4), (curve, single_process_curve)
+
+
+def test_eight_ranks_fsdp_and_hsdp_2x4_train_alike(tmp_path):
+    """The host side of the 8-GPU configurations (FSDP over 8, HSDP as 2 replicas of 4 shards) on 8 CPU ranks: same
+    global batch, so the same loss curve on every rank of both meshes."""
+    fsdp = run_distributed_test(_entry_worker, world_size=8, func_args=("FSDP", [], 1, str(tmp_path / "a")), timeout=600)
+    hsdp = run_distributed_test(_entry_worker, world_size=8, func_args=("HSDP", ["--shard-degree=4"], 1, str(tmp_path / "b")),
+                                timeout=600)
+    for curve in fsdp + hsdp:
+        assert len(curve) == 10
+        for got, want in zip(curve, fsdp[0]):
+            assert got == pytest.approx(want, rel=2e-4)
+
