@@ -7,9 +7,12 @@
 // memory.  Each query tile has its own softmax warpgroup (4 warps, one thread per query row, the whole 128-score
 // row in registers, so no exchange between threads), and the MMA warp interleaves the two tiles:
 //     P V (tile 0, keys j), Q K^T (tile 0, keys j+1), P V (tile 1, keys j), Q K^T (tile 1, keys j+1), ...
-// so that the tensor cores work on one tile while the other tile is in its softmax.  K and V tiles go through
-// two-stage rings shared by both query tiles.  The running maximum is only raised when it grows by more than 2^8
-// ("lazy rescale"), which keeps the O correction (a TMEM read-modify-write) off most iterations.
+// so that the tensor cores work on one tile while the other tile is in its softmax.  P is announced in two halves, so
+// that P V of the first 64 keys runs under the exponentials of the rest.  K and V tiles go through rings shared by
+// both query tiles (three K stages, two V stages; K is loaded one tile ahead of V because the next Q K^T is issued
+// before the current P V).  The softmax warpgroups take registers from the producer warpgroup (`setmaxnreg`), so that
+// the 128-score row stays in registers without spills.  The running maximum is only raised when it grows by more
+// than 2^8 ("lazy rescale"), which keeps the O correction (a TMEM read-modify-write) off most iterations.
 //
 // Work items are handed out heaviest first inside groups of eight (batch, head) slices, so that the CTAs that run
 // at the same time read the K / V of few heads (L2 reuse) and the light items fill the tail.
