@@ -874,6 +874,9 @@ extern "C" int ob_gemm_bf16(const ObGemmArgs* a, cudaStream_t stream) {
     const long long pair_tiles = (long long)kp.m_shards * ((M_s + 2 * BM - 1) / (2 * BM)) * n_t;
     const long long single_tiles = (long long)kp.m_shards * ((M_s + BM - 1) / BM) * n_t;
     CG = (pair_tiles >= cap / 2 || single_tiles == pair_tiles) ? 2 : 1;
+    // row shards of at most 128 rows (e.g. the k / v weight gradients of a grouped-query model over 8 GPUs): the
+    // second CTA of every pair would have no rows at all
+    if (kp.m_shards > 1 && M_s <= BM) CG = 1;
   }
   if (cap < 2) CG = 1;
   const int BMT = BM * CG;            // tile rows

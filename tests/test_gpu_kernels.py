@@ -139,6 +139,7 @@ def test_gemm_column_shards_that_end_inside_a_store_chunk(K):
     (4096, 4096, 8192, 4, "bf16"),
     (4096, 4096, 8192, 2, "f32"),
     (11008, 1024, 4096, 8, "bf16"),    # 1376-row shards: partly filled tiles at every shard boundary
+    (1024, 5120, 2048, 8, "bf16"),     # 128-row shards (k / v of a grouped-query model over 8 owners): single-CTA tiles
 ])
 def test_gemm_store_to_shards(K, N, Kd, M, R, epi_name):
     """Weight-gradient GEMM whose row blocks are stored into per-owner buffers in either wire format (the fused
