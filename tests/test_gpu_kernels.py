@@ -112,6 +112,51 @@ def test_gemm_sharded_operands(K):
     _check_status()
 
 
+@pytest.mark.parametrize("rows", [128, 352, 640, 1152, 1376])
+def test_gemm_every_sharded_layout_over_shard_sizes(K, rows):
+    """The five GEMM forms of a linear layer whose weight is split into R row shards of ``rows`` rows (forward, gated
+    forward, dgrad, weight gradient accumulated into a sharded buffer, weight gradient stored to per-owner buffers),
+    for shard sizes that are and are not multiples of 64 / 128 / 256: the sizes 8-way sharding produces for real
+    models (1376 = 11008 / 8, 640 = 5120 / 8, 1152 = 4608 / 4, 128 = 1024 / 8)."""
+    dev = "cuda"
+    torch.manual_seed(rows)
+    R, Kd, M, gap = 4, 256, 512, 1024
+    N = R * rows
+    x = torch.randn(M, Kd, device=dev, dtype=torch.bfloat16) * 0.25
+    W = torch.randn(N, Kd, device=dev, dtype=torch.bfloat16) * 0.1
+    W2 = torch.randn(N, Kd, device=dev, dtype=torch.bfloat16) * 0.1
+    stride = rows * Kd + gap
+
+    def pieces(w):
+        buf = torch.zeros(R * stride, device=dev, dtype=torch.bfloat16)
+        for r in range(R):
+            buf[r * stride : r * stride + rows * Kd] = w[r * rows : (r + 1) * rows].reshape(-1)
+        return buf
+
+    b1, b2 = pieces(W), pieces(W2)
+    y = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    K.gemm(x, b1, y, M, N, Kd, ldb=Kd, ldc=N, N_s=rows, b_shard_stride=stride)
+    assert rel_err(y, x.float() @ W.float().t()) < 5e-3, "forward"
+    act, cg, cu = torch.empty_like(y), torch.empty_like(y), torch.empty_like(y)
+    K.gemm(x, b1, act, M, N, Kd, ldb=Kd, ldc=N, N_s=rows, b_shard_stride=stride, epi=K.EPI_SWIGLU, b2=b2, c2=cg, c3=cu)
+    g, u = x.float() @ W.float().t(), x.float() @ W2.float().t()
+    assert rel_err(cg, g) < 5e-3 and rel_err(cu, u) < 5e-3 and rel_err(act, torch.nn.functional.silu(g) * u) < 1e-2, "gated"
+    dy = torch.randn(M, N, device=dev, dtype=torch.bfloat16) * 0.25
+    dx = torch.empty(M, Kd, device=dev, dtype=torch.bfloat16)
+    K.gemm(dy, b1, dx, M, Kd, N, b_mn=True, ldb=Kd, ldc=Kd, Kc_s=rows, b_shard_stride=stride)
+    assert rel_err(dx, dy.float() @ W.float()) < 5e-3, "dgrad"
+    want = dy.float().t() @ x.float()
+    acc = torch.zeros(R, stride, device=dev, dtype=torch.float32)
+    K.gemm(dy, x, acc, N, Kd, M, a_mn=True, b_mn=True, epi=K.EPI_F32_ACC, ldc=Kd, M_s=rows, c_shard_stride=stride)
+    got = torch.cat([acc[r, : rows * Kd].view(rows, Kd) for r in range(R)])
+    assert rel_err(got, want) < 1e-4, "wgrad into a sharded accumulator"
+    outs = [torch.full((rows, Kd), float("nan"), device=dev, dtype=torch.bfloat16) for _ in range(R)]
+    table = K.pointer_table([o.data_ptr() for o in outs], torch.device(dev))
+    K.gemm(dy, x, outs[0], N, Kd, M, a_mn=True, b_mn=True, epi=K.EPI_BF16, ldc=Kd, M_s=rows, c_shards=table)
+    assert rel_err(torch.cat(outs), want) < 5e-3, "wgrad stored to the owners"
+    _check_status()
+
+
 def test_gemm_column_shards_that_end_inside_a_store_chunk(K):
     """Forward GEMM over weights gathered as 8 row shards of 1376 rows (11008 / 8): a shard's last tile holds 96 output
     columns, so the epilogue must not write whole 64-column chunks across the shard's end."""
