@@ -117,6 +117,18 @@ def comm_selfcheck(args, model_cfg, mesh, mesh_res, dev, seq, inst_local, k):
             "layers": 2, "optimizer_steps": 2, "microbatches": k, "tolerance": 1e-2}
 
 
+def selfcheck_verdict(selfcheck: dict, comm: str, tolerance: float = 1e-2):
+    """What a multi-GPU run does with the result of :func:`comm_selfcheck`: ``("ok", [])`` when every difference is
+    within the tolerance (a NaN is not), else ``("fail", names)`` when the fused backend was asked for explicitly and
+    ``("fallback", names)`` with ``--comm auto`` (the NCCL backend is measured instead)."""
+    if "skipped" in selfcheck:
+        return "ok", []
+    bad = [n for n in ("loss_rel", "grad_rel", "param_rel_after_2_steps") if not (selfcheck.get(n, 0.0) <= tolerance)]
+    if not bad:
+        return "ok", []
+    return ("fail" if comm == "fused" else "fallback"), bad
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons of this rank's GPU with nvidia-smi while the timed region runs."""
 
@@ -258,12 +270,12 @@ def main() -> int:
     selfcheck = None
     if world > 1 and args.comm in ("auto", "fused") and not args.skip_selfcheck:
         selfcheck = comm_selfcheck(args, model_cfg, mesh, mesh_res, dev, seq, inst_local, k)
-        bad = [n for n in ("loss_rel", "grad_rel", "param_rel_after_2_steps") if not (selfcheck.get(n, 0.0) <= 1e-2)]
-        if bad and args.comm == "fused":
+        action, bad = selfcheck_verdict(selfcheck, args.comm)
+        if action == "fail":
             if rank == 0:
                 print(json.dumps({"error": "fused and NCCL backends disagree", "selfcheck": selfcheck}), flush=True)
             return 2
-        if bad:
+        if action == "fallback":
             # Never time a backend that failed its check, and never report nothing: with --comm auto the measurement
             # falls back to the NCCL backend (the values are the all-reduced maxima, so every rank decides alike) and
             # the JSON line says so in "selfcheck" and "config".
